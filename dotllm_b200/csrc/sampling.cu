@@ -1,0 +1,372 @@
+// Token selection on the device: repetition penalty, greedy argmax, and the sampled chain
+// temperature -> top-k -> top-p -> min-p -> categorical draw, one thread block per row.
+//
+// Semantics follow the reference's host-side samplers:
+//   RepetitionPenaltyProcessor.cs:14-55  each distinct recent id once: logit>0 ? /p : *p
+//   SamplerPipeline.cs:141-157           processors, argmax if greedy, else steps, then draw
+//   TemperatureSampler.cs:22-29          logits *= 1/T, skipped for T == 1
+//   TopKSampler.cs:32-79                 keep the k largest; ties at the k-th value admitted in
+//                                        index order until exactly k are kept
+//   TopPSampler.cs:23-81                 smallest set of most probable tokens reaching p
+//   MinPSampler.cs:23-37                 mask logit < max + ln(min_p)
+//   CategoricalSampler.cs:18-41          first index whose running probability exceeds r
+// (all under src/DotLLM.Engine/Samplers/).
+//
+// Nothing is sorted.  Thresholds are found by an 8-bit radix descent over order-preserving
+// integer keys of the logits, by count for top-k and by probability mass for top-p.  Masses
+// are exp(v - max) in float32 converted to 32.32 fixed point and summed as integers, so every
+// sum is exact, independent of thread order, and a seeded draw is reproducible bit for bit.
+#include "common.cuh"
+
+#define SMP_THREADS 1024
+#define SMP_ITEMS 4
+typedef unsigned long long u64;
+
+__device__ __forceinline__ uint32_t smp_key(float v) {          // ascending float order -> ascending uint
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float smp_unkey(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ u64 smp_mass(float v, float vmax) {   // exp(v - vmax) in 32.32 fixed point
+    return __float2ull_rn(expf(v - vmax) * 4294967296.0f);
+}
+
+template <typename V>
+__device__ __forceinline__ V smp_block_sum(V v, V* scratch /* 33 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        V w = lane < (SMP_THREADS / 32) ? scratch[lane] : (V)0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+        if (lane == 0) scratch[32] = w;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Exclusive prefix sum over the block in thread order; *total receives the block's sum.
+template <typename V>
+__device__ __forceinline__ V smp_block_scan(V v, V* scratch /* 33 */, V* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    V inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        V n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    __syncthreads();
+    if (lane == 31) scratch[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        V w = lane < (SMP_THREADS / 32) ? scratch[lane] : (V)0;
+        V winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            V n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        scratch[lane] = winc - w;                  // exclusive offset of each warp
+        if (lane == 31) scratch[32] = winc;
+    }
+    __syncthreads();
+    *total = scratch[32];
+    return scratch[warp] + inc - v;
+}
+
+struct SmpShared {
+    u64 hist_mass[256];
+    unsigned int hist_count[256];
+    u64 scratch64[33];
+    int scratch32[33];
+    float red_val[32];
+    int red_idx[32];
+    uint32_t prefix;
+    u64 above;          // mass or count strictly above the chosen bin
+    unsigned int equal;  // elements in the chosen bin (after the last pass: equal to the key)
+    int found;
+};
+
+// Radix descent.  BY_MASS: find the key at which the mass of keys >= it first reaches
+// `target`; else the key with `target` elements at or above it.  Elements below `low_key` are
+// ignored; of those equal to low_key only `low_allowed` of `low_equal` count.
+template <bool BY_MASS>
+__device__ void smp_select(SmpShared& sh, const float* x, int V, float inv_t, float vmax, uint32_t low_key,
+                           unsigned int low_allowed, unsigned int low_equal, u64 target, uint32_t* key_out,
+                           u64* above_out, unsigned int* equal_out) {
+    uint32_t prefix = 0;
+    u64 above = 0;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int b = threadIdx.x; b < 256; b += SMP_THREADS) { sh.hist_mass[b] = 0; sh.hist_count[b] = 0; }
+        __syncthreads();
+        for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
+            float v = x[i] * inv_t;
+            if (v != v) v = -INFINITY;
+            const uint32_t key = smp_key(v);
+            if (key < low_key) continue;
+            if (pass > 0 && (key >> (shift + 8)) != prefix) continue;
+            const int bin = (key >> shift) & 255;
+            atomicAdd(&sh.hist_count[bin], 1u);
+            if (BY_MASS) atomicAdd(&sh.hist_mass[bin], smp_mass(v, vmax));
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            // Only `low_allowed` of the `low_equal` elements at low_key take part.
+            if (low_equal > low_allowed && (pass == 0 || (low_key >> (shift + 8)) == prefix)) {
+                const int bin = (low_key >> shift) & 255;
+                sh.hist_count[bin] -= (low_equal - low_allowed);
+                if (BY_MASS) sh.hist_mass[bin] -= (u64)(low_equal - low_allowed) * smp_mass(smp_unkey(low_key), vmax);
+            }
+            int digit = 0;
+            u64 cum = above;
+            for (int b = 255; b >= 0; --b) {
+                const u64 w = BY_MASS ? sh.hist_mass[b] : (u64)sh.hist_count[b];
+                if (sh.hist_count[b] != 0 && cum + w >= target) { digit = b; break; }
+                cum += w;
+                if (b == 0) {                       // target beyond the total: settle on the lowest used bin
+                    for (int c = 0; c < 256; ++c)
+                        if (sh.hist_count[c] != 0) { digit = c; break; }
+                    cum = above;
+                    for (int c = 255; c > digit; --c) cum += BY_MASS ? sh.hist_mass[c] : (u64)sh.hist_count[c];
+                }
+            }
+            sh.prefix = (pass == 0 ? 0u : (prefix << 8)) | (uint32_t)digit;
+            sh.above = cum;
+            sh.equal = sh.hist_count[digit];
+        }
+        __syncthreads();
+        prefix = sh.prefix;
+        above = sh.above;
+    }
+    *key_out = prefix;
+    *above_out = above;
+    *equal_out = sh.equal;
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(SMP_THREADS)
+sample_kernel(const float* __restrict__ logits, int row_stride, int V, const float* __restrict__ temperature,
+              const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ min_p, const float* __restrict__ uniform, int32_t* __restrict__ out) {
+    __shared__ SmpShared sh;
+    const int row = blockIdx.x;
+    const float* x = logits + (size_t)row * row_stride;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float temp = temperature ? temperature[row] : 0.f;
+    const float inv_t = (temp > 0.f && temp != 1.0f) ? 1.0f / temp : 1.0f;
+
+    // ---- maximum and its first index (the greedy answer and the softmax shift)
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
+        float v = x[i] * inv_t;
+        if (v != v) v = -INFINITY;
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) { sh.red_val[warp] = best; sh.red_idx[warp] = best_i; }
+    __syncthreads();
+    if (warp == 0) {
+        best = sh.red_val[lane];
+        best_i = sh.red_idx[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+        }
+        if (lane == 0) { sh.red_val[0] = best; sh.red_idx[0] = best_i; }
+    }
+    __syncthreads();
+    const float vmax = sh.red_val[0];
+    const int arg_max = sh.red_idx[0] < V ? sh.red_idx[0] : 0;
+    __syncthreads();
+    if (!(temp > 0.f) || vmax == -INFINITY) {        // greedy, or nothing finite to draw from
+        if (threadIdx.x == 0) out[row] = arg_max;
+        return;
+    }
+
+    // ---- thresholds: everything above low_key is kept, and `allowed` of the `equal` at it
+    uint32_t low_key = 0;
+    unsigned int allowed = 0, equal = 0;
+    const int k = top_k ? top_k[row] : 0;
+    if (k > 0 && k < V) {
+        u64 above;
+        smp_select<false>(sh, x, V, inv_t, vmax, 0u, 0u, 0u, (u64)k, &low_key, &above, &equal);
+        allowed = (unsigned int)((u64)k - above);
+        if (allowed > equal) allowed = equal;
+    }
+    const float p = top_p ? top_p[row] : 1.0f;
+    if (p < 1.0f) {
+        u64 part = 0;
+        for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
+            float v = x[i] * inv_t;
+            if (v != v) v = -INFINITY;
+            if (smp_key(v) > low_key) part += smp_mass(v, vmax);
+        }
+        u64 z1 = smp_block_sum<u64>(part, sh.scratch64);
+        z1 += (u64)allowed * smp_mass(smp_unkey(low_key), vmax);
+        double want = ceil((double)p * (double)z1);
+        u64 target = want < 1.0 ? 1ull : (u64)want;
+        uint32_t key_p;
+        u64 above;
+        unsigned int equal_p;
+        smp_select<true>(sh, x, V, inv_t, vmax, low_key, allowed, equal, target, &key_p, &above, &equal_p);
+        const unsigned int avail = equal_p;         // already reduced to `allowed` when key_p == low_key
+        const u64 unit = smp_mass(smp_unkey(key_p), vmax);
+        unsigned int needed = avail;
+        if (unit > 0 && target > above) {
+            const u64 n = (target - above + unit - 1) / unit;
+            needed = n < (u64)avail ? (unsigned int)n : avail;
+        }
+        if (needed < 1) needed = 1;
+        if (key_p == low_key) {
+            // ranks are counted among all `equal` elements at the key; fewer of them are admitted
+            allowed = needed;
+        } else {
+            low_key = key_p;
+            allowed = needed;
+            equal = equal_p;
+        }
+    }
+    const float mp = min_p ? min_p[row] : 0.f;
+    const float floor_v = mp > 0.f ? vmax + logf(mp) : -INFINITY;
+
+    // ---- total kept mass
+    u64 part = 0;
+    for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
+        float v = x[i] * inv_t;
+        if (v != v) v = -INFINITY;
+        if (smp_key(v) > low_key && !(v < floor_v)) part += smp_mass(v, vmax);
+    }
+    u64 z = smp_block_sum<u64>(part, sh.scratch64);
+    const float low_v = smp_unkey(low_key);
+    const bool low_in = low_key != 0 && !(low_v < floor_v);
+    if (low_in) z += (u64)allowed * smp_mass(low_v, vmax);
+    if (z == 0) {
+        if (threadIdx.x == 0) out[row] = arg_max;
+        return;
+    }
+    const float r = uniform ? uniform[row] : 0.f;
+    u64 target = (u64)((double)r * (double)z);
+    if (target >= z) target = z - 1;
+
+    // ---- walk in index order to the first index whose running mass exceeds the target
+    const bool need_rank = low_in && allowed < equal;
+    if (threadIdx.x == 0) sh.found = -1;
+    __syncthreads();
+    u64 run_mass = 0;
+    int run_ties = 0;
+    for (int base = 0; base < V; base += SMP_THREADS * SMP_ITEMS) {
+        float v[SMP_ITEMS];
+        uint32_t key[SMP_ITEMS];
+        int ties = 0;
+#pragma unroll
+        for (int e = 0; e < SMP_ITEMS; ++e) {
+            const int i = base + threadIdx.x * SMP_ITEMS + e;
+            float t = i < V ? x[i] * inv_t : -INFINITY;
+            if (t != t) t = -INFINITY;
+            v[e] = t;
+            key[e] = i < V ? smp_key(t) : 0u;
+            if (i < V && key[e] == low_key) ++ties;
+        }
+        int rank = 0;
+        if (need_rank) {
+            int total;
+            rank = run_ties + smp_block_scan<int>(ties, sh.scratch32, &total);
+            run_ties += total;
+        }
+        u64 m[SMP_ITEMS];
+        u64 mine = 0;
+#pragma unroll
+        for (int e = 0; e < SMP_ITEMS; ++e) {
+            const int i = base + threadIdx.x * SMP_ITEMS + e;
+            bool keep = false;
+            if (i < V) {
+                if (key[e] > low_key) keep = !(v[e] < floor_v);
+                else if (key[e] == low_key && low_in) {
+                    keep = need_rank ? (rank < (int)allowed) : true;
+                    ++rank;
+                }
+            }
+            m[e] = keep ? smp_mass(v[e], vmax) : 0ull;
+            mine += m[e];
+        }
+        u64 total;
+        u64 before = run_mass + smp_block_scan<u64>(mine, sh.scratch64, &total);
+        if (target >= before && target < before + mine) {
+#pragma unroll
+            for (int e = 0; e < SMP_ITEMS; ++e) {
+                if (m[e] != 0 && target >= before && target < before + m[e]) sh.found = base + threadIdx.x * SMP_ITEMS + e;
+                before += m[e];
+            }
+        }
+        run_mass += total;
+        __syncthreads();
+        if (sh.found >= 0) break;
+    }
+    if (threadIdx.x == 0) out[row] = sh.found >= 0 ? sh.found : arg_max;
+}
+
+// One block per row.  `prev` holds each row's generated ids, row r in prev[r*prev_stride ..
+// +prev_len[r]).  The last `window[r]` of them (0 = all) are penalised once per distinct id.
+__global__ void __launch_bounds__(256)
+repetition_penalty_kernel(float* __restrict__ logits, int row_stride, int V, const int32_t* __restrict__ prev,
+                          int prev_stride, const int32_t* __restrict__ prev_len,
+                          const float* __restrict__ penalty, const int32_t* __restrict__ window) {
+    const int row = blockIdx.x;
+    const float pen = penalty[row];
+    const int n = prev_len[row];
+    if (pen == 1.0f || n <= 0) return;
+    const int w = window[row];
+    const int start = (w > 0 && n - w > 0) ? n - w : 0;
+    const int32_t* ids = prev + (size_t)row * prev_stride;
+    float* x = logits + (size_t)row * row_stride;
+    for (int i = start + threadIdx.x; i < n; i += blockDim.x) {
+        const int id = ids[i];
+        if (id < 0 || id >= V) continue;
+        bool first = true;
+        for (int j = start; j < i; ++j)
+            if (ids[j] == id) { first = false; break; }
+        if (!first) continue;
+        const float v = x[id];
+        x[id] = v > 0.f ? v / pen : v * pen;
+    }
+}
+
+// logits: float32 [rows, V] rows row_stride apart.  temperature/top_k/top_p/min_p/uniform: one
+// value per row (NULL = greedy / off).  out: int32 [rows].
+extern "C" int dl_sample(const float* logits, int row_stride, int rows, int V, const float* temperature,
+                         const int32_t* top_k, const float* top_p, const float* min_p, const float* uniform,
+                         int32_t* out, void* stream) {
+    DL_REQUIRE(rows >= 0 && V > 0 && row_stride >= V, "sample: bad sizes rows=%d V=%d", rows, V);
+    DL_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: a sampled draw needs uniform numbers");
+    if (rows == 0) return DL_OK;
+    sample_kernel<<<rows, SMP_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, V, temperature, top_k, top_p,
+                                                                 min_p, uniform, out);
+    DL_CHECK_LAUNCH("sample");
+    return DL_OK;
+}
+
+extern "C" int dl_repetition_penalty(float* logits, int row_stride, int rows, int V, const int32_t* prev,
+                                     int prev_stride, const int32_t* prev_len, const float* penalty,
+                                     const int32_t* window, void* stream) {
+    DL_REQUIRE(rows >= 0 && V > 0 && row_stride >= V && prev_stride >= 0, "repetition_penalty: bad sizes");
+    if (rows == 0 || prev_stride == 0) return DL_OK;
+    repetition_penalty_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(logits, row_stride, V, prev, prev_stride,
+                                                                     prev_len, penalty, window);
+    DL_CHECK_LAUNCH("repetition_penalty");
+    return DL_OK;
+}

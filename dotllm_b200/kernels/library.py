@@ -1,0 +1,95 @@
+"""Loads the compiled kernel library through ctypes and declares its entry points.
+
+There is no fallback: if the library cannot be built or loaded, or the device is not
+sm_100, every call raises ``KernelError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+from ..errors import KernelError
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_F = ctypes.c_float
+
+# name -> argument types (every function returns int status)
+_SIGNATURES = {
+    "dl_gather_rows": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "dl_add_rmsnorm": [_P, _P, _I, _P, _P, _I, _I, _I, _F, _P],
+    "dl_rope_cache_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I,
+                            _I, _I, _I, _I, _I, _P],
+    "dl_attention_generic": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "dl_swiglu": [_P, _P, _I, _P, _I, _I, _I, _P],
+    "dl_gemm_f32": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
+    "dl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "dl_repetition_penalty": [_P, _I, _I, _I, _P, _I, _P, _P, _P, _P],
+}
+
+_lock = threading.Lock()
+_lib = None
+_checked_device = False
+
+
+def declare(lib, signatures):
+    for name, argtypes in signatures.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise KernelError(f"kernel library lacks entry point {name}") from exc
+        fn.argtypes = argtypes
+        fn.restype = ctypes.c_int
+
+
+def library():
+    """The loaded library (built on first use)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        from . import build
+        path = build.build()
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as exc:
+            raise KernelError(f"cannot load {path}: {exc}") from exc
+        declare(lib, _SIGNATURES)
+        lib.dl_last_error.restype = ctypes.c_char_p
+        lib.dl_last_error.argtypes = []
+        lib.dl_device_arch.restype = ctypes.c_int
+        lib.dl_sm_count.restype = ctypes.c_int
+        _lib = lib
+        return lib
+
+
+def register_signatures(signatures):
+    """Entry points of kernels added later (each module declares its own)."""
+    _SIGNATURES.update(signatures)
+    if _lib is not None:
+        declare(_lib, signatures)
+
+
+def require_device():
+    """Raise unless the current CUDA device can run the sm_100a kernels."""
+    global _checked_device
+    if _checked_device:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this library runs on NVIDIA B200 (sm_100) only "
+                          "and has no CPU fallback")
+    arch = library().dl_device_arch()
+    if arch // 10 != 10:
+        raise KernelError(f"the kernels are compiled for sm_100a; the current device reports "
+                          f"compute capability {arch / 10:.1f}")
+    _checked_device = True
+
+
+def call(name, *args):
+    lib = library()
+    status = getattr(lib, name)(*args)
+    if status != 0:
+        raise KernelError(f"{name}: {lib.dl_last_error().decode(errors='replace')} (status {status})")

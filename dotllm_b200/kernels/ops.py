@@ -1,0 +1,266 @@
+"""Tensor-level wrappers of the CUDA kernels.
+
+Each function checks devices, dtypes, shapes and strides on the host, then launches on
+the current CUDA stream.  Tensors that are not on a CUDA device are refused: there is no
+CPU path.  Parts call these functions through the module (``ops.add_rmsnorm(...)``).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..errors import KernelError
+from . import library as _library
+
+PAGE = 64                      # tokens per cache page (DL_PAGE in csrc/common.cuh)
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _code(dtype):
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only: there is no CPU fallback")
+    _library.require_device()
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _rows_view(t, what):
+    """A 2-D tensor whose rows are contiguous (a column slice of a wider matrix is fine)."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{what}: need a 2-D tensor with contiguous rows, got shape "
+                          f"{tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def _int32(t, what):
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{what}: need a contiguous int32 tensor")
+    return t
+
+
+# ------------------------------------------------------------------ embedding
+def gather_rows(table, ids, out=None):
+    """out[r] = float32(table[ids[r]]).  table [n, width] float32 or bfloat16; ids int32 [R]."""
+    _need_cuda(table, ids, out)
+    if table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("gather_rows: table must be a contiguous matrix")
+    _int32(ids, "gather_rows ids")
+    n, width = table.shape
+    rows = ids.numel()
+    if out is None:
+        out = torch.empty((rows, width), dtype=torch.float32, device=table.device)
+    elif out.shape != (rows, width) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("gather_rows: out must be contiguous float32 [rows, width]")
+    _library.call("dl_gather_rows", _ptr(table), _code(table.dtype), _ptr(ids), _ptr(out),
+                  rows, width, n, _stream())
+    return out
+
+
+# ----------------------------------------------------------------------- norm
+def add_rmsnorm(residual, delta, gain, eps, out_dtype):
+    """residual += delta (when delta is given), then rmsnorm(residual) * gain in ``out_dtype``.
+
+    residual: float32 [T, H] contiguous, updated in place.  delta: [T, H] float32/bfloat16 or None.
+    gain: float32 [H]."""
+    _need_cuda(residual, delta, gain)
+    if residual.dtype != torch.float32 or residual.dim() != 2 or not residual.is_contiguous():
+        raise KernelError("rmsnorm: the residual stream must be contiguous float32 [T, H]")
+    rows, width = residual.shape
+    if gain.dtype != torch.float32 or gain.shape != (width,) or not gain.is_contiguous():
+        raise KernelError(f"rmsnorm: gain must be float32 [{width}]")
+    if delta is not None and (delta.shape != residual.shape or not delta.is_contiguous()):
+        raise KernelError("rmsnorm: delta must be contiguous with the residual's shape")
+    out = torch.empty((rows, width), dtype=out_dtype, device=residual.device)
+    _library.call("dl_add_rmsnorm", _ptr(residual), _ptr(delta),
+                  _code(delta.dtype) if delta is not None else 0, _ptr(gain), _ptr(out),
+                  _code(out_dtype), rows, width, float(eps), _stream())
+    return out
+
+
+# --------------------------------------------------- position + cache write
+def rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table,
+                     k_pool, v_pool, n_heads, n_kv_heads, head_dim, write_cache=True):
+    """Rotate Q in place (and K on its way into the cache); store K and V at each token's page.
+
+    q [T, nh*hd], k, v [T, nkv*hd]: row-contiguous views of one dtype.  cos, sin: float32
+    [positions, rotary_dim/2] (None with rotary_dim 0: no rotation).  k_pool [pages, nkv, 64, hd],
+    v_pool [pages, nkv, hd, 64].  block_table int32 [B, P]; token_seq/token_pos int32 [T]."""
+    _need_cuda(q, k, v, cos, sin, token_seq, token_pos, block_table, k_pool, v_pool)
+    T = q.shape[0]
+    qs = _rows_view(q, "rope q")
+    if q.shape[1] != n_heads * head_dim:
+        raise KernelError("rope: q width is not n_heads * head_dim")
+    ks = vs = 0
+    n_pages = 0
+    bt_stride = 0
+    if write_cache:
+        ks = _rows_view(k, "rope k")
+        vs = _rows_view(v, "rope v")
+        if k.shape != (T, n_kv_heads * head_dim) or v.shape != k.shape:
+            raise KernelError("rope: k and v must be [T, n_kv_heads * head_dim]")
+        if k.dtype != q.dtype or v.dtype != q.dtype or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+            raise KernelError("rope: q, k, v and the cache must share one dtype")
+        n_pages = _check_pools(k_pool, v_pool, n_kv_heads, head_dim)
+        _int32(block_table, "block_table")
+        bt_stride = block_table.shape[1]
+        _int32(token_seq, "token_seq")
+    _int32(token_pos, "token_pos")
+    table_rows = 0
+    if rotary_dim:
+        if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape != sin.shape \
+                or cos.dim() != 2 or cos.shape[1] != rotary_dim // 2 or not cos.is_contiguous() \
+                or not sin.is_contiguous():
+            raise KernelError("rope: cos/sin must be contiguous float32 [positions, rotary_dim/2]")
+        table_rows = cos.shape[0]
+    _library.call("dl_rope_cache_write", _ptr(q), qs, _ptr(k) if write_cache else None, ks,
+                  _ptr(v) if write_cache else None, vs, _code(q.dtype),
+                  _ptr(cos) if rotary_dim else None, _ptr(sin) if rotary_dim else None,
+                  int(rotary_dim), table_rows, _ptr(token_seq) if write_cache else None, _ptr(token_pos),
+                  _ptr(block_table) if write_cache else None, bt_stride,
+                  _ptr(k_pool) if write_cache else None, _ptr(v_pool) if write_cache else None, n_pages,
+                  T, n_heads, n_kv_heads, head_dim, 1 if write_cache else 0, _stream())
+
+
+def _check_pools(k_pool, v_pool, n_kv_heads, head_dim):
+    if k_pool.dim() != 4 or not k_pool.is_contiguous() or not v_pool.is_contiguous() \
+            or tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE, head_dim) \
+            or tuple(v_pool.shape) != (k_pool.shape[0], n_kv_heads, head_dim, PAGE):
+        raise KernelError(f"cache pools must be K [pages, {n_kv_heads}, {PAGE}, {head_dim}] and "
+                          f"V [pages, {n_kv_heads}, {head_dim}, {PAGE}], got {tuple(k_pool.shape)} "
+                          f"and {tuple(v_pool.shape)}")
+    return k_pool.shape[0]
+
+
+# ------------------------------------------------------------------ attention
+def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads,
+              head_dim, scale, window=0, plan=None):
+    """Causal attention of the step's tokens over their sequences' cached keys and values.
+
+    q [T, nh*hd] (row-contiguous view); returns [T, nh*hd] of q's dtype.  ``window`` 0 means
+    every earlier key; w > 0 means the last w keys.  ``plan`` carries the per-step layout
+    (sequence lengths, chunking) that the tensor-core kernels need; without one, or for sizes
+    they do not take, the generic kernel runs."""
+    _need_cuda(q, k_pool, v_pool, token_seq, token_pos, block_table)
+    T = q.shape[0]
+    qs = _rows_view(q, "attention q")
+    if q.shape[1] != n_heads * head_dim:
+        raise KernelError("attention: q width is not n_heads * head_dim")
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+        raise KernelError("attention: q and the cache must share one dtype")
+    n_pages = _check_pools(k_pool, v_pool, n_kv_heads, head_dim)
+    _int32(token_seq, "token_seq")
+    _int32(token_pos, "token_pos")
+    _int32(block_table, "block_table")
+    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    if plan is not None and q.dtype == torch.bfloat16:
+        from . import attention_fast
+        if attention_fast.run(q, qs, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_table,
+                              n_heads, n_kv_heads, head_dim, float(scale), int(window), plan):
+            return out
+    _library.call("dl_attention_generic", _ptr(q), qs, _ptr(out), out.stride(0), _code(q.dtype),
+                  _ptr(k_pool), _ptr(v_pool), n_pages, _ptr(token_seq), _ptr(token_pos),
+                  _ptr(block_table), block_table.shape[1], T, n_heads, n_kv_heads, head_dim,
+                  float(scale), int(window), _stream())
+    return out
+
+
+# ---------------------------------------------------------------- feed-forward
+def swiglu(gate_up):
+    """silu(gate) * up for gate_up = [gate | up] of shape [T, 2I]; returns [T, I]."""
+    _need_cuda(gate_up)
+    if gate_up.dim() != 2 or gate_up.shape[1] % 2 or not gate_up.is_contiguous():
+        raise KernelError("swiglu: need a contiguous [T, 2I] tensor")
+    rows, two_i = gate_up.shape
+    width = two_i // 2
+    out = torch.empty((rows, width), dtype=gate_up.dtype, device=gate_up.device)
+    esize = gate_up.element_size()
+    _library.call("dl_swiglu", gate_up.data_ptr(), gate_up.data_ptr() + width * esize, two_i,
+                  _ptr(out), _code(gate_up.dtype), rows, width, _stream())
+    return out
+
+
+# --------------------------------------------------------------------- linear
+def linear(x, w, out_dtype=None):
+    """y = x W^T for W [N, K].
+
+    float32: the library's own FFMA kernel (true 32-bit, the same bits for any number of rows).
+    bfloat16: cuBLAS through torch with float32 accumulation, the library product that the
+    reference also uses for its projections (src/DotLLM.Cuda/CudaGemm.cs:29-40)."""
+    _need_cuda(x, w)
+    if w.dim() != 2 or not w.is_contiguous() or x.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not match W {tuple(w.shape)}")
+    if x.dtype != w.dtype:
+        raise KernelError(f"linear: x is {x.dtype} but W is {w.dtype}")
+    out_dtype = out_dtype or x.dtype
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype == torch.float32:
+        if out_dtype != torch.float32:
+            raise KernelError("linear: the float32 product writes float32")
+        xs = _rows_view(x, "linear x")
+        y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        _library.call("dl_gemm_f32", _ptr(x), xs, _ptr(w), _ptr(y), N, M, N, K, _stream())
+        return y
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: unsupported dtype {x.dtype}")
+    if M > 0:
+        from . import gemm_skinny
+        y = gemm_skinny.maybe_run(x, w, out_dtype)
+        if y is not None:
+            return y
+    if out_dtype == torch.bfloat16:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------------- sampling
+def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None):
+    """One token per row of float32 logits [R, V].  With ``temperature`` None every row is
+    greedy (first index of the maximum).  Otherwise per-row float32/int32 tensors [R] give the
+    chain temperature -> top-k -> top-p -> min-p and ``uniform`` the draw in [0, 1);
+    a row with temperature <= 0 is greedy."""
+    _need_cuda(logits, temperature, top_k, top_p, min_p, uniform)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 [rows, vocab] with contiguous rows")
+    rows, vocab = logits.shape
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("min_p", min_p, torch.float32),
+                        ("uniform", uniform, torch.float32)):
+        if t is not None and (t.dtype != dt or t.shape != (rows,) or not t.is_contiguous()):
+            raise KernelError(f"sample: {name} must be a contiguous {dt} tensor of {rows} values")
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _library.call("dl_sample", _ptr(logits), logits.stride(0) if rows > 1 else vocab, rows, vocab,
+                  _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(out),
+                  _stream())
+    return out
+
+
+def repetition_penalty(logits, prev, prev_len, penalty, window):
+    """In place: each distinct id among the last ``window[r]`` (0 = all) of row r's
+    ``prev[r, :prev_len[r]]`` has its logit divided (if positive) or multiplied by ``penalty[r]``."""
+    _need_cuda(logits, prev, prev_len, penalty, window)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("repetition_penalty: logits must be float32 [rows, vocab]")
+    rows, vocab = logits.shape
+    if prev.dtype != torch.int32 or prev.dim() != 2 or prev.shape[0] != rows or not prev.is_contiguous():
+        raise KernelError("repetition_penalty: prev must be contiguous int32 [rows, n]")
+    _int32(prev_len, "prev_len")
+    _int32(window, "window")
+    if penalty.dtype != torch.float32 or not penalty.is_contiguous():
+        raise KernelError("repetition_penalty: penalty must be float32 [rows]")
+    _library.call("dl_repetition_penalty", _ptr(logits), logits.stride(0) if rows > 1 else vocab, rows,
+                  vocab, _ptr(prev), prev.shape[1], _ptr(prev_len), _ptr(penalty), _ptr(window), _stream())
+    return logits

@@ -1,0 +1,120 @@
+"""The Python entry point: load a model folder (or random weights), step it, generate with it.
+
+Mirrors the reference's top-level objects: ``ModelLoader`` (src/DotLLM.Models/ModelLoader.cs:21-28),
+``IModel`` with ``Config`` and ``Forward`` (src/DotLLM.Core/Models/IModel.cs:9-35) and
+``TextGenerator`` (src/DotLLM.Engine/TextGenerator.cs:68).  The model class is chosen by
+config.json through the architecture registry.
+"""
+from __future__ import annotations
+
+import torch
+
+from .config.registry import build_spec, load_config
+from .engine.generate import TextGenerator
+from .engine.step import StepEntry, run_step
+from .errors import ConfigError, KernelError
+from .models.decoder import DecoderModel
+from .parts.base import Runtime
+from .sampling.options import InferenceOptions
+from .sampling.pipeline import sample_rows
+from .weights.loader import load_into
+from .weights.random_init import init_random
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, "f32": torch.float32}
+
+
+def parse_dtype(dtype):
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ConfigError(f"models run in bfloat16 or float32, not {dtype}")
+        return dtype
+    try:
+        return _DTYPES[str(dtype).lower()]
+    except KeyError:
+        raise ConfigError(f"unknown dtype {dtype!r}; use 'bfloat16' or 'float32'") from None
+
+
+def parse_device(device):
+    """'cuda', 'cuda:N', or the reference's 'gpu' / 'gpu:N' (src/DotLLM.Cli/Commands/RunCommand.cs:95-98)."""
+    if isinstance(device, torch.device):
+        return device
+    name = str(device).lower().replace("gpu", "cuda")
+    dev = torch.device(name)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)
+    return dev
+
+
+class Model:
+    """A loaded model: its typed configuration, its description, its parts on the device."""
+
+    def __init__(self, config, spec, decoder):
+        self.config = config
+        self.spec = spec
+        self.decoder = decoder
+        self.runtime = decoder.runtime
+        self._generator = None
+
+    # ---------------------------------------------------------------- making
+    @classmethod
+    def _skeleton(cls, config, dtype, device, spec=None):
+        runtime = Runtime(parse_dtype(dtype), parse_device(device))
+        if runtime.device.type != "cuda":
+            raise KernelError(f"models run on a CUDA device (sm_100a); got device {runtime.device}")
+        torch.cuda.set_device(runtime.device)
+        spec = spec or build_spec(config)
+        return cls(config, spec, DecoderModel(spec, runtime))
+
+    @classmethod
+    def load(cls, folder, dtype="bfloat16", device="cuda"):
+        """From a folder with config.json and model.safetensors (or an index and shards)."""
+        config = load_config(folder)
+        model = cls._skeleton(config, dtype, device)
+        load_into(model.decoder, folder)
+        return model
+
+    @classmethod
+    def random(cls, config, seed=0, dtype="bfloat16", device="cuda", on_device=True, spec=None):
+        """Random weights drawn in memory from (config, seed); nothing is written."""
+        model = cls._skeleton(config, dtype, device, spec)
+        init_random(model.decoder, seed, on_device=on_device)
+        return model
+
+    # --------------------------------------------------------------- running
+    def new_cache(self, max_tokens, max_sequences=None):
+        return self.decoder.new_cache(max_tokens, max_sequences)
+
+    def step(self, cache, entries):
+        """Run one step; ``entries`` are StepEntry objects (or (sequence, tokens[, want]) tuples).
+        Returns float32 logits [wanted, vocab]."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        return run_step(self.decoder, cache, entries)
+
+    def generator(self, cache=None, max_tokens=None, max_batch=None):
+        """A TextGenerator over this model.  Without a cache one is made for ``max_tokens``."""
+        if cache is None:
+            cache = self.new_cache(max_tokens or min(self.spec.max_positions * 8, 1 << 16))
+        return TextGenerator(lambda entries: self.step(cache, entries), sample_rows, cache,
+                             max_positions=self.spec.max_positions, vocab_size=self.spec.vocab_size,
+                             default_stop_ids=self.spec.stop_token_ids, bos_token_id=self.spec.bos_token_id,
+                             max_batch=max_batch, synchronize=torch.cuda.synchronize)
+
+    def generate(self, prompts, options=None, on_token=None, **option_fields):
+        """Generate for one prompt (a list of ints) or many.  Options as an InferenceOptions (or
+        a list of them), or as keyword fields of one."""
+        if options is None:
+            options = InferenceOptions(**option_fields)
+        elif option_fields:
+            raise ValueError("give either an InferenceOptions or keyword fields, not both")
+        if self._generator is None:
+            self._generator = self.generator()
+        return self._generator.generate(prompts, options, on_token)
+
+
+class ModelLoader:
+    """The reference's loading entry point by name (src/DotLLM.Models/ModelLoader.cs:21-28)."""
+
+    @staticmethod
+    def load(folder, dtype="bfloat16", device="cuda"):
+        return Model.load(folder, dtype, device)

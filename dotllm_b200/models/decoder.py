@@ -1,0 +1,104 @@
+"""The generic decoder: runs any model description over a step of tokens.
+
+Embedding, then the scheduled layer executions, then the final norm and the head on the rows
+whose logits are wanted - the reference's forward pass
+(src/DotLLM.Models/Architectures/TransformerModel.cs:134-425), with its GPU variant's habit of
+computing the head only where logits are needed (src/DotLLM.Cuda/CudaTransformerModel.cs:289-297).
+Nothing in this file knows an architecture's name.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.model_cache import ModelCache
+from ..config.spec import ModelSpec
+from ..kernels import ops
+from ..parts.base import Runtime, make_arrangement, make_part
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, runtime: Runtime):
+        spec.validate()
+        self.spec = spec
+        self.runtime = runtime
+        h = spec.hidden_size
+        self.embedding = make_part("embedding", spec.embedding, h, runtime)
+        self.blocks = []
+        self._named_parts = [(spec.embedding.prefix, self.embedding)]
+        for layer in spec.layers:
+            mixer = make_part("mixer", layer.mixer, h, runtime)
+            ffn = make_part("feed_forward", layer.feed_forward, h, runtime)
+            n1 = make_part("norm", layer.mixer_norm, h, runtime)
+            n2 = make_part("norm", layer.feed_forward_norm, h, runtime)
+            self.blocks.append(make_arrangement(layer.arrangement, mixer, ffn, n1, n2))
+            self._named_parts += [(layer.mixer_norm.prefix, n1), (layer.mixer.prefix, mixer),
+                                  (layer.feed_forward_norm.prefix, n2), (layer.feed_forward.prefix, ffn)]
+        self.final_norm = make_part("norm", spec.final_norm, h, runtime)
+        self.head = make_part("head", spec.head, h, runtime)
+        self._named_parts += [(spec.final_norm.prefix, self.final_norm), (spec.head.prefix, self.head)]
+        self.bound = False
+
+    # ------------------------------------------------------------- weights
+    def named_parts(self):
+        """(prefix, part) for every part that may own tensors."""
+        return list(self._named_parts)
+
+    def expected_weights(self):
+        """Full tensor name -> WeightSpec, and the set of names that may be present and are ignored."""
+        expected, optional = {}, set()
+        for prefix, part in self._named_parts:
+            for local, spec in part.weight_specs().items():
+                expected[prefix + local] = spec
+            optional |= {prefix + local for local in part.optional_names()}
+        return expected, optional
+
+    def convert(self, spec, tensor):
+        """A loaded tensor in the dtype its role asks for, on the device."""
+        t = tensor.to(self.runtime.device)
+        if spec.role == "matrix":
+            return t.to(self.runtime.dtype)
+        if spec.role == "precise":
+            return t.to(torch.float32)
+        if spec.role == "index":
+            return t.to(torch.int32)
+        raise ValueError(f"unknown weight role {spec.role!r}")
+
+    def bind(self, fetch):
+        """Give every part its tensors.  ``fetch(full_name)`` returns the stored tensor."""
+        for prefix, part in self._named_parts:
+            tensors = {local: self.convert(spec, fetch(prefix + local))
+                       for local, spec in part.weight_specs().items()}
+            part.bind(tensors)
+        if getattr(self.head, "tied", False):
+            self.head.tie(self.embedding.table)
+        self.bound = True
+
+    def weight_bytes_per_step(self):
+        """Bytes of weights a decode step reads: every matrix once; the embedding table only
+        when the head shares it (a lookup touches a few rows)."""
+        return sum(part.weight_bytes() for _, part in self._named_parts)
+
+    # --------------------------------------------------------------- cache
+    def cache_needs(self):
+        return [self.blocks[e.layer].mixer.cache_need() for e in self.spec.schedule]
+
+    def new_cache(self, max_tokens, max_sequences=None):
+        return ModelCache(self.cache_needs(), [e.cache_of for e in self.spec.schedule], self.runtime,
+                          max_tokens, max_sequences)
+
+    # ------------------------------------------------------------- forward
+    def forward(self, step, cache):
+        """Logits float32 [wanted rows, vocab] of one step (see engine.step)."""
+        residual = self.embedding.forward(step.tokens)
+        pending = None
+        for e, entry in enumerate(self.spec.schedule):
+            view = cache.view(e, step.block_tables, step.slots)
+            residual, pending = self.blocks[entry.layer].forward(residual, pending, step, view)
+        if step.n_wanted == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
+        if not step.want_all:
+            residual = ops.gather_rows(residual, step.want_rows)
+            pending = ops.gather_rows(pending, step.want_rows) if pending is not None else None
+        n = self.final_norm.add_forward(residual, pending) if pending is not None \
+            else self.final_norm.forward(residual)
+        return self.head.forward(n)

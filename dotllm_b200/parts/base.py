@@ -1,0 +1,220 @@
+"""Interfaces of the parts a layer is made of, and the registries that build them by kind.
+
+A part knows its own sizes and constants (given as ``params``) and nothing about the model
+it sits in.  The reference declares the same seams as ``IAttentionStrategy``
+(src/DotLLM.Core/Attention/IAttentionStrategy.cs:9-27) and ``IPositionEncoding``
+(src/DotLLM.Core/PositionEncoding/IPositionEncoding.cs:10-34) but wires its forward pass
+around them (docs/ATTENTION.md:5); here the block really runs through the interfaces.
+
+Kinds are registered by name:
+
+    register_mixer("attention", AttentionMixer)
+    register_feed_forward("gated_mlp", GatedFeedForward)
+    register_norm("rmsnorm", RmsNorm)
+    register_position_encoding("rotary", RotaryEncoding)
+    register_arrangement("pre_norm", PreNormBlock)
+
+and a ``PartSpec(kind, params, prefix)`` picks one per layer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..errors import ConfigError
+
+
+@dataclass(frozen=True)
+class Runtime:
+    """Where and in which precision a model runs."""
+    dtype: torch.dtype            # torch.float32 or torch.bfloat16: matrices, activations, cache
+    device: torch.device
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    """One tensor a part needs.
+
+    role "matrix": operand of a matrix product or a lookup table; converted to the run dtype.
+    role "precise": used in 32-bit arithmetic (norm gains); widened to / kept in float32.
+    role "index": integer table; kept as int32.
+    ``init`` says how the random-weights mode fills it: ("normal", std), ("ones",),
+    ("one_plus_uniform", a) or ("zeros",).
+    """
+    shape: tuple
+    role: str = "matrix"
+    init: tuple = ("normal", 0.02)
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What one execution of a mixer keeps per sequence.
+
+    kind "kv": keys and values per token, ``n_kv_heads`` x ``head_dim`` each; ``window`` None
+    keeps every token, an integer keeps the last ``window``.
+    kind "state": a fixed-size tensor of ``state_shape`` / ``state_dtype`` per sequence, zero
+    when the sequence starts.
+    """
+    kind: str
+    n_kv_heads: int = 0
+    head_dim: int = 0
+    window: Optional[int] = None
+    state_shape: tuple = ()
+    state_dtype: torch.dtype = torch.float32
+
+    def group_key(self, run_dtype):
+        if self.kind == "kv":
+            return ("kv", self.n_kv_heads, self.head_dim, self.window, run_dtype)
+        return ("state", tuple(self.state_shape), self.state_dtype)
+
+
+class Part:
+    """Base of every part: declares tensors, receives them, runs."""
+
+    def __init__(self, params: dict, hidden_size: int, runtime: Runtime):
+        self.params = dict(params)
+        self.hidden_size = hidden_size
+        self.runtime = runtime
+
+    def weight_specs(self) -> dict:
+        """local tensor name -> WeightSpec"""
+        return {}
+
+    def optional_names(self) -> set:
+        """Local names that a checkpoint may hold and this part ignores."""
+        return set()
+
+    def bind(self, tensors: dict) -> None:
+        """Receive the declared tensors, already on the device in the dtype their role asks for."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights that one step reads (for the roofline account)."""
+        return 0
+
+
+class Norm(Part):
+    def forward(self, x):
+        """Normalised copy of the float32 stream ``x`` in the run dtype."""
+        raise NotImplementedError
+
+    def add_forward(self, residual, delta):
+        """residual += delta in place (float32), then the normalised result in the run dtype."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Position information for a mixer's queries and keys.
+
+    ``fused_rotary()`` returns (cos, sin, rotary_dim) when the encoding is a rotation that the
+    cache-write kernel can apply on the fly, else None, in which case the mixer calls
+    ``apply(q, k, positions)`` before the plain cache write."""
+
+    def fused_rotary(self):
+        return None
+
+    def apply(self, q, k, positions):
+        """Encode in place.  q [T, nh*hd], k [T, nkv*hd] (k may be None), positions int32 [T]."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Mixes information across the tokens of a sequence (attention, recurrence, ...)."""
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def forward(self, x, step, cache_view):
+        """x [T, H] in the run dtype -> the branch output [T, H] (run dtype or float32).
+
+        ``step`` is the engine's StepContext (token -> sequence map, positions, lengths);
+        ``cache_view`` gives this execution's storage (``LayerCacheView``) or None."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x):
+        """x [T, H] in the run dtype -> the branch output [T, H]."""
+        raise NotImplementedError
+
+
+class Arrangement:
+    """How a layer's parts and the residual stream are wired."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(self, residual, pending, step, cache_view):
+        """Returns (residual, pending): the float32 stream and a branch output not yet added."""
+        raise NotImplementedError
+
+
+_REGISTRIES = {"mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "arrangement": {},
+               "embedding": {}, "head": {}}
+
+
+def _register(family, kind, cls):
+    _REGISTRIES[family][kind] = cls
+    return cls
+
+
+def register_mixer(kind, cls):
+    return _register("mixer", kind, cls)
+
+
+def register_feed_forward(kind, cls):
+    return _register("feed_forward", kind, cls)
+
+
+def register_norm(kind, cls):
+    return _register("norm", kind, cls)
+
+
+def register_position_encoding(kind, cls):
+    return _register("position_encoding", kind, cls)
+
+
+def register_arrangement(kind, cls):
+    return _register("arrangement", kind, cls)
+
+
+def register_embedding(kind, cls):
+    return _register("embedding", kind, cls)
+
+
+def register_head(kind, cls):
+    return _register("head", kind, cls)
+
+
+def registered(family):
+    _ensure_builtin()
+    return sorted(_REGISTRIES[family])
+
+
+def _ensure_builtin():
+    from . import norms, rotary, attention, feed_forward, blocks, embedding  # noqa: F401
+
+
+def make_part(family, spec, hidden_size, runtime):
+    """Build the part a PartSpec names."""
+    _ensure_builtin()
+    try:
+        cls = _REGISTRIES[family][spec.kind]
+    except KeyError:
+        raise ConfigError(f"no {family} of kind {spec.kind!r}; registered: "
+                          f"{sorted(_REGISTRIES[family])}") from None
+    return cls(spec.params, hidden_size, runtime)
+
+
+def make_arrangement(kind, mixer, feed_forward, mixer_norm, feed_forward_norm):
+    _ensure_builtin()
+    try:
+        cls = _REGISTRIES["arrangement"][kind]
+    except KeyError:
+        raise ConfigError(f"no block arrangement {kind!r}; registered: "
+                          f"{sorted(_REGISTRIES['arrangement'])}") from None
+    return cls(mixer, feed_forward, mixer_norm, feed_forward_norm)

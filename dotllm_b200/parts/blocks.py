@@ -1,0 +1,23 @@
+"""Block arrangements: how a layer's parts meet the residual stream.
+
+"pre_norm" is the reference's wiring, r=h; h=r+mixer(norm(h)); r=h; h=r+ffn(norm(h))
+(src/DotLLM.Models/Architectures/TransformerModel.cs:185-392).  As in the reference's GPU path
+(src/DotLLM.Cuda/CudaTransformerModel.cs:252-286) each residual add is folded into the norm
+that follows it, across the layer boundary too: a block returns its last branch output still
+to be added ("pending"), and whoever normalises next adds it.
+"""
+from __future__ import annotations
+
+from .base import Arrangement, register_arrangement
+
+
+class PreNormBlock(Arrangement):
+    def forward(self, residual, pending, step, cache_view):
+        n = self.mixer_norm.add_forward(residual, pending) if pending is not None \
+            else self.mixer_norm.forward(residual)
+        a = self.mixer.forward(n, step, cache_view)
+        n = self.feed_forward_norm.add_forward(residual, a)
+        return residual, self.feed_forward.forward(n)
+
+
+register_arrangement("pre_norm", PreNormBlock)

@@ -1,0 +1,114 @@
+"""Plain torch references of every kernel wrapper in ``dotllm_b200.kernels.ops``, with the same
+signatures, on whatever device the tensors live on.
+
+Two uses: each CUDA kernel is compared with its function here, alone and at sizes the engine
+does not use; and the CPU tests swap these in for the CUDA wrappers to exercise the engine's
+host logic.  Arithmetic is float32 (float64 where it is free); results are rounded to the dtype
+the kernel writes.  Formulas as in tests/plain_llama.py, which cites the reference.
+"""
+from __future__ import annotations
+
+import torch
+
+import plain_llama
+
+PAGE = 64
+
+
+def gather_rows(table, ids, out=None):
+    res = table[ids.long()].to(torch.float32)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def add_rmsnorm(residual, delta, gain, eps, out_dtype):
+    if delta is not None:
+        residual += delta.to(torch.float32)
+    return plain_llama.rms_norm(residual, gain, eps).to(out_dtype)
+
+
+def _rotate(x, cos, sin, positions, n_heads, head_dim, rotary_dim):
+    t = x.shape[0]
+    xf = x.to(torch.float32).reshape(t, n_heads, head_dim)
+    c, s = cos[positions.long()], sin[positions.long()]
+    return plain_llama.apply_rope(xf, c, s).reshape(t, n_heads * head_dim)
+
+
+def rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table,
+                     k_pool, v_pool, n_heads, n_kv_heads, head_dim, write_cache=True):
+    if rotary_dim:
+        q.copy_(_rotate(q, cos, sin, token_pos, n_heads, head_dim, rotary_dim).to(q.dtype))
+    if not write_cache:
+        return
+    kr = _rotate(k, cos, sin, token_pos, n_kv_heads, head_dim, rotary_dim).to(k.dtype) if rotary_dim else k
+    for t in range(q.shape[0]):
+        pos = int(token_pos[t])
+        page = int(block_table[int(token_seq[t]), pos // PAGE])
+        assert page >= 0
+        k_pool[page, :, pos % PAGE, :] = kr[t].reshape(n_kv_heads, head_dim)
+        v_pool[page, :, :, pos % PAGE] = v[t].reshape(n_kv_heads, head_dim)
+
+
+def gather_kv(k_pool, v_pool, pages, length):
+    """Keys and values [length, nkv, hd] of one sequence from its pages (float32)."""
+    ks, vs = [], []
+    for j in range(length):
+        page = int(pages[j // PAGE])
+        ks.append(k_pool[page, :, j % PAGE, :])
+        vs.append(v_pool[page, :, :, j % PAGE])
+    return torch.stack(ks).to(torch.float32), torch.stack(vs).to(torch.float32)
+
+
+def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads,
+              head_dim, scale, window=0, plan=None):
+    T = q.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.float32, device=q.device)
+    for t in range(T):
+        pos = int(token_pos[t])
+        first = max(0, pos - window + 1) if window else 0
+        pages = block_table[int(token_seq[t])]
+        ks, vs = [], []
+        for j in range(first, pos + 1):
+            page = int(pages[j // PAGE])
+            ks.append(k_pool[page, :, j % PAGE, :])
+            vs.append(v_pool[page, :, :, j % PAGE])
+        k = torch.stack(ks).to(torch.float32).reshape(len(ks), n_kv_heads * head_dim)
+        v = torch.stack(vs).to(torch.float32).reshape(len(vs), n_kv_heads * head_dim)
+        # one query at the last of these keys: the causal mask hides nothing
+        out[t] = plain_llama.causal_attention(q[t:t + 1].to(torch.float32), k, v, n_heads, n_kv_heads,
+                                              scale, position_offset=len(ks) - 1)[0]
+    return out.to(q.dtype)
+
+
+def swiglu(gate_up):
+    i = gate_up.shape[1] // 2
+    g, u = gate_up[:, :i].to(torch.float32), gate_up[:, i:].to(torch.float32)
+    return plain_llama.swiglu(g, u).to(gate_up.dtype)
+
+
+def linear(x, w, out_dtype=None):
+    y = x.to(torch.float32) @ w.to(torch.float32).T
+    return y.to(out_dtype or x.dtype)
+
+
+def repetition_penalty(logits, prev, prev_len, penalty, window):
+    for r in range(logits.shape[0]):
+        previous = prev[r, :int(prev_len[r])].tolist()
+        logits[r] = plain_llama.apply_repetition_penalty(logits[r].cpu(), previous, float(penalty[r]),
+                                                         int(window[r])).to(logits.device)
+    return logits
+
+
+def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None):
+    out = []
+    for r in range(logits.shape[0]):
+        row = logits[r].detach().cpu()
+        t = float(temperature[r]) if temperature is not None else 0.0
+        out.append(plain_llama.sample(
+            row, [], temperature=t, top_k=int(top_k[r]) if top_k is not None else 0,
+            top_p=float(top_p[r]) if top_p is not None else 1.0,
+            min_p=float(min_p[r]) if min_p is not None else 0.0,
+            r=float(uniform[r]) if uniform is not None else None))
+    return torch.tensor(out, dtype=torch.int32, device=logits.device)
