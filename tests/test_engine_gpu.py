@@ -1,0 +1,215 @@
+"""The engine against the plain implementation, in float32 and bfloat16, under every cut:
+whole requests, the last 32 tokens one by one, unequal batches with early finishers and reused
+slots, long decoding, the first tokens, and greedy generation through the entry point."""
+import pytest
+import torch
+
+import plain_llama
+import tiny_models
+from engine_checks import TOL, assert_close, first_wrong, load_pair
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def requests_for(which, cfg):
+    lens = {"A": [5, 11, 17, 100, 64, 65, 128], "B": [1, 9, 33, 70, 200, 256, 63],
+            "C": [300, 40, 129, 7, 1000]}[which]
+    return [tiny_models.random_tokens(n, cfg["vocab_size"], seed=100 + i) for i, n in enumerate(lens)]
+
+
+@pytest.fixture(scope="module")
+def tmp(tmp_path_factory):
+    return tmp_path_factory.mktemp("models")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_whole_tail_and_batched(tmp, which, dtype):
+    from dotllm_b200 import StepEntry
+    model, cfg, weights, _ = load_pair(tmp, which, dtype)
+    reqs = requests_for(which, cfg)
+    refs = [plain_llama.forward(cfg, weights, r) for r in reqs]
+    longest = max(len(r) for r in reqs)
+    cache = model.new_cache(max_tokens=2 * ((longest + 63) // 64 * 64) + 128)
+
+    # 1. each request alone and whole, every position wanted
+    for i, (r, ref) in enumerate(zip(reqs, refs)):
+        cache.fill_free_pages(float("nan"))
+        s = cache.open_sequence()
+        out = model.step(cache, [StepEntry(s, r, list(range(len(r))))])
+        cache.close_sequence(s)
+        assert first_wrong(out, ref, dtype) is None, \
+            f"whole: request {i} first wrong position {first_wrong(out, ref, dtype)}"
+
+    # 2. the last 32 tokens one by one (shorter requests: everything one by one)
+    for i, (r, ref) in enumerate(zip(reqs, refs)):
+        cache.fill_free_pages(float("nan"))
+        s = cache.open_sequence()
+        head = max(0, len(r) - 32)
+        got = []
+        if head:
+            got.append(model.step(cache, [StepEntry(s, r[:head], list(range(head)))]))
+        for t in range(head, len(r)):
+            got.append(model.step(cache, [StepEntry(s, [r[t]])]))
+        cache.close_sequence(s)
+        out = torch.cat(got)
+        assert first_wrong(out, ref, dtype) is None, \
+            f"tail: request {i} (head {head}) first wrong position {first_wrong(out, ref, dtype)}"
+    cache.check()
+
+    # 3. unequal batches: prompts whole in one step (all but the last k_b tokens), then one token
+    # each; shorter requests end earlier; batches follow one another and reuse slots and pages.
+    # The cache is sized for one batch only.
+    batches = [reqs[:3], reqs[3:5], reqs[5:]]
+    need = max(sum((len(r) + 63) // 64 * 64 for r in b) for b in batches if b)
+    small = model.new_cache(max_tokens=need)
+    for bi, batch in enumerate(batches):
+        if not batch:
+            continue
+        small.fill_free_pages(float("nan"))
+        seqs = [small.open_sequence() for _ in batch]
+        tails = [min(len(r) - 1, 3 + 5 * j) for j, r in enumerate(batch)]     # unequal decode lengths
+        heads = [len(r) - k for r, k in zip(batch, tails)]
+        out = model.step(small, [StepEntry(s, r[:h], list(range(h))) for s, r, h in zip(seqs, batch, heads)])
+        at = 0
+        for j, (r, h) in enumerate(zip(batch, heads)):
+            ref = refs[reqs.index(r)]
+            assert_close(out[at:at + h], ref[:h], dtype, f"batched prefill: batch {bi} request {j}")
+            at += h
+        done = [0] * len(batch)
+        live = [j for j in range(len(batch)) if tails[j] > 0]
+        for j in range(len(batch)):
+            if tails[j] == 0:
+                small.close_sequence(seqs[j])
+        while live:
+            out = model.step(small, [StepEntry(seqs[j], [batch[j][heads[j] + done[j]]]) for j in live])
+            for row, j in enumerate(live):
+                ref = refs[reqs.index(batch[j])]
+                assert_close(out[row], ref[heads[j] + done[j]], dtype,
+                             f"batched decode: batch {bi} request {j} position {heads[j] + done[j]}")
+                done[j] += 1
+            for j in list(live):
+                if done[j] == tails[j]:
+                    small.close_sequence(seqs[j])           # ends earlier than its neighbours
+                    live.remove(j)
+                    small.fill_free_pages(float("nan"))     # what it held must not matter any more
+        small.check()
+    assert small.slots.n_held == 0 and all(g.pages.n_held == 0 for g in small.kv_groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_float32_cuts_give_the_same_bits(tmp, dtype):
+    """In float32 every kernel's order of operations for a position is fixed, so whole, one by one
+    and batched give identical bits.  (bfloat16 uses library products whose rounding depends on
+    the number of rows, so it is only close.)"""
+    if dtype != torch.float32:
+        pytest.skip("bit equality holds for the float32 path only")
+    from dotllm_b200 import StepEntry
+    model, cfg, _, _ = load_pair(tmp, "B", dtype)
+    a = tiny_models.random_tokens(90, cfg["vocab_size"], 1)
+    b = tiny_models.random_tokens(50, cfg["vocab_size"], 2)
+    cache = model.new_cache(512)
+    s = cache.open_sequence()
+    whole = model.step(cache, [StepEntry(s, a, list(range(90)))])
+    cache.close_sequence(s)
+    s1, s2 = cache.open_sequence(), cache.open_sequence()
+    got = [model.step(cache, [StepEntry(s2, b[:20], []), StepEntry(s1, a[:60], list(range(60)))])]
+    for t in range(60, 90):
+        got.append(model.step(cache, [StepEntry(s2, [b[t - 40]], []), StepEntry(s1, [a[t]])]))
+    assert torch.equal(torch.cat(got).cpu(), whole.cpu())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_and_first_tokens(tmp, dtype):
+    """One token at a time from position 0 to the model's last position (past the rope scaling's
+    original length, across page boundaries)."""
+    from dotllm_b200 import StepEntry
+    model, cfg, weights, _ = load_pair(tmp, "B", dtype)
+    n = cfg["max_position_embeddings"]
+    toks = tiny_models.random_tokens(n, cfg["vocab_size"], 5)
+    ref = plain_llama.forward(cfg, weights, toks)
+    cache = model.new_cache(n)
+    s = cache.open_sequence()
+    for t in range(n):
+        out = model.step(cache, [StepEntry(s, [toks[t]])])
+        assert_close(out[0], ref[t], dtype, f"decode position {t}")
+    from dotllm_b200.errors import StepError
+    with pytest.raises(StepError):
+        model.step(cache, [StepEntry(s, [0])])              # beyond max positions
+    cache.close_sequence(s)
+
+
+def test_far_key_decides_the_next_token(tmp):
+    """Weights made so that a far key matters: scale one layer's query and key projections so the
+    scores are sharp.  A cache or mask fault at a far position then changes logits by O(1)."""
+    from dotllm_b200 import Model, StepEntry
+    from dotllm_b200.weights import SafetensorsFile, save_safetensors
+    folder = tiny_models.make_folder(tmp, "C", seed=3, dtype=torch.float32)
+    with SafetensorsFile(folder / "model.safetensors") as f:
+        tensors = {n: f.tensor(n).clone() for n in f.names()}
+    for name in tensors:
+        if "q_proj" in name or "k_proj" in name:
+            tensors[name] *= 12.0
+    sharp = tmp / "sharp_C"
+    sharp.mkdir(exist_ok=True)
+    save_safetensors(sharp / "model.safetensors", tensors)
+    (sharp / "config.json").write_text((folder / "config.json").read_text())
+    cfg, weights = plain_llama.read_model_folder(sharp)
+    toks = tiny_models.random_tokens(600, cfg["vocab_size"], 9)
+    ref = plain_llama.forward(cfg, weights, toks)
+    for dtype in (torch.float32,):
+        model = Model.load(sharp, dtype=dtype)
+        cache = model.new_cache(1024)
+        s = cache.open_sequence()
+        out = [model.step(cache, [StepEntry(s, toks[:570], [0, 1, 63, 64, 569])])]
+        out += [model.step(cache, [StepEntry(s, [toks[t]])]) for t in range(570, 600)]
+        out = torch.cat(out)
+        want = ref[[0, 1, 63, 64, 569] + list(range(570, 600))]
+        err = float((out.cpu() - want).abs().max())
+        assert err < 5e-4, err
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(tmp, which, dtype):
+    from dotllm_b200 import InferenceOptions, Model
+    model, cfg, weights, folder = load_pair(tmp, which, dtype)
+    lens = tiny_models.TINY_A_PROMPTS if which == "A" else tiny_models.TINY_B_PROMPTS
+    n_new = tiny_models.TINY_A_DECODE if which == "A" else tiny_models.TINY_B_DECODE
+    prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 40 + n) for n in lens]
+    opts = InferenceOptions(temperature=0.0, max_tokens=n_new, stop_token_ids=[])
+    outs = model.generate(prompts, opts)
+    for p, o in zip(prompts, outs):
+        assert o.finish_reason.value == "length" and o.generated_token_count == n_new
+        # teacher-forced check: every generated token is the plain argmax, or ties it within tolerance
+        ref = plain_llama.forward(cfg, weights, p + o.generated_token_ids)
+        for i, tok in enumerate(o.generated_token_ids):
+            row = ref[len(p) - 1 + i]
+            assert float(row.max() - row[tok]) <= 2 * TOL[dtype], (i, tok, int(row.argmax()))
+    if dtype == torch.float32:
+        for p, o in zip(prompts, outs):
+            want, _ = plain_llama.greedy_generate(cfg, weights, p, n_new)
+            assert o.generated_token_ids == want
+    # a stop token ends a request early, is not returned, and frees its slot
+    stop = outs[0].generated_token_ids[2]
+    o = model.generate(prompts[0], InferenceOptions(temperature=0.0, max_tokens=n_new, stop_token_ids=[stop]))
+    assert o.finish_reason.value == "stop"
+    assert o.generated_token_ids == outs[0].generated_token_ids[:outs[0].generated_token_ids.index(stop)]
+    # one request alone gives what it gave in the batch
+    alone = model.generate(prompts[-1], opts)
+    if dtype == torch.float32:
+        assert alone.generated_token_ids == outs[-1].generated_token_ids
+
+
+def test_seeded_sampling_is_reproducible_and_batch_independent(tmp):
+    from dotllm_b200 import InferenceOptions
+    model, cfg, _, _ = load_pair(tmp, "A", torch.float32)
+    prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 70 + n) for n in (6, 13, 9)]
+    opts = [InferenceOptions(temperature=0.9, top_k=50, top_p=0.95, seed=11 + i, max_tokens=10, stop_token_ids=[])
+            for i in range(3)]
+    a = model.generate(prompts, opts)
+    b = model.generate(prompts, opts)
+    assert [o.generated_token_ids for o in a] == [o.generated_token_ids for o in b]
+    different = model.generate(prompts, [InferenceOptions(temperature=0.9, seed=99, max_tokens=10, stop_token_ids=[])] * 3)
+    assert [o.generated_token_ids for o in different] != [o.generated_token_ids for o in a]

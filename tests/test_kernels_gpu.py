@@ -1,0 +1,339 @@
+"""Each CUDA kernel alone against its plain torch reference, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+import kernel_refs
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def ops():
+    from dotllm_b200.kernels import ops as o
+    return o
+
+
+def close(a, b, atol, rtol=0.0):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    bound = atol + rtol * b.abs()
+    assert bool((err <= bound).all()), f"max err {float(err.max()):.3e} (bound {atol:.1e}+{rtol:.1e}*|ref|)"
+
+
+def bf16_round(x):
+    return x.to(torch.bfloat16).to(torch.float32)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,width,vocab", [(1, 48, 7), (37, 1000, 301)])
+def test_gather_rows(dtype, rows, width, vocab):
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(vocab, width, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (rows,), generator=g, dtype=torch.int32).to(DEV)
+    out = ops().gather_rows(table, ids)
+    assert out.dtype == torch.float32
+    assert torch.equal(out.cpu(), kernel_refs.gather_rows(table.cpu(), ids.cpu()))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("delta_dtype", [None, torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,width,eps", [(3, 72, 1e-5), (17, 1000, 1e-6), (2, 4096, 1e-5)])
+def test_add_rmsnorm(out_dtype, delta_dtype, rows, width, eps):
+    g = torch.Generator().manual_seed(2)
+    res = torch.randn(rows, width, generator=g) * 3
+    res[0, :5] = 100.0                                   # a row with large entries
+    gain = 1 + 0.1 * torch.randn(width, generator=g)
+    delta = None if delta_dtype is None else torch.randn(rows, width, generator=g).to(delta_dtype)
+    ref_res = res.clone()
+    ref = kernel_refs.add_rmsnorm(ref_res, delta, gain, eps, torch.float32)
+    d_res = res.to(DEV)
+    out = ops().add_rmsnorm(d_res, None if delta is None else delta.to(DEV), gain.to(DEV), eps, out_dtype)
+    assert out.dtype == out_dtype
+    close(d_res, ref_res, 0, 0) if delta is None else close(d_res, ref_res, 1e-6, 1e-6)
+    if out_dtype == torch.float32:
+        close(out, ref, 1e-5, 1e-5)
+    else:
+        close(out, ref, 1e-6, 2 ** -8)
+
+
+def test_rmsnorm_known_values():
+    """Hand-calculated case in the manner of the reference's RmsNormTests.KnownValues_HandCalculated
+    (tests/DotLLM.Tests.Unit/Cpu/Kernels/RmsNormTests.cs): x=[1,2,3,4], w=1, eps=0:
+    rms = sqrt(30/4)."""
+    x = torch.tensor([[1.0, 2.0, 3.0, 4.0]], device=DEV)
+    out = ops().add_rmsnorm(x, None, torch.ones(4, device=DEV), 1e-12, torch.float32)
+    rms = math.sqrt(30.0 / 4.0)
+    close(out, torch.tensor([[1 / rms, 2 / rms, 3 / rms, 4 / rms]]), 1e-6)
+    zeros = torch.zeros(1, 8, device=DEV)               # eps keeps 0/0 away
+    out = ops().add_rmsnorm(zeros, None, torch.ones(8, device=DEV), 1e-5, torch.float32)
+    assert bool(torch.isfinite(out).all()) and float(out.abs().max()) == 0.0
+
+
+def make_paged(n_seqs, lengths, nkv, hd, dtype, seed, n_pages=None, shuffle=True):
+    """Random K/V for sequences of the given lengths scattered over pages; returns pools, the
+    block table and the dense per-sequence K, V [len, nkv, hd] (already rounded to dtype)."""
+    g = torch.Generator().manual_seed(seed)
+    need = [(n + 63) // 64 for n in lengths]
+    total = sum(need)
+    n_pages = n_pages or total + 3
+    order = torch.randperm(n_pages, generator=g).tolist() if shuffle else list(range(n_pages))
+    width = max(need)
+    table = torch.full((n_seqs, width), -1, dtype=torch.int32)
+    k_pool = torch.full((n_pages, nkv, 64, hd), float("nan"))
+    v_pool = torch.full((n_pages, nkv, hd, 64), float("nan"))
+    dense = []
+    at = 0
+    for b, n in enumerate(lengths):
+        k = torch.randn(n, nkv, hd, generator=g).to(dtype).float()
+        v = torch.randn(n, nkv, hd, generator=g).to(dtype).float()
+        dense.append((k, v))
+        for p in range(need[b]):
+            page = order[at]
+            at += 1
+            table[b, p] = page
+            m = min(64, n - 64 * p)
+            k_pool[page, :, :m, :] = k[64 * p:64 * p + m].permute(1, 0, 2)
+            v_pool[page, :, :, :m] = v[64 * p:64 * p + m].permute(1, 2, 0)
+    return k_pool.to(dtype), v_pool.to(dtype), table, dense
+
+
+def dense_attention(q, k, v, nh, nkv, scale, pos, window):
+    first = max(0, pos - window + 1) if window else 0
+    kk = k[first:pos + 1].reshape(pos + 1 - first, -1)
+    vv = v[first:pos + 1].reshape(pos + 1 - first, -1)
+    return plain_llama.causal_attention(q[None].float(), kk, vv, nh, nkv, scale, position_offset=pos - first)[0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (6, 6, 32, 0), (8, 2, 64, 0), (5, 1, 48, 0),
+                                              (8, 2, 128, 0), (4, 4, 80, 0), (4, 2, 32, 37), (3, 3, 256, 100)])
+def test_attention_generic(dtype, nh, nkv, hd, window):
+    """Prefill chunks and decode tokens mixed in one call, unequal lengths, scattered pages with
+    NaN in every unused place."""
+    lengths = [1, 70, 133, 64, 200]
+    news = [1, 70, 5, 1, 130]                           # tokens this "step" brings (the tail of each)
+    k_pool, v_pool, table, dense = make_paged(5, lengths, nkv, hd, dtype, seed=3)
+    g = torch.Generator().manual_seed(4)
+    token_seq, token_pos = [], []
+    for b, (n, new) in enumerate(zip(lengths, news)):
+        for p in range(n - new, n):
+            token_seq.append(b)
+            token_pos.append(p)
+    T = len(token_seq)
+    q = torch.randn(T, nh * hd, generator=g).to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    out = ops().attention(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV),
+                          torch.tensor(token_seq, dtype=torch.int32, device=DEV),
+                          torch.tensor(token_pos, dtype=torch.int32, device=DEV), table.to(DEV),
+                          nh, nkv, hd, scale, window)
+    ref = torch.stack([dense_attention(q[t], *dense[token_seq[t]], nh, nkv, scale, token_pos[t], window)
+                       for t in range(T)])
+    assert bool(torch.isfinite(out).all())
+    if dtype == torch.float32:
+        close(out, ref, 2e-6, 1e-5)
+    else:
+        close(out, ref, 1e-3, 2 ** -7)
+
+
+def test_attention_far_key_stands_out():
+    """One far key among hundreds is made to dominate the scores: the output must be its value."""
+    nh, nkv, hd, n = 4, 2, 32, 700
+    k_pool, v_pool, table, dense = make_paged(1, [n], nkv, hd, torch.float32, seed=5)
+    k, v = dense[0]
+    q = torch.randn(1, nh * hd, generator=torch.Generator().manual_seed(6))
+    far = 3
+    for h in range(nh):
+        q[0, h * hd:(h + 1) * hd] = k[far, h // 2] * 50.0      # score ~ 50*|k|^2*scale: dominates
+    out = ops().attention(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                          torch.tensor([n - 1], dtype=torch.int32, device=DEV), table.to(DEV), nh, nkv, hd,
+                          1 / math.sqrt(hd), 0)
+    want = torch.cat([v[far, h // 2] for h in range(nh)])
+    close(out[0], want, 1e-4)
+    # the same query under a window that excludes the far key must not see it
+    out_w = ops().attention(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                            torch.tensor([n - 1], dtype=torch.int32, device=DEV), table.to(DEV), nh, nkv, hd,
+                            1 / math.sqrt(hd), 64)
+    ref_w = dense_attention(q[0], k, v, nh, nkv, 1 / math.sqrt(hd), n - 1, 64)
+    close(out_w[0], ref_w, 1e-5, 1e-5)
+    assert float((out_w[0].cpu() - want).abs().max()) > 0.1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rd", [(4, 2, 16, 16), (6, 6, 32, 32), (8, 2, 64, 32), (3, 1, 48, 0)])
+def test_rope_cache_write(dtype, nh, nkv, hd, rd):
+    g = torch.Generator().manual_seed(7)
+    lengths, news = [70, 5, 130], [70, 1, 3]
+    token_seq, token_pos = [], []
+    for b, (n, new) in enumerate(zip(lengths, news)):
+        for p in range(n - new, n):
+            token_seq.append(b)
+            token_pos.append(p)
+    T = len(token_seq)
+    n_pages = 9
+    table = torch.tensor([[4, 1, -1], [7, -1, -1], [0, 8, 2]], dtype=torch.int32)
+    q = torch.randn(T, nh * hd, generator=g).to(dtype)
+    kv = torch.randn(T, 2 * nkv * hd, generator=g).to(dtype)
+    k, v = kv[:, :nkv * hd], kv[:, nkv * hd:]           # views with a wider row stride
+    cos, sin = plain_llama.rope_tables(range(256), rd, 10000.0) if rd else (None, None)
+    pools = [torch.zeros(n_pages, nkv, 64, hd, dtype=dtype), torch.zeros(n_pages, nkv, hd, 64, dtype=dtype)]
+    ref_q = q.clone()
+    ref_pools = [p.clone() for p in pools]
+    seq_t, pos_t = torch.tensor(token_seq, dtype=torch.int32), torch.tensor(token_pos, dtype=torch.int32)
+    kernel_refs.rope_cache_write(ref_q, k, v, cos, sin, rd, seq_t, pos_t, table, *ref_pools, nh, nkv, hd)
+    d_q, d_kv = q.to(DEV), kv.to(DEV)
+    d_pools = [p.to(DEV) for p in pools]
+    ops().rope_cache_write(d_q, d_kv[:, :nkv * hd], d_kv[:, nkv * hd:],
+                           None if cos is None else cos.to(DEV), None if sin is None else sin.to(DEV), rd,
+                           seq_t.to(DEV), pos_t.to(DEV), table.to(DEV), *d_pools, nh, nkv, hd)
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -7
+    close(d_q, ref_q, tol, tol)
+    close(d_pools[0], ref_pools[0], tol, tol)
+    assert torch.equal(d_pools[1].cpu(), ref_pools[1])  # V is copied, not computed
+
+
+def test_rope_known_rotation():
+    """Position 0 changes nothing; at position 1 the pair (1, 0) of frequency 1 becomes
+    (cos 1, sin 1) (cf. RoPETests.PositionZero_NoChange / KnownRotation_HandCalculated,
+    tests/DotLLM.Tests.Unit/Cpu/Kernels/RoPETests.cs)."""
+    hd = 4
+    cos, sin = plain_llama.rope_tables(range(4), hd, 10000.0)
+    q = torch.tensor([[1.0, 2.0, 0.0, 0.0], [1.0, 0.0, 0.0, 0.0]], device=DEV)
+    ops().rope_cache_write(q, None, None, cos.to(DEV), sin.to(DEV), hd, None,
+                           torch.tensor([0, 1], dtype=torch.int32, device=DEV), None, None, None, 1, 1, hd,
+                           write_cache=False)
+    close(q[0], torch.tensor([1.0, 2.0, 0.0, 0.0]), 0)
+    close(q[1], torch.tensor([math.cos(1.0), 0.0, math.sin(1.0), 0.0]), 1e-7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,width", [(1, 176), (33, 1000)])
+def test_swiglu(dtype, rows, width):
+    x = (torch.randn(rows, 2 * width, generator=torch.Generator().manual_seed(8)) * 4).to(dtype)
+    out = ops().swiglu(x.to(DEV))
+    ref = kernel_refs.swiglu(x.float())
+    close(out, ref, 1e-6, 1e-5 if dtype == torch.float32 else 2 ** -8)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 5, 3), (7, 130, 70), (64, 64, 16), (65, 257, 1001), (300, 48, 176)])
+def test_gemm_f32(M, N, K):
+    g = torch.Generator().manual_seed(9)
+    x, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    y = ops().linear(x.to(DEV), w.to(DEV))
+    ref = (x.double() @ w.double().T).float()
+    close(y, ref, 1e-5 * math.sqrt(K), 1e-5)
+    # a row's result is the same bits whatever else is in the launch
+    y1 = ops().linear(x[:1].to(DEV), w.to(DEV))
+    assert torch.equal(y1.cpu(), y[:1].cpu())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 128), (5, 200, 320), (70, 1000, 176), (2048, 384, 192)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_bf16(M, N, K, out_dtype):
+    g = torch.Generator().manual_seed(10)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    y = ops().linear(x.to(DEV), w.to(DEV), out_dtype=out_dtype)
+    assert y.dtype == out_dtype
+    ref = x.double() @ w.double().T
+    close(y, ref.float(), 1e-3, 2 ** -8 if out_dtype == torch.bfloat16 else 1e-4)
+
+
+def test_argmax_ties_and_sizes():
+    g = torch.Generator().manual_seed(11)
+    for rows, vocab in [(1, 5), (3, 1000), (9, 128256)]:
+        x = torch.randn(rows, vocab, generator=g)
+        x[0, vocab // 2] = 50.0
+        x[0, vocab - 1] = 50.0                          # a tie: the first index wins
+        out = ops().sample(x.to(DEV))
+        assert out.tolist()[0] == vocab // 2
+        assert out.tolist()[1:] == torch.argmax(x, dim=-1).tolist()[1:]
+
+
+def _sampled_ok(row, tok, r, **kw):
+    """The kernel's token is the plain sampler's, or r lies within rounding of the boundary
+    between them on the plain sampler's running sum."""
+    ref = plain_llama.sample(row, [], r=r, **kw)
+    if tok == ref:
+        return True
+    x = plain_llama.apply_min_p(plain_llama.apply_top_p(plain_llama.apply_top_k(
+        plain_llama.apply_temperature(row, kw.get("temperature", 1.0)), kw.get("top_k", 0)),
+        kw.get("top_p", 1.0)), kw.get("min_p", 0.0))
+    if not math.isfinite(float(x[tok])):
+        return False
+    lo, hi = plain_llama.cdf_interval(x, tok)
+    return lo - 1e-5 <= r <= hi + 1e-5
+
+
+@pytest.mark.parametrize("vocab", [50, 1000, 32003])
+def test_sample_chain(vocab):
+    g = torch.Generator().manual_seed(12)
+    settings = [dict(temperature=1.0), dict(temperature=0.7), dict(temperature=1.3, top_k=5),
+                dict(temperature=0.9, top_p=0.8), dict(temperature=1.0, min_p=0.1),
+                dict(temperature=0.8, top_k=40, top_p=0.9, min_p=0.05), dict(temperature=2.0, top_k=1),
+                dict(temperature=1.0, top_p=0.01)]
+    rows = len(settings) * 4
+    x = torch.randn(rows, vocab, generator=g) * 3
+    u = torch.rand(rows, generator=g)
+    temp = torch.tensor([settings[i % len(settings)].get("temperature", 1.0) for i in range(rows)])
+    top_k = torch.tensor([settings[i % len(settings)].get("top_k", 0) for i in range(rows)], dtype=torch.int32)
+    top_p = torch.tensor([settings[i % len(settings)].get("top_p", 1.0) for i in range(rows)])
+    min_p = torch.tensor([settings[i % len(settings)].get("min_p", 0.0) for i in range(rows)])
+    out = ops().sample(x.to(DEV), temp.to(DEV), top_k.to(DEV), top_p.to(DEV), min_p.to(DEV), u.to(DEV)).tolist()
+    again = ops().sample(x.to(DEV), temp.to(DEV), top_k.to(DEV), top_p.to(DEV), min_p.to(DEV), u.to(DEV)).tolist()
+    assert out == again                                 # a seeded draw is reproducible
+    for i in range(rows):
+        assert _sampled_ok(x[i], out[i], float(u[i]), **settings[i % len(settings)]), (i, settings[i % len(settings)])
+
+
+def test_sample_top_k_ties_in_index_order():
+    """Five logits tie at the k-th value; only the first of them (by index) may be drawn
+    (src/DotLLM.Engine/Samplers/TopKSampler.cs:58-78)."""
+    vocab = 300
+    x = torch.full((64, vocab), -5.0)
+    x[:, 10] = 3.0
+    x[:, [20, 40, 60, 80, 100]] = 1.0                    # k = 3: 10, 20, 40 are kept
+    u = torch.linspace(0, 0.999, 64)
+    out = ops().sample(x.to(DEV), torch.ones(64, device=DEV), torch.full((64,), 3, dtype=torch.int32, device=DEV),
+                       torch.ones(64, device=DEV), torch.zeros(64, device=DEV), u.to(DEV)).tolist()
+    assert set(out) == {10, 20, 40}
+    for i in range(64):
+        assert out[i] == plain_llama.sample(x[i], [], temperature=1.0, top_k=3, r=float(u[i])) or \
+            _sampled_ok(x[i], out[i], float(u[i]), temperature=1.0, top_k=3)
+
+
+def test_sample_distribution():
+    """Many draws follow softmax(logits / T)."""
+    logits = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5])
+    n = 20000
+    u = (torch.arange(n) + 0.5) / n
+    out = ops().sample(logits.repeat(n, 1).to(DEV), torch.full((n,), 0.5, device=DEV), None, None, None, u.to(DEV))
+    freq = torch.bincount(out.cpu().long(), minlength=5).float() / n
+    close(freq, torch.softmax(logits / 0.5, 0), 2e-4)
+
+
+def test_repetition_penalty():
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(3, 200, generator=g)
+    prev = torch.tensor([[5, 7, 5, 9, 0, 0], [1, 2, 3, 4, 5, 6], [0, 0, 0, 0, 0, 0]], dtype=torch.int32)
+    n = torch.tensor([4, 6, 0], dtype=torch.int32)
+    pen = torch.tensor([1.3, 2.0, 1.5])
+    window = torch.tensor([0, 2, 0], dtype=torch.int32)
+    ref = kernel_refs.repetition_penalty(x.clone(), prev, n, pen, window)
+    out = ops().repetition_penalty(x.to(DEV), prev.to(DEV), n.to(DEV), pen.to(DEV), window.to(DEV))
+    close(out, ref, 1e-6)
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    from dotllm_b200.errors import KernelError
+    with pytest.raises(KernelError):
+        ops().add_rmsnorm(torch.zeros(2, 8), None, torch.ones(8), 1e-5, torch.float32)     # CPU tensors
+    with pytest.raises(KernelError):
+        ops().linear(torch.zeros(2, 8, device=DEV), torch.zeros(4, 9, device=DEV))
+    with pytest.raises(KernelError):
+        ops().attention(torch.zeros(1, 3 * 1024, device=DEV), torch.zeros(1, 1, 64, 1024, device=DEV),
+                        torch.zeros(1, 1, 1024, 64, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                        torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                        3, 1, 1024, 1.0)                                                    # head_dim too large
