@@ -1,0 +1,146 @@
+"""Decode steps replayed as CUDA graphs.
+
+A decode step launches a few hundred small kernels; issued one by one the host cannot keep up
+with the device (the reference pays ~14 launches per layer per token,
+src/DotLLM.Cuda/CudaTransformerModel.cs:198-286).  Here the whole forward pass of a step that
+brings one token per sequence is captured once per batch size and replayed.  Everything that
+changes from step to step - tokens, positions, lengths, slots, block tables - lives in fixed device
+buffers that one pinned host-to-device copy refreshes before each replay, so a captured graph
+serves any set of sequences of its batch size, wherever they are in the cache.
+
+The same kernels run, on the same data, as in an eager step: graphs change launch cost only.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.model_cache import PAGE
+from ..errors import StepError
+from .step import AttentionPlan, StepContext
+
+_RING = 4            # pinned staging buffers in flight
+
+
+class _Captured:
+    def __init__(self, model, cache, batch, pages, n_groups):
+        dev = model.runtime.device
+        self.batch, self.pages = batch, pages
+        self.capacity = pages * PAGE                       # longest sequence this graph serves
+        n = 3 * batch + n_groups * batch * pages           # positions, lengths, slots, block tables
+        self.ints = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.host = [torch.zeros(n + batch, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.events = [None] * _RING
+        self.turn = 0
+        b = batch
+        self.pos, self.total, self.slots = self.ints[0:b], self.ints[b:2 * b], self.ints[2 * b:3 * b]
+        self.tables = {}
+        at = 3 * b
+        for g in cache.kv_groups:
+            self.tables[g.index] = self.ints[at:at + b * pages].view(b, pages)
+            at += b * pages
+        arange = torch.arange(b + 1, dtype=torch.int32, device=dev)
+        ones = torch.ones(b, dtype=torch.int32, device=dev)
+        plan = AttentionPlan(n_seqs=b, max_new=1, max_total=self.capacity, all_single=True,
+                             seq_start=self.pos, seq_new=ones, cu_new=arange, seq_total=self.total,
+                             starts=[], news=[1] * b)
+        self.ctx = StepContext(n_tokens=b, n_seqs=b, tokens=self.tokens, token_seq=arange[:b].contiguous(),
+                               token_pos=self.pos, slots=self.slots, block_tables=self.tables,
+                               want_rows=arange[:b].contiguous(), n_wanted=b, want_all=True,
+                               attention_plan=plan, seq_start=self.pos, seq_new=ones, cu_new=arange)
+        self.graph = None
+        self.logits = None
+
+    def stage(self, seqs, tokens, kv_groups):
+        """Copy this step's positions, lengths, slots and block tables (and tokens, when the host
+        supplies them) to the device."""
+        i = self.turn
+        self.turn = (self.turn + 1) % _RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()                   # the copy that last used this buffer is done
+        b, p = self.batch, self.pages
+        rows = [[s.length for s in seqs], [s.length + 1 for s in seqs], [s.slot for s in seqs]]
+        flat = [v for r in rows for v in r]
+        for g in kv_groups:
+            for s in seqs:
+                pages = s.pages[g.index]
+                flat.extend(pages)
+                flat.extend([-1] * (p - len(pages)))
+        host = self.host[i]
+        n = len(flat)
+        host[:n] = torch.tensor(flat, dtype=torch.int32)
+        self.ints.copy_(host[:n], non_blocking=True)
+        if tokens is not None:
+            host[n:n + b] = torch.tensor(tokens, dtype=torch.int32)
+            self.tokens.copy_(host[n:n + b], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+    def capture(self, model, cache):
+        # One eager run first: lazy allocations (counters, library workspaces) must not happen
+        # inside the capture.  It writes the same cache entries the replay will write.
+        side = torch.cuda.Stream(device=model.runtime.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            model.forward(self.ctx, cache)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.ctx.attention_plan.scratch.clear()            # scratch must come from the graph's own pool
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = model.forward(self.ctx, cache)
+
+
+class DecodeGraphs:
+    """Captured decode steps of one model and cache, by batch size."""
+
+    def __init__(self, model, cache):
+        self.model = model
+        self.cache = cache
+        self.captured = {}
+        self.captures = 0
+
+    def takes(self, entries):
+        return all(len(e.tokens) == 1 and (e.want is None or list(e.want) == [0]) for e in entries)
+
+    def run(self, entries, device_tokens=False):
+        """One decode step for ``entries`` (one token each).  Returns float32 logits [B, vocab] in a
+        buffer that the next replay of the same batch size overwrites.  With ``device_tokens`` the
+        tokens already in the graph's token buffer are used (``token_buffer(B)``), and the entries'
+        tokens are ignored."""
+        model, cache = self.model, self.cache
+        seqs = [e.sequence for e in entries]
+        b = len(seqs)
+        slots = set()
+        for i, (e, s) in enumerate(zip(entries, seqs)):
+            if not getattr(s, "open", False):
+                raise StepError(f"entry {i}: its sequence is closed")
+            if s.slot in slots:
+                raise StepError(f"entry {i}: slot {s.slot} occurs twice in one step")
+            slots.add(s.slot)
+            if s.length + 1 > model.spec.max_positions:
+                raise StepError(f"entry {i}: position {s.length} is beyond the model's max positions "
+                                f"{model.spec.max_positions}")
+            if not device_tokens and not 0 <= int(e.tokens[0]) < model.spec.vocab_size:
+                raise StepError(f"entry {i}: token id {e.tokens[0]} is outside the vocabulary")
+        cache.reserve([(s, s.length + 1) for s in seqs])
+        pages = max(max((len(s.pages[g.index]) for g in cache.kv_groups), default=1) for s in seqs)
+        cap = self.captured.get(b)
+        fresh = cap is None or cap.pages < pages
+        if fresh:
+            room = min((model.spec.max_positions + PAGE - 1) // PAGE, max(pages + 16, (pages * 5) // 4))
+            cap = _Captured(model, cache, b, max(room, pages), len(cache.kv_groups))
+            self.captured[b] = cap
+        cap.stage(seqs, None if device_tokens else [int(e.tokens[0]) for e in entries], cache.kv_groups)
+        if fresh:
+            cap.capture(model, cache)
+            self.captures += 1
+        cap.graph.replay()
+        for s in seqs:
+            cache.commit(s, s.length + 1)
+        return cap.logits
+
+    def token_buffer(self, batch):
+        """The device token buffer of the graph for ``batch`` sequences (after its first run)."""
+        return self.captured[batch].tokens

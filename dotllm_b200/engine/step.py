@@ -40,6 +40,7 @@ class AttentionPlan:
     seq_start: torch.Tensor       # int32 [B] cached length before the step
     seq_new: torch.Tensor         # int32 [B] tokens brought
     cu_new: torch.Tensor          # int32 [B+1] offsets of each sequence's tokens in the packed step
+    seq_total: torch.Tensor       # int32 [B] length after the step
     starts: list = field(default_factory=list)
     news: list = field(default_factory=list)
     scratch: dict = field(default_factory=dict)
@@ -114,7 +115,8 @@ def plan_step(entries, cache, vocab_size, max_positions, device):
     for n in news:
         cu.append(cu[-1] + n)
     # one packed int32 buffer, one copy
-    parts = [tokens, token_seq, token_pos, slots, starts, news, cu, want_rows]
+    totals = [s + n for s, n in zip(starts, news)]
+    parts = [tokens, token_seq, token_pos, slots, starts, news, cu, want_rows, totals]
     for rows, width in tables.values():
         parts.append([p for row in rows for p in row])
     flat = [v for part in parts for v in part]
@@ -127,18 +129,18 @@ def plan_step(entries, cache, vocab_size, max_positions, device):
     for part in parts:
         views.append(dev[at:at + len(part)])
         at += len(part)
-    d_tokens, d_seq, d_pos, d_slots, d_starts, d_news, d_cu, d_want = views[:8]
+    d_tokens, d_seq, d_pos, d_slots, d_starts, d_news, d_cu, d_want, d_totals = views[:9]
     block_tables = {}
-    for (gi, (rows, width)), view in zip(tables.items(), views[8:]):
+    for (gi, (rows, width)), view in zip(tables.items(), views[9:]):
         block_tables[gi] = view.view(B, width)
-    plan = AttentionPlan(n_seqs=B, max_new=max(news), max_total=max(s + n for s, n in zip(starts, news)),
+    plan = AttentionPlan(n_seqs=B, max_new=max(news), max_total=max(totals),
                          all_single=all(n == 1 for n in news), seq_start=d_starts, seq_new=d_news,
-                         cu_new=d_cu, starts=starts, news=news)
+                         cu_new=d_cu, seq_total=d_totals, starts=starts, news=news)
     ctx = StepContext(n_tokens=T, n_seqs=B, tokens=d_tokens, token_seq=d_seq, token_pos=d_pos,
                       slots=d_slots, block_tables=block_tables, want_rows=d_want, n_wanted=R,
                       want_all=(R == T and want_rows == list(range(T))), attention_plan=plan,
                       seq_start=d_starts, seq_new=d_news, cu_new=d_cu)
-    return ctx, [s + n for s, n in zip(starts, news)]
+    return ctx, totals
 
 
 def run_step(model, cache, entries):

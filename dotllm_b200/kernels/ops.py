@@ -226,8 +226,24 @@ def linear(x, w, out_dtype=None):
     return torch.mm(x, w.t(), out_dtype=out_dtype)
 
 
+def gated_linear(x, w_gate_up):
+    """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] of shape [2I, K]; returns [T, I] in x's dtype.
+    For a few bfloat16 rows one kernel does the product and the gating; otherwise the product
+    is followed by the gating kernel."""
+    _need_cuda(x, w_gate_up)
+    if w_gate_up.dim() != 2 or w_gate_up.shape[0] % 2 or not w_gate_up.is_contiguous() or x.dim() != 2 \
+            or x.shape[1] != w_gate_up.shape[1]:
+        raise KernelError(f"gated_linear: x {tuple(x.shape)} does not match W {tuple(w_gate_up.shape)}")
+    if x.dtype == torch.bfloat16 and x.shape[0] > 0:
+        from . import gemm_skinny
+        y = gemm_skinny.maybe_run(x, w_gate_up, x.dtype, fuse_swiglu=True)
+        if y is not None:
+            return y
+    return swiglu(linear(x, w_gate_up))
+
+
 # ------------------------------------------------------------------- sampling
-def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None):
+def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None, out=None):
     """One token per row of float32 logits [R, V].  With ``temperature`` None every row is
     greedy (first index of the maximum).  Otherwise per-row float32/int32 tensors [R] give the
     chain temperature -> top-k -> top-p -> min-p and ``uniform`` the draw in [0, 1);
@@ -241,7 +257,10 @@ def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform
                         ("uniform", uniform, torch.float32)):
         if t is not None and (t.dtype != dt or t.shape != (rows,) or not t.is_contiguous()):
             raise KernelError(f"sample: {name} must be a contiguous {dt} tensor of {rows} values")
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    elif out.dtype != torch.int32 or out.shape != (rows,) or not out.is_contiguous() or not out.is_cuda:
+        raise KernelError("sample: out must be a contiguous int32 CUDA tensor of one id per row")
     _library.call("dl_sample", _ptr(logits), logits.stride(0) if rows > 1 else vocab, rows, vocab,
                   _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(out),
                   _stream())

@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from .config.registry import build_spec, load_config
+from .engine.decode_graph import DecodeGraphs
 from .engine.generate import TextGenerator
 from .engine.step import StepEntry, run_step
 from .errors import ConfigError, KernelError
@@ -85,17 +86,33 @@ class Model:
     def new_cache(self, max_tokens, max_sequences=None):
         return self.decoder.new_cache(max_tokens, max_sequences)
 
-    def step(self, cache, entries):
+    def step(self, cache, entries, graphs=False):
         """Run one step; ``entries`` are StepEntry objects (or (sequence, tokens[, want]) tuples).
-        Returns float32 logits [wanted, vocab]."""
+        Returns float32 logits [wanted, vocab].
+
+        With ``graphs`` a step that brings one token per sequence and wants each one's logits is
+        replayed as a CUDA graph (captured once per batch size); the returned tensor is then a
+        buffer that the next such step overwrites."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if graphs:
+            runner = self.decode_graphs(cache)
+            if runner.takes(entries):
+                return runner.run(entries)
         return run_step(self.decoder, cache, entries)
 
-    def generator(self, cache=None, max_tokens=None, max_batch=None):
+    def decode_graphs(self, cache):
+        """The captured decode steps that belong to ``cache``."""
+        runner = getattr(cache, "_decode_graphs", None)
+        if runner is None or runner.model is not self.decoder:
+            runner = DecodeGraphs(self.decoder, cache)
+            cache._decode_graphs = runner
+        return runner
+
+    def generator(self, cache=None, max_tokens=None, max_batch=None, use_graphs=True):
         """A TextGenerator over this model.  Without a cache one is made for ``max_tokens``."""
         if cache is None:
             cache = self.new_cache(max_tokens or min(self.spec.max_positions * 8, 1 << 16))
-        return TextGenerator(lambda entries: self.step(cache, entries), sample_rows, cache,
+        return TextGenerator(lambda entries: self.step(cache, entries, graphs=use_graphs), sample_rows, cache,
                              max_positions=self.spec.max_positions, vocab_size=self.spec.vocab_size,
                              default_stop_ids=self.spec.stop_token_ids, bos_token_id=self.spec.bos_token_id,
                              max_batch=max_batch, synchronize=torch.cuda.synchronize)

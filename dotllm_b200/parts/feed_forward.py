@@ -39,8 +39,7 @@ class GatedFeedForward(FeedForward):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
     def forward(self, x):
-        gate_up = ops.linear(x, self.w_gate_up)
-        return ops.linear(ops.swiglu(gate_up), self.w_down, out_dtype=BRANCH_DTYPE)
+        return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down, out_dtype=BRANCH_DTYPE)
 
 
 register_feed_forward("gated_mlp", GatedFeedForward)

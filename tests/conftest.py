@@ -27,7 +27,7 @@ def cpu_kernels(monkeypatch):
     host logic (step planning, cache addressing, block wiring) can run without a GPU."""
     import kernel_refs
     from dotllm_b200.kernels import ops
-    for name in ("gather_rows", "add_rmsnorm", "rope_cache_write", "attention", "swiglu", "linear",
+    for name in ("gather_rows", "add_rmsnorm", "rope_cache_write", "attention", "swiglu", "linear", "gated_linear",
                  "sample", "repetition_penalty"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
     return kernel_refs

@@ -93,6 +93,10 @@ def linear(x, w, out_dtype=None):
     return y.to(out_dtype or x.dtype)
 
 
+def gated_linear(x, w_gate_up):
+    return swiglu(linear(x, w_gate_up, torch.float32)).to(x.dtype)
+
+
 def repetition_penalty(logits, prev, prev_len, penalty, window):
     for r in range(logits.shape[0]):
         previous = prev[r, :int(prev_len[r])].tolist()
@@ -101,7 +105,7 @@ def repetition_penalty(logits, prev, prev_len, penalty, window):
     return logits
 
 
-def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None):
+def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None, out=None):
     out = []
     for r in range(logits.shape[0]):
         row = logits[r].detach().cpu()
