@@ -464,4 +464,7 @@ def test_attention_prefill_packed_unequal(nh, nkv, hd, window):
     ref = torch.stack([dense_attention(q[t], *dense[token_seq[t]], nh, nkv, scale, token_pos[t], window)
                        for t in range(T)])
     assert bool(torch.isfinite(fast).all())
-    close(fast, ref, 2e-3, 2 ** -7)
+    # The tensor-core kernel rounds the softmax weights to bfloat16 (relative step 2^-9 after
+    # rounding to nearest) for the P V product: |error| <= 2^-9 max|v|, plus the output's rounding.
+    v_max = max(float(v.abs().max()) for _, v in dense)
+    close(fast, ref, 2 ** -9 * v_max + 1e-3, 2 ** -8)

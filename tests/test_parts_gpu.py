@@ -1,0 +1,247 @@
+"""Each part alone against the plain implementation, and a toy architecture defined here - a
+mixer with state of its own, a windowed attention layer, a layer that runs twice, a layer that
+reads another's cache - registered, built and stepped without touching the package."""
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_llama
+import tiny_models
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+
+
+def runtime(dtype=torch.float32):
+    from dotllm_b200.parts import Runtime
+    return Runtime(dtype, DEV)
+
+
+def bind_random(part, seed, dtype):
+    from dotllm_b200.weights import random_tensor
+    tensors = {}
+    for name, spec in part.weight_specs().items():
+        t = random_tensor(name, spec, seed)
+        tensors[name] = (t.to(dtype) if spec.role == "matrix" else t).to(DEV)
+    part.bind(tensors)
+    return {k: v.float().cpu() for k, v in tensors.items()}
+
+
+def test_norm_part():
+    from dotllm_b200.config import PartSpec
+    from dotllm_b200.parts import make_part
+    norm = make_part("norm", PartSpec("rmsnorm", {"eps": 1e-6, "gain_init": ("one_plus_uniform", 0.2)}), 200, runtime())
+    w = bind_random(norm, 1, torch.float32)
+    x = torch.randn(7, 200, generator=torch.Generator().manual_seed(0))
+    d = torch.randn(7, 200, generator=torch.Generator().manual_seed(1))
+    want = plain_llama.rms_norm(x, w["weight"], 1e-6)
+    assert torch.allclose(norm.forward(x.to(DEV)).cpu(), want, atol=1e-5)
+    res = x.to(DEV)
+    got = norm.add_forward(res, d.to(DEV))
+    assert torch.allclose(res.cpu(), x + d, atol=1e-6)
+    assert torch.allclose(got.cpu(), plain_llama.rms_norm(x + d, w["weight"], 1e-6), atol=1e-5)
+
+
+def test_rotary_part_tables_and_bands():
+    from dotllm_b200.config import PartSpec
+    from dotllm_b200.parts import make_part
+    scaling = dict(tiny_models.TINY_B["rope_scaling"])
+    pe = make_part("position_encoding", PartSpec("rotary", {"rotary_dim": 32, "head_dim": 32, "theta": 500000.0,
+                                                            "max_positions": 256, "scaling": scaling}), 192, runtime())
+    cos, sin = plain_llama.rope_tables(range(256), 32, 500000.0, scaling)
+    assert torch.equal(pe.cos.cpu(), cos) and torch.equal(pe.sin.cpu(), sin)
+    q = torch.randn(5, 3 * 32, generator=torch.Generator().manual_seed(2))
+    pos = torch.tensor([0, 1, 63, 64, 255], dtype=torch.int32)
+    d_q = q.to(DEV)
+    pe.apply(d_q, None, pos.to(DEV))
+    want = plain_llama.apply_rope(q.view(5, 3, 32), cos[pos.long()], sin[pos.long()]).reshape(5, 96)
+    assert torch.allclose(d_q.cpu(), want, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from dotllm_b200.config import PartSpec
+    from dotllm_b200.parts import make_part
+    ffn = make_part("feed_forward", PartSpec("gated_mlp", {"intermediate_size": 176, "activation": "silu"}), 64,
+                    runtime(dtype))
+    w = bind_random(ffn, 3, dtype)
+    weights = {"p.mlp." + k: v for k, v in w.items()}
+    for rows in (3, 40):                                 # few rows: fused kernel; many: product + gating
+        x = torch.randn(rows, 64, generator=torch.Generator().manual_seed(rows)).to(dtype)
+        want = plain_llama.feed_forward_part(x.float(), weights, "p.")
+        got = ffn.forward(x.to(DEV)).float().cpu()
+        assert torch.allclose(got, want, atol=1e-6 if dtype == torch.float32 else 2e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts(dtype):
+    from dotllm_b200.config import PartSpec
+    from dotllm_b200.parts import make_part
+    emb = make_part("embedding", PartSpec("token_embedding", {"vocab_size": 300}), 48, runtime(dtype))
+    head = make_part("head", PartSpec("linear_head", {"vocab_size": 300, "tied": True}), 48, runtime(dtype))
+    w = bind_random(emb, 4, dtype)
+    head.bind({})
+    head.tie(emb.table)
+    ids = torch.tensor([0, 299, 5, 5], dtype=torch.int32)
+    h = emb.forward(ids.to(DEV))
+    assert h.dtype == torch.float32 and torch.equal(h.cpu(), w["weight"][ids.long()])
+    logits = head.forward(h.to(dtype))
+    want = w["weight"][ids.long()] @ w["weight"].T
+    assert logits.dtype == torch.float32
+    assert torch.allclose(logits.cpu(), want, atol=1e-6 if dtype == torch.float32 else 1e-4)
+
+
+# ---------------------------------------------------------------------------------- a toy model
+def toy_parts():
+    """Parts defined in the test: a mixer with a decaying state per sequence, and a position
+    encoding that is not a rotation."""
+    from dotllm_b200.parts import (CacheNeed, Mixer, PositionEncoding, WeightSpec, register_mixer,
+                                   register_position_encoding)
+
+    class DecayMixer(Mixer):
+        """s_t = a * s_{t-1} + x_t W_in ; y_t = s_t W_out.  Keeps s per sequence in the cache's
+        fixed-size state."""
+
+        def __init__(self, params, hidden_size, runtime):
+            super().__init__(params, hidden_size, runtime)
+            self.width = int(params["state_width"])
+            self.decay = float(params["decay"])
+
+        def weight_specs(self):
+            return {"in_proj.weight": WeightSpec((self.width, self.hidden_size)),
+                    "out_proj.weight": WeightSpec((self.hidden_size, self.width))}
+
+        def bind(self, tensors):
+            self.w_in, self.w_out = tensors["in_proj.weight"], tensors["out_proj.weight"]
+
+        def cache_need(self):
+            return CacheNeed("state", state_shape=(self.width,), state_dtype=torch.float32)
+
+        def forward(self, x, step, view):
+            u = x.float() @ self.w_in.float().T                      # [T, width]
+            out = torch.empty_like(u)
+            seqs, slots = step.token_seq.tolist(), view.slots.tolist()
+            for t in range(u.shape[0]):                              # tokens of a sequence arrive in order
+                slot = slots[seqs[t]]
+                view.state[slot] = self.decay * view.state[slot] + u[t]
+                out[t] = view.state[slot]
+            return (out @ self.w_out.float().T).to(torch.float32)
+
+    class ShiftEncoding(PositionEncoding):
+        """Adds pos * slope to the first dimension of every query and key head (not a rotation)."""
+
+        def apply(self, q, k, positions):
+            hd = int(self.params["head_dim"])
+            shift = positions.float() * float(self.params["slope"])
+            for x in (q, k):
+                if x is not None:
+                    x[:, ::hd] += shift[:, None].to(x.dtype)
+
+    register_mixer("toy_decay", DecayMixer)
+    register_position_encoding("toy_shift", ShiftEncoding)
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int = 97
+    hidden_size: int = 48
+    architecture: str = "ToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(int(d["vocab_size"]), int(d["hidden_size"]))
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size}
+
+
+def toy_spec(cfg):
+    from dotllm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    norm = lambda p: PartSpec("rmsnorm", {"eps": 1e-5, "gain_init": ("one_plus_uniform", 0.1)}, p)
+    ffn = lambda p, i: PartSpec("gated_mlp", {"intermediate_size": i, "activation": "silu"}, p)
+    attn = PartSpec("attention", {"n_heads": 3, "n_kv_heads": 1, "head_dim": 16, "window": 40,
+                                  "position": {"kind": "toy_shift", "params": {"head_dim": 16, "slope": 0.01}}},
+                    "l0.attn.")
+    decay = PartSpec("toy_decay", {"state_width": 24, "decay": 0.9}, "l1.mix.")
+    layers = (LayerSpec("pre_norm", attn, ffn("l0.ffn.", 80), norm("l0.n1."), norm("l0.n2.")),
+              LayerSpec("pre_norm", decay, ffn("l1.ffn.", 56), norm("l1.n1."), norm("l1.n2.")))
+    # layer 0, layer 1, layer 1 again (its own state), layer 0 again reading the first run's cache
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(0, cache_of=0))
+    return ModelSpec("ToyForCausalLM", cfg.hidden_size, cfg.vocab_size, 512,
+                     PartSpec("token_embedding", {"vocab_size": cfg.vocab_size}, "emb."), layers, schedule,
+                     norm("final."), PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "tied": False}, "head."))
+
+
+def toy_plain(w, tokens):
+    """The toy model over a whole sequence with elementary operations."""
+    n = len(tokens)
+    h = w["emb.weight"][torch.tensor(tokens)]
+    pos = torch.arange(n, dtype=torch.float32)
+    kept = {}
+    for e, (layer, share) in enumerate([(0, None), (1, None), (1, None), (0, 0)]):
+        p = f"l{layer}."
+        x = plain_llama.rms_norm(h, w[p + "n1.weight"], 1e-5)
+        if layer == 0:
+            q = (x @ w[p + "attn.q_proj.weight"].T).clone()
+            q[:, ::16] += pos[:, None] * 0.01
+            if share is None:
+                k = (x @ w[p + "attn.k_proj.weight"].T).clone()
+                k[:, ::16] += pos[:, None] * 0.01
+                kept[e] = (k, x @ w[p + "attn.v_proj.weight"].T)
+            k, v = kept[e if share is None else share]
+            a = plain_llama.causal_attention(q, k, v, 3, 1, 0.25, window=40)
+            h = h + a @ w[p + "attn.o_proj.weight"].T
+        else:
+            u = x @ w[p + "mix.in_proj.weight"].T
+            s = torch.zeros(24)
+            outs = []
+            for t in range(n):
+                s = 0.9 * s + u[t]
+                outs.append(s.clone())
+            h = h + torch.stack(outs) @ w[p + "mix.out_proj.weight"].T
+        x = plain_llama.rms_norm(h, w[p + "n2.weight"], 1e-5)
+        g, u2 = x @ w[p + "ffn.gate_proj.weight"].T, x @ w[p + "ffn.up_proj.weight"].T
+        h = h + plain_llama.swiglu(g, u2) @ w[p + "ffn.down_proj.weight"].T
+    return plain_llama.rms_norm(h, w["final.weight"], 1e-5) @ w["head.weight"].T
+
+
+def test_toy_architecture_registers_builds_and_steps(tmp_path):
+    from dotllm_b200 import Model, StepEntry
+    from dotllm_b200.config import register_architecture
+    from dotllm_b200.weights import write_random_model
+    toy_parts()
+    register_architecture("ToyForCausalLM", ToyConfig, toy_spec)
+    folder = write_random_model(tmp_path / "toy", ToyConfig(), seed=2, dtype=torch.float32)
+    _, w = plain_llama.read_model_folder(folder)
+    model = Model.load(folder, dtype="float32")                     # the class is chosen by config.json
+    assert model.spec.architecture == "ToyForCausalLM"
+    cache = model.new_cache(64 * 6, max_sequences=3)
+    kinds = sorted((g.kind, len(g.entries)) for g in cache.groups)
+    assert kinds == [("kv", 1), ("state", 2)]                        # the shared execution owns no storage
+    a = tiny_models.random_tokens(150, 97, 1)
+    b = tiny_models.random_tokens(60, 97, 2)
+    ra, rb = toy_plain(w, a), toy_plain(w, b)
+    sa, sb = cache.open_sequence(), cache.open_sequence()
+    got_a = [model.step(cache, [StepEntry(sa, a[:100], list(range(100))), StepEntry(sb, b[:7], [])])]
+    got_b = []
+    for t in range(100, 150):
+        entries = [StepEntry(sa, [a[t]])]
+        if t - 93 < 60:
+            entries.append(StepEntry(sb, [b[t - 93]]))
+        out = model.step(cache, entries)
+        got_a.append(out[:1])
+        if len(entries) == 2:
+            got_b.append(out[1:2])
+    assert float((torch.cat(got_a).cpu() - ra).abs().max()) < 5e-5
+    assert float((torch.cat(got_b).cpu() - rb[7:57]).abs().max()) < 5e-5
+    # the window released pages of the attention group; the state slot is zeroed for its next owner
+    assert -1 in sa.pages[cache.kv_groups[0].index]
+    slot = sb.slot
+    cache.close_sequence(sb)
+    sc = cache.open_sequence()
+    assert sc.slot == slot
+    out = model.step(cache, [StepEntry(sc, b[:30], list(range(30)))])
+    assert float((out.cpu() - rb[:30]).abs().max()) < 5e-5
+    cache.check()
