@@ -8,6 +8,9 @@
 // rotated in place and rotated K goes straight to its cache page.  V pages are transposed.
 #include "common.cuh"
 
+// Grid: (token, head) with the query heads first, then the KV heads; a block's threads each take
+// one rotation pair (query heads) or one dimension (KV heads), so a decode step's handful of
+// tokens still spreads over hundreds of blocks and no thread loops over dependent loads.
 template <typename T>
 __global__ void __launch_bounds__(128)
 rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
@@ -23,37 +26,37 @@ rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
     const float* cs = cos_t + (size_t)pos * half;
     const float* sn = sin_t + (size_t)pos * half;
 
-    // Q: rotate in place.
-    T* qrow = q + (size_t)t * q_stride;
-    for (int w = threadIdx.x; w < nh * half; w += blockDim.x) {
-        const int h = w / half, i = w - h * half;
-        T* p = qrow + h * hd;
-        const float x0 = dl_to_f32<T>(p[i]), x1 = dl_to_f32<T>(p[i + half]);
-        const float c = cs[i], s = sn[i];
-        p[i] = dl_from_f32<T>(x0 * c - x1 * s);
-        p[i + half] = dl_from_f32<T>(x0 * s + x1 * c);
+    if ((int)blockIdx.y < nh) {                                   // a query head: rotate in place
+        T* p = q + (size_t)t * q_stride + (size_t)blockIdx.y * hd;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float x0 = dl_to_f32<T>(p[i]), x1 = dl_to_f32<T>(p[i + half]);
+            const float c = cs[i], s = sn[i];
+            p[i] = dl_from_f32<T>(x0 * c - x1 * s);
+            p[i + half] = dl_from_f32<T>(x0 * s + x1 * c);
+        }
+        return;
     }
     if (!write_cache) return;
-
+    const int h = blockIdx.y - nh;                                // a KV head: rotate K on its way to the page
     const int seq = token_seq[t];
     const int page = block_table[(size_t)seq * bt_stride + pos / DL_PAGE];
     if (page < 0 || page >= n_pages) return;
     const int in_page = pos % DL_PAGE;
-    const T* krow = k + (size_t)t * k_stride;
-    const T* vrow = v + (size_t)t * v_stride;
-    for (int w = threadIdx.x; w < nkv * hd; w += blockDim.x) {
-        const int h = w / hd, d = w - h * hd;
+    const T* krow = k + (size_t)t * k_stride + (size_t)h * hd;
+    const T* vrow = v + (size_t)t * v_stride + (size_t)h * hd;
+    T* kdst = k_pool + dl_k_offset(page, nkv, h, in_page, hd);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float kv;
         if (d < half) {
-            kv = dl_to_f32<T>(krow[h * hd + d]) * cs[d] - dl_to_f32<T>(krow[h * hd + d + half]) * sn[d];
+            kv = dl_to_f32<T>(krow[d]) * cs[d] - dl_to_f32<T>(krow[d + half]) * sn[d];
         } else if (d < 2 * half) {
             const int i = d - half;
-            kv = dl_to_f32<T>(krow[h * hd + i]) * sn[i] + dl_to_f32<T>(krow[h * hd + d]) * cs[i];
+            kv = dl_to_f32<T>(krow[i]) * sn[i] + dl_to_f32<T>(krow[d]) * cs[i];
         } else {
-            kv = dl_to_f32<T>(krow[h * hd + d]);
+            kv = dl_to_f32<T>(krow[d]);
         }
-        k_pool[dl_k_offset(page, nkv, h, in_page, hd) + d] = dl_from_f32<T>(kv);
-        v_pool[dl_v_offset(page, nkv, h, d, hd) + in_page] = vrow[h * hd + d];
+        kdst[d] = dl_from_f32<T>(kv);
+        v_pool[dl_v_offset(page, nkv, h, d, hd) + in_page] = vrow[d];
     }
 }
 
@@ -73,13 +76,15 @@ extern "C" int dl_rope_cache_write(void* q, int q_stride, const void* k, int k_s
                "rope_cache_write: cache write needs k, v, pools and a block table");
     if (n_tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    DL_REQUIRE(nh + nkv <= 65535, "rope_cache_write: too many heads");
+    dim3 grid(n_tokens, write_cache ? nh + nkv : nh);
     if (dtype == DL_F32)
-        rope_cache_write_kernel<float><<<n_tokens, 128, 0, s>>>(
+        rope_cache_write_kernel<float><<<grid, 128, 0, s>>>(
             (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, cos_t, sin_t, rotary_dim,
             table_rows, token_seq, token_pos, block_table, bt_stride, (float*)k_pool, (float*)v_pool, n_pages, nh,
             nkv, hd, write_cache);
     else if (dtype == DL_BF16)
-        rope_cache_write_kernel<__nv_bfloat16><<<n_tokens, 128, 0, s>>>(
+        rope_cache_write_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(
             (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride,
             cos_t, sin_t, rotary_dim, table_rows, token_seq, token_pos, block_table, bt_stride,
             (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, nh, nkv, hd, write_cache);

@@ -1,0 +1,153 @@
+"""Time one kernel alone at a given size (CUDA events, warm-up, L2 flushed between runs).
+
+    python -m dotllm_b200.kernels.microbench attention_decode --batch 8 --context 8192
+    python -m dotllm_b200.kernels.microbench gemm_skinny --rows 8 --n 28672 --k 4096 --gated
+    python -m dotllm_b200.kernels.microbench attention_prefill --tokens 2048
+    python -m dotllm_b200.kernels.microbench norm --rows 8 --width 4096
+    python -m dotllm_b200.kernels.microbench rope --rows 8
+
+Prints one JSON line with the time, the algorithmic bytes or FLOPs, and the fraction of the
+measured peak.  The same command under ``ncu -k regex:<kernel>`` gives the counters for the
+summaries in profiles/.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        d = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except (OSError, ValueError, KeyError):
+        return 6650.0, 1590.0, "fallback"
+
+
+def _time(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1)                                   # more bytes than the L2 holds
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def _paged(batch, context, nkv, hd, dev):
+    pages_per = (context + 63) // 64
+    n_pages = batch * pages_per
+    k_pool = torch.randn(n_pages, nkv, 64, hd, device=dev, dtype=torch.bfloat16)
+    v_pool = torch.randn(n_pages, nkv, hd, 64, device=dev, dtype=torch.bfloat16)
+    table = torch.randperm(n_pages, device=dev).to(torch.int32).view(batch, pages_per).contiguous()
+    return k_pool, v_pool, table
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_skinny", "norm", "rope"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--width", type=int, default=4096)
+    ap.add_argument("--gated", action="store_true")
+    ap.add_argument("--out-f32", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args(argv)
+
+    from ..engine.step import AttentionPlan
+    from . import gemm_skinny, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm, tflops, source = _peaks()
+    flush = None if args.no_flush else torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    nh, nkv, hd = args.heads, args.kv_heads, args.head_dim
+    t32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    result = {"kernel": args.kernel}
+
+    if args.kernel == "attention_decode":
+        b, ctx = args.batch, args.context
+        k_pool, v_pool, table = _paged(b, ctx, nkv, hd, dev)
+        q = torch.randn(b, nh * hd, device=dev, dtype=torch.bfloat16)
+        plan = AttentionPlan(n_seqs=b, max_new=1, max_total=ctx, all_single=True, seq_start=t32([ctx - 1] * b),
+                             seq_new=t32([1] * b), cu_new=t32(list(range(b + 1))), seq_total=t32([ctx] * b),
+                             starts=[ctx - 1] * b, news=[1] * b)
+        seqs, pos = t32(list(range(b))), t32([ctx - 1] * b)
+        fn = lambda: ops.attention(q, k_pool, v_pool, seqs, pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0, plan=plan)
+        nbytes = 2 * b * ctx * nkv * hd * 2
+        ms, best = _time(fn, args.iters, flush)
+        result.update(batch=b, context=ctx, bytes=nbytes, ms=ms, best_ms=best, gbs=nbytes / ms / 1e6,
+                      frac_of_hbm=nbytes / ms / 1e6 / hbm)
+    elif args.kernel == "attention_prefill":
+        T = args.tokens
+        k_pool, v_pool, table = _paged(1, T, nkv, hd, dev)
+        q = torch.randn(T, nh * hd, device=dev, dtype=torch.bfloat16)
+        plan = AttentionPlan(n_seqs=1, max_new=T, max_total=T, all_single=False, seq_start=t32([0]), seq_new=t32([T]),
+                             cu_new=t32([0, T]), seq_total=t32([T]), starts=[0], news=[T])
+        seqs, pos = t32([0] * T), t32(list(range(T)))
+        fn = lambda: ops.attention(q, k_pool, v_pool, seqs, pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0, plan=plan)
+        flops = 2 * T * T * nh * hd                        # causal: half of 4 T^2 nh hd
+        ms, best = _time(fn, args.iters, flush)
+        result.update(tokens=T, flops=flops, ms=ms, best_ms=best, tflops=flops / ms / 1e9,
+                      frac_of_bf16_peak=flops / ms / 1e9 / tflops)
+    elif args.kernel == "gemm_skinny":
+        M, N, K = args.rows, args.n, args.k
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn((2 if args.gated else 1) * N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        out_dtype = torch.float32 if args.out_f32 else torch.bfloat16
+        fn = lambda: gemm_skinny.run(x, w, out_dtype, fuse_swiglu=args.gated)
+        nbytes = w.numel() * 2
+        ms, best = _time(fn, args.iters, flush)
+        result.update(rows=M, n=N, k=K, gated=args.gated, bytes=nbytes, ms=ms, best_ms=best, gbs=nbytes / ms / 1e6,
+                      frac_of_hbm=nbytes / ms / 1e6 / hbm)
+        lib_fn = lambda: torch.mm(x, w.t())
+        lib_ms, _ = _time(lib_fn, args.iters, flush)
+        result["library_mm_ms"] = lib_ms
+    elif args.kernel == "norm":
+        rows, width = args.rows, args.width
+        res = torch.randn(rows, width, device=dev)
+        delta = torch.randn(rows, width, device=dev)
+        gain = torch.ones(width, device=dev)
+        fn = lambda: ops.add_rmsnorm(res, delta, gain, 1e-5, torch.bfloat16)
+        ms, best = _time(fn, args.iters, flush)
+        result.update(rows=rows, width=width, ms=ms, best_ms=best)
+    elif args.kernel == "rope":
+        rows = args.rows
+        k_pool, v_pool, table = _paged(rows, 128, nkv, hd, dev)
+        qkv = torch.randn(rows, (nh + 2 * nkv) * hd, device=dev, dtype=torch.bfloat16)
+        cos = torch.rand(256, hd // 2, device=dev)
+        sin = torch.rand(256, hd // 2, device=dev)
+        seqs, pos = t32(list(range(rows))), t32([100] * rows)
+        qd, kvd = nh * hd, nkv * hd
+        fn = lambda: ops.rope_cache_write(qkv[:, :qd], qkv[:, qd:qd + kvd], qkv[:, qd + kvd:], cos, sin, hd, seqs, pos,
+                                          table, k_pool, v_pool, nh, nkv, hd)
+        ms, best = _time(fn, args.iters, flush)
+        result.update(rows=rows, ms=ms, best_ms=best)
+    result["peaks"] = source
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
