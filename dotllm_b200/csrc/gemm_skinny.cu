@@ -225,3 +225,76 @@ extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, v
     DL_CHECK_LAUNCH("gemm_skinny");
     return DL_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same product for callers that must not allocate (declared in gemm_skinny_static.h).
+//
+// dl_gemm_skinny_bf16 above takes its split-k scratch from the caller, who normally gets it from
+// an allocator.  Some callers have no allocator to ask: code that runs between a framework's
+// allocation phases, a host process whose device memory is handed out once at start-up and then
+// frozen, a real-time loop that may not take the allocator's lock.  For them the scratch lives in
+// this library's own image: a file-scope __device__ array of a fixed, modest size that every GPU
+// loading the library holds until the process exits.
+//
+// The array's name is only a host-side handle for the device object; its device address is asked
+// for once per device, with that device current, through cudaGetSymbolAddress.
+#include "gemm_skinny_static.h"
+#include <mutex>
+
+#define GS_STATIC_PARTIAL_FLOATS (DL_GEMM_SKINNY_STATIC_SCRATCH_BYTES / 4 - DL_GEMM_SKINNY_STATIC_MAX_TILES)
+
+struct GsStaticScratch {
+    int counters[DL_GEMM_SKINNY_STATIC_MAX_TILES];
+    float partials[GS_STATIC_PARTIAL_FLOATS];
+};
+static __device__ __align__(256) GsStaticScratch gs_static_scratch;
+
+#define GS_MAX_DEVICES 64
+static GsStaticScratch* gs_static_ptr[GS_MAX_DEVICES];      // device address of the array, per device
+static std::mutex gs_static_mutex;
+
+// The device address of the scratch on the current device (looked up on the first call there).
+static int gs_static_address(GsStaticScratch** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= GS_MAX_DEVICES) return dl_fail(DL_ERR_UNSUPPORTED, "gemm_skinny_static: device %d out of range", dev);
+    std::lock_guard<std::mutex> lock(gs_static_mutex);
+    if (gs_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, gs_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        gs_static_ptr[dev] = static_cast<GsStaticScratch*>(p);
+    }
+    *out = gs_static_ptr[dev];
+    return DL_OK;
+}
+
+extern "C" int dl_gemm_skinny_bf16_static(const void* x, int x_stride, const void* w, void* out, int out_dtype,
+                                          int out_stride, int M, int N, int K, int fuse_swiglu, void* stream) {
+    DL_REQUIRE(M >= 1 && M <= 64 && N > 0 && K > 0, "gemm_skinny_static: bad sizes M=%d N=%d K=%d", M, N, K);
+    int sms = 0, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static: cannot query the device");
+    const int tiles = fuse_swiglu ? (N + 7) / 8 : (N + 15) / 16;
+    const int ksplit = dl_gemm_skinny_splits(tiles, K, sms);
+    const int nt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
+    const size_t need = ksplit > 1 ? (size_t)tiles * ksplit * nt * 128 : 0;
+    if (tiles > DL_GEMM_SKINNY_STATIC_MAX_TILES || need > (size_t)GS_STATIC_PARTIAL_FLOATS)
+        return dl_fail(DL_ERR_UNSUPPORTED,
+                       "gemm_skinny_static: M=%d N=%d K=%d needs %d row tiles and %zu scratch floats; the built-in "
+                       "scratch holds %d tiles and %d floats - use dl_gemm_skinny_bf16 with your own scratch",
+                       M, N, K, tiles, need, DL_GEMM_SKINNY_STATIC_MAX_TILES, (int)GS_STATIC_PARTIAL_FLOATS);
+    GsStaticScratch* scratch = nullptr;
+    const int rc = gs_static_address(&scratch);
+    if (rc != DL_OK) return rc;
+    if (ksplit > 1) {
+        // The array keeps whatever the last call left; the arrival counters must start at zero.
+        cudaError_t e = cudaMemsetAsync(scratch->counters, 0, sizeof(int) * tiles, (cudaStream_t)stream);
+        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static: memset: %s", cudaGetErrorString(e));
+    }
+    return dl_gemm_skinny_bf16(x, x_stride, w, out, out_dtype, out_stride, M, N, K, fuse_swiglu, ksplit,
+                               scratch->partials, scratch->counters, stream);
+}
