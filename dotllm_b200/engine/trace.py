@@ -34,6 +34,12 @@ class TraceReplayer:
         self.out_dir.mkdir(parents=True, exist_ok=True)
         self.sequences = {}
 
+    @staticmethod
+    def check_kernels():
+        """Raise if a kernel gave up on a bounded wait (its result would be wrong)."""
+        from ..kernels import library
+        library.check_status()
+
     def run_step(self, record):
         step_id = record["step"]
         entries = []
@@ -50,6 +56,7 @@ class TraceReplayer:
                 if logits.shape[0] > 0:
                     data = logits.detach().to("cpu").contiguous().numpy().astype("<f4", copy=False)
                     data.tofile(self.out_dir / f"{step_id}.f32")
+                    self.check_kernels()
         except Exception:
             for rid in opened:                      # a refused step leaves no half-opened request
                 self.cache.close_sequence(self.sequences.pop(rid))

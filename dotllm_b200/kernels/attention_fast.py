@@ -13,7 +13,7 @@ from . import library as _library
 _P, _I, _F = _library._P, _library._I, _library._F
 _library.register_signatures({
     "dl_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I,
-                                 _P, _P, _P, _P],
+                                 _P, _P, _P, _P, _P],
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                   _F, _I, _P],
 })
@@ -24,9 +24,12 @@ DECODE_HEAD_DIMS = (32, 64, 96, 128)
 _counters = {}
 
 
-def keys_per_split(longest):
-    """Keys one block streams.  Shorter runs for short caches keep all multiprocessors busy."""
-    return 256 if longest <= 4096 else 512
+def keys_per_split(longest, pairs, sms=148):
+    """Keys one block streams: long runs amortise a block's start-up, but there must be about two
+    blocks per multiprocessor.  ``pairs`` is sequences x KV heads."""
+    want_splits = max(1, (2 * sms + pairs - 1) // pairs)
+    kps = (longest // want_splits) // 64 * 64
+    return max(64, min(512, kps))
 
 
 def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads, head_dim,
@@ -34,7 +37,7 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
     B = plan.n_seqs
     group = n_heads // n_kv_heads
     longest = min(plan.max_total, window + 64) if window else plan.max_total
-    kps = keys_per_split(longest)
+    kps = keys_per_split(longest, B * n_kv_heads)
     max_splits = max(1, (longest + kps - 1) // kps)
     key = ("decode", n_kv_heads, group, head_dim, max_splits)
     if key not in plan.scratch:
@@ -42,7 +45,6 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
             torch.empty(B * n_kv_heads * max_splits * group * head_dim, dtype=torch.float32, device=q.device),
             torch.empty(B * n_kv_heads * max_splits * group * 2, dtype=torch.float32, device=q.device))
     part_o, part_ml = plan.scratch[key]
-    ckey = (q.device.index, B * n_kv_heads)
     counters = _counters.get(q.device.index)
     if counters is None or counters.numel() < B * n_kv_heads:
         counters = torch.zeros(max(4096, B * n_kv_heads), dtype=torch.int32, device=q.device)
@@ -51,7 +53,8 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, plan.seq_total.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim,
                   scale, window, kps, max_splits, part_o.data_ptr(), part_ml.data_ptr(),
-                  counters.data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  counters.data_ptr(), _library.status_word(q.device).data_ptr(),
+                  torch.cuda.current_stream().cuda_stream)
     return True
 
 

@@ -93,3 +93,27 @@ def call(name, *args):
     status = getattr(lib, name)(*args)
     if status != 0:
         raise KernelError(f"{name}: {lib.dl_last_error().decode(errors='replace')} (status {status})")
+
+
+_status = {}
+_STATUS_TEXT = {1: "a producer's wait for a free shared-memory stage expired",
+                2: "a block table named a page outside the pool",
+                3: "a consumer's wait for a bulk copy expired"}
+
+
+def status_word(device):
+    """The per-device int32 that kernels with bounded waits set when a wait expires."""
+    key = device.index
+    if key not in _status:
+        import torch
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status():
+    """Raise if a kernel reported an expired wait since the last check (synchronises)."""
+    for key, word in _status.items():
+        code = int(word.item())
+        if code:
+            word.zero_()
+            raise KernelError(f"a kernel on cuda:{key} gave up: {_STATUS_TEXT.get(code, code)}")

@@ -25,6 +25,13 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
            "fp32": torch.float32, "f32": torch.float32}
 
 
+def _synchronize():
+    """Wait for the device and surface any kernel that gave up on a bounded wait."""
+    from .kernels import library
+    torch.cuda.synchronize()
+    library.check_status()
+
+
 def parse_dtype(dtype):
     if isinstance(dtype, torch.dtype):
         if dtype not in (torch.bfloat16, torch.float32):
@@ -115,7 +122,7 @@ class Model:
         return TextGenerator(lambda entries: self.step(cache, entries, graphs=use_graphs), sample_rows, cache,
                              max_positions=self.spec.max_positions, vocab_size=self.spec.vocab_size,
                              default_stop_ids=self.spec.stop_token_ids, bos_token_id=self.spec.bos_token_id,
-                             max_batch=max_batch, synchronize=torch.cuda.synchronize)
+                             max_batch=max_batch, synchronize=_synchronize)
 
     def generate(self, prompts, options=None, on_token=None, **option_fields):
         """Generate for one prompt (a list of ints) or many.  Options as an InferenceOptions (or
