@@ -1,35 +1,82 @@
 // y = x W^T for a handful of rows of x (decode steps): a weight-streaming product.
 //
-// With M <= 64 rows every projection is bound by the bytes of W, read once.  The reference runs
+// With M <= 16 rows every projection is bound by the bytes of W, read once.  The reference runs
 // these through cuBLAS or one-block-per-output-row GEMV kernels
 // (src/DotLLM.Cuda/CudaTransformerModel.cs:317-349, native/kernels/quantized_gemv.cu:13-63).
-// Here W is the 16-row operand of mma.sync.m16n8k16 and the tokens are its 8 columns, so the
-// tensor cores do the arithmetic while every lane streams 16-byte pieces of W rows straight
-// from global memory into registers: within a 32-wide slice of k, lane (g, t) holds k = 8t..8t+7
-// of rows g and g+8, and the same slice of token g's activations, which is a consistent
-// permutation of k for both operands of two MMAs.  Nothing is staged in shared memory.
+// Here W is the 16-row operand of mma.sync.m16n8k16 and the tokens are its 8 columns: within a
+// 32-wide slice of k, lane (g, t) holds k = 8t..8t+7 of rows g and g+8 and the same slice of token
+// g's activations, which is a consistent permutation of k for both operands of two MMAs.
 //
-// A block of 4 warps owns one 16-row tile and a contiguous range of k; its warps take
-// 32-wide slices in turn and their partial sums are added in a fixed order.  When a tile's k is
-// split over several blocks, each writes its partial to scratch and the last one to arrive adds
-// them, again in a fixed order, so the result is deterministic and the same for any number of
-// rows of x.  With FUSE_SWIGLU the tile's rows 0-7 are gate rows and rows 8-15 the matching up
-// rows, and the epilogue writes silu(gate) * up (native/kernels/swiglu.cu:7-41).
+// Shape: persistent, warp-specialised, stream-K.  The work is the list of (16-row tile, 256-wide
+// chunk of k) pairs in tile-major order, cut into equal contiguous shares, one per consumer warp of
+// the whole grid, so every warp streams the same number of bytes whatever N and K are.  One producer
+// warp per block copies chunks with cp.async.bulk (16 row pieces of 512 bytes) into a private ring
+// of shared-memory stages for each consumer warp, signalling an mbarrier per stage; copies run ahead
+// of the arithmetic by the depth of the ring.  A consumer never synchronises with another warp of
+// its block.  A tile that lies wholly inside one share is finished by that warp; a tile cut between
+// shares is summed, in share order, by whichever of its warps arrives last, so the result is
+// deterministic and does not depend on the number of rows of x.  With FUSE_SWIGLU a tile's rows
+// 0-7 are gate rows and rows 8-15 the matching up rows, and the epilogue writes silu(gate) * up
+// (native/kernels/swiglu.cu:7-41).
+//
+// Every wait on an mbarrier is bounded (about a second of clock cycles); on expiry the kernel records
+// a code in `status` and returns after waiting (bounded) for copies in flight.
 #include "common.cuh"
+#include "tma.cuh"
+#include <mutex>
+#include <unordered_map>
 
-#define GS_WARPS 4
+#define GS_CONSUMERS 6
+#define GS_SLOTS 4                         // ring stages per consumer warp
+#define GS_BK 256                          // k per chunk
+#define GS_STAGE_ELEMS (16 * GS_BK)         // a stage is the dense box the copy engine writes: [16 rows][256 k]
+#define GS_THREADS (32 * (GS_CONSUMERS + 1))
+#define GS_WAIT_CYCLES (1ll << 31)
+#define GS_MAX_ROWS 16
 
 __device__ __forceinline__ void gs_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                        uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 gs_load16(const __nv_bfloat16* p, bool ok) {
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (ok) v = __ldg(reinterpret_cast<const uint4*>(p));
+__device__ __forceinline__ uint32_t gs_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gs_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gs_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void gs_mbar_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(gs_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gs_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gs_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool gs_mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(gs_smem(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool gs_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* gave_up) {
+    if (gs_mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!gs_mbar_try(bar, parity)) {
+        if (*gave_up || clock64() - t0 > GS_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void gs_bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(gs_smem(dst)),
+                 "l"(src), "r"(bytes), "r"(gs_smem(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ uint4 gs_lds128(uint32_t addr) {     // 16 bytes from a shared-space byte address
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
     return v;
 }
 
@@ -39,109 +86,23 @@ template <> __device__ __forceinline__ void gs_store<__nv_bfloat16>(__nv_bfloat1
     *p = __float2bfloat16_rn(v);
 }
 
-template <int NT, typename TOut, bool FUSE_SWIGLU>
-__global__ void __launch_bounds__(32 * GS_WARPS)
-gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ w,
-                   TOut* __restrict__ out, int out_stride, int M, int N, int K, int up_offset,
-                   int chunks_per_block, float* __restrict__ partials, int* __restrict__ counters) {
-    __shared__ float red[GS_WARPS][NT * 4][32];
-    __shared__ int is_last;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int tile = blockIdx.x, split = blockIdx.y, ksplit = gridDim.y;
-
-    // rows of W behind fragment rows g and g+8
-    int row_lo, row_hi;
-    bool ok_lo, ok_hi;
+// Row of W behind fragment row r (0..15) of a tile, and whether it exists.
+template <bool FUSE_SWIGLU>
+__device__ __forceinline__ int gs_row(int tile, int r, int N, int up_offset, bool* ok) {
     if (FUSE_SWIGLU) {
-        row_lo = tile * 8 + g;                 // gate row i
-        row_hi = up_offset + tile * 8 + g;     // up row i
-        ok_lo = ok_hi = (tile * 8 + g) < N;
-    } else {
-        row_lo = tile * 16 + g;
-        row_hi = row_lo + 8;
-        ok_lo = row_lo < N;
-        ok_hi = row_hi < N;
+        const int i = tile * 8 + (r & 7);
+        *ok = i < N;
+        return r < 8 ? i : up_offset + i;
     }
-    const __nv_bfloat16* w_lo = w + (size_t)row_lo * K;
-    const __nv_bfloat16* w_hi = w + (size_t)row_hi * K;
+    const int row = tile * 16 + r;
+    *ok = row < N;
+    return row;
+}
 
-    float acc[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-
-    const int n_chunks = (K + 31) / 32;
-    const int c_begin = split * chunks_per_block;
-    const int c_end = min(n_chunks, c_begin + chunks_per_block);
-#pragma unroll 4
-    for (int c = c_begin + warp; c < c_end; c += GS_WARPS) {
-        const int k = c * 32 + t * 8;
-        const bool k_ok = k < K;               // K is a multiple of 8
-        const uint4 a_lo = gs_load16(w_lo + k, ok_lo && k_ok);
-        const uint4 a_hi = gs_load16(w_hi + k, ok_hi && k_ok);
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const int tok = j * 8 + g;
-            const uint4 b = gs_load16(x + (size_t)tok * x_stride + k, tok < M && k_ok);
-            gs_mma(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-            gs_mma(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
-        }
-    }
-
-    // add the block's warps in a fixed order
-#pragma unroll
-    for (int j = 0; j < NT; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) red[warp][j * 4 + e][lane] = acc[j][e];
-    __syncthreads();
-    if (warp != 0) {
-        // warps 1.. only help when the tile is split over blocks (they wait at the barrier below)
-    } else {
-#pragma unroll
-        for (int j = 0; j < NT; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float s = red[0][j * 4 + e][lane];
-#pragma unroll
-                for (int ww = 1; ww < GS_WARPS; ++ww) s += red[ww][j * 4 + e][lane];
-                acc[j][e] = s;
-            }
-    }
-
-    if (ksplit > 1) {
-        float* mine = partials + ((size_t)tile * ksplit + split) * (NT * 4 * 32);
-        if (warp == 0) {
-#pragma unroll
-            for (int j = 0; j < NT; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) mine[(j * 4 + e) * 32 + lane] = acc[j][e];
-            __threadfence();
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const int seen = atomicAdd(&counters[tile], 1);
-            is_last = (seen == ksplit - 1);
-            if (is_last) counters[tile] = 0;        // ready for the next launch
-        }
-        __syncthreads();
-        if (!is_last || warp != 0) return;
-        __threadfence();
-        const float* all = partials + (size_t)tile * ksplit * (NT * 4 * 32);
-#pragma unroll
-        for (int j = 0; j < NT; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float s = 0.f;
-                for (int sp = 0; sp < ksplit; ++sp) s += __ldcg(all + (size_t)sp * (NT * 4 * 32) + (j * 4 + e) * 32 + lane);
-                acc[j][e] = s;
-            }
-    } else if (warp != 0) {
-        return;
-    }
-
-    // epilogue: acc[j] = {(row g, tok 2t), (row g, tok 2t+1), (row g+8, tok 2t), (row g+8, tok 2t+1)}
+// acc[j] = {(row g, tok 2t), (row g, tok 2t+1), (row g+8, tok 2t), (row g+8, tok 2t+1)} of 8-token group j
+template <int NT, typename TOut, bool FUSE_SWIGLU>
+__device__ __forceinline__ void gs_epilogue(const float (&acc)[NT][4], TOut* out, int out_stride, int tile, int M,
+                                            int N, int g, int t) {
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         const int tok0 = j * 8 + 2 * t;
@@ -153,11 +114,12 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, const __nv
                 if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + col, g1 * (1.0f / (1.0f + expf(-g1))) * acc[j][3]);
             }
         } else {
-            if (ok_lo) {
+            const int row_lo = tile * 16 + g, row_hi = row_lo + 8;
+            if (row_lo < N) {
                 if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + row_lo, acc[j][0]);
                 if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + row_lo, acc[j][1]);
             }
-            if (ok_hi) {
+            if (row_hi < N) {
                 if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + row_hi, acc[j][2]);
                 if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + row_hi, acc[j][3]);
             }
@@ -165,72 +127,290 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, const __nv
     }
 }
 
+template <int NT, typename TOut, bool FUSE_SWIGLU>
+__global__ void __launch_bounds__(GS_THREADS, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const __nv_bfloat16* __restrict__ x, int x_stride,
+                   TOut* __restrict__ out, int out_stride, int M, int N, int K, int up_offset, int cpt,
+                   int total_chunks, int share, float* __restrict__ partials, int* __restrict__ counters,
+                   int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char gs_smem_raw[];
+    __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(gs_smem_raw);   // [consumer][slot][16][GS_PITCH]
+    __shared__ uint64_t full_bar[GS_CONSUMERS][GS_SLOTS], empty_bar[GS_CONSUMERS][GS_SLOTS];
+    __shared__ volatile int gave_up;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int c = 0; c < GS_CONSUMERS; ++c)
+            for (int s = 0; s < GS_SLOTS; ++s) {
+                gs_mbar_init(&full_bar[c][s], 1);
+                gs_mbar_init(&empty_bar[c][s], 1);
+            }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == GS_CONSUMERS) {
+        // ------------------------------------------------------------ producer warp
+        // Lane c (< GS_CONSUMERS) feeds consumer c: it walks that warp's share chunk by chunk, waits for
+        // the ring slot to be free, and issues one tiled copy (two for gate + up) per chunk.
+        if (lane < GS_CONSUMERS) {
+            const int gw = blockIdx.x * GS_CONSUMERS + lane;
+            int cur = min(total_chunks, gw * share);
+            const int end = min(total_chunks, (gw + 1) * share);
+            int cnt = 0;
+            bool stop = false;
+            for (; cur < end && !stop; ++cur, ++cnt) {
+                const int slot = cnt % GS_SLOTS;
+                if (cnt >= GS_SLOTS && !gs_mbar_wait(&empty_bar[lane][slot], ((cnt / GS_SLOTS) - 1) & 1, &gave_up)) {
+                    if (!gave_up) atomicExch(status, 1);
+                    gave_up = 1;
+                    stop = true;
+                    break;
+                }
+                const int tile = cur / cpt, kc = cur - tile * cpt;
+                __nv_bfloat16* dst = stage_mem + (size_t)(lane * GS_SLOTS + slot) * GS_STAGE_ELEMS;
+                // a box is always written whole: parts outside the matrix arrive as zeros
+                gs_mbar_expect(&full_bar[lane][slot], GS_STAGE_ELEMS * 2);
+                if (FUSE_SWIGLU) {
+                    dl_tma_load_2d(dst, &tmap, kc * GS_BK, tile * 8, &full_bar[lane][slot]);
+                    dl_tma_load_2d(dst + 8 * GS_BK, &tmap, kc * GS_BK, up_offset + tile * 8, &full_bar[lane][slot]);
+                } else {
+                    dl_tma_load_2d(dst, &tmap, kc * GS_BK, tile * 16, &full_bar[lane][slot]);
+                }
+            }
+            if (stop) {
+                // copies already issued must land before the block's shared memory is released
+                for (int i = max(0, cnt - GS_SLOTS); i < cnt; ++i) {
+                    const long long t0 = clock64();
+                    while (!gs_mbar_try(&full_bar[lane][i % GS_SLOTS], (i / GS_SLOTS) & 1) && clock64() - t0 < GS_WAIT_CYCLES) {}
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ consumer warp
+        const int g = lane >> 2, t = lane & 3;
+        const int gw = blockIdx.x * GS_CONSUMERS + warp;
+        const int begin = min(total_chunks, gw * share), end = min(total_chunks, (gw + 1) * share);
+        float acc[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+        int seg_begin = begin;                               // first chunk of the current tile's segment
+        bool dead = false;
+        for (int cur = begin; cur < end; ++cur) {
+            const int cnt = cur - begin, slot = cnt % GS_SLOTS;
+            const int tile = cur / cpt, kc = cur - tile * cpt;
+            const int k0 = kc * GS_BK;
+            // activations of this chunk, asked for before waiting on the weights
+            uint4 xf[GS_BK / 32][NT];
+#pragma unroll
+            for (int s = 0; s < GS_BK / 32; ++s)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const int tok = j * 8 + g, k = k0 + 32 * s + 8 * t;
+                    xf[s][j] = make_uint4(0u, 0u, 0u, 0u);
+                    if (tok < M && k < K) xf[s][j] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)tok * x_stride + k));
+                }
+            if (!dead && !gs_mbar_wait(&full_bar[warp][slot], (cnt / GS_SLOTS) & 1, &gave_up)) {
+                if (!gave_up) atomicExch(status, 3);
+                gave_up = 1;
+                dead = true;
+            }
+            if (!dead) {
+                // this lane's byte address in shared space; the loads below are constant offsets away.
+                // Rows beyond the matrix and k beyond K arrived as zeros, so nothing needs guarding.
+                const uint32_t st = gs_smem(stage_mem + (size_t)(warp * GS_SLOTS + slot) * GS_STAGE_ELEMS) +
+                                    (uint32_t)(g * GS_BK + 8 * t) * 2u;
+#pragma unroll
+                for (int s = 0; s < GS_BK / 32; ++s) {
+                    const uint4 a_lo = gs_lds128(st + (uint32_t)(32 * s * 2));
+                    const uint4 a_hi = gs_lds128(st + (uint32_t)((8 * GS_BK + 32 * s) * 2));
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        gs_mma(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, xf[s][j].x, xf[s][j].y);
+                        gs_mma(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, xf[s][j].z, xf[s][j].w);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) gs_mbar_arrive(&empty_bar[warp][slot]);
+            }
+            if (kc == cpt - 1 || cur == end - 1) {
+                // ---- the segment [seg_begin, cur] of this tile is done
+                const bool whole = (seg_begin == tile * cpt) && (kc == cpt - 1);
+                if (whole) {
+                    gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, out_stride, tile, M, N, g, t);
+                } else {
+                    // a warp's first tile may be shared with the share before, its last with the share after
+                    const int which = (tile == begin / cpt) ? 0 : 1;
+                    float* mine = partials + ((size_t)gw * 2 + which) * (NT * 4 * 32);
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) mine[(j * 4 + e) * 32 + lane] = acc[j][e];
+                    __syncwarp();
+                    const int g_lo = (tile * cpt) / share, g_hi = ((tile + 1) * cpt - 1) / share;
+                    int last = 0;
+                    if (lane == 0) {
+                        __threadfence();
+                        const int seen = atomicAdd(&counters[tile], 1);
+                        last = (seen == g_hi - g_lo) ? 1 : 0;
+                        if (last) {
+                            counters[tile] = 0;              // ready for the next launch
+                            __threadfence();
+                        }
+                    }
+                    last = __shfl_sync(0xffffffffu, last, 0);
+                    if (last) {
+#pragma unroll
+                        for (int j = 0; j < NT; ++j)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+                        for (int gg = g_lo; gg <= g_hi; ++gg) {          // share order: fixed
+                            const int wh = (tile == (gg * share) / cpt) ? 0 : 1;
+                            const float* theirs = partials + ((size_t)gg * 2 + wh) * (NT * 4 * 32);
+#pragma unroll
+                            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) acc[j][e] += __ldcg(theirs + (j * 4 + e) * 32 + lane);
+                        }
+                        gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, out_stride, tile, M, N, g, t);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+                seg_begin = cur + 1;
+            }
+        }
+    }
+    __syncthreads();                                         // nobody leaves while copies may still land
+}
+
+// How the work of an (N, K) matrix is cut: tiles of 16 rows (8 gate + 8 up when gated), chunks per
+// tile, blocks, chunks per consumer warp.  Depends on the matrix and the device only, never on M.
+struct GsPlan {
+    int tiles, cpt, total, blocks, share;
+};
+
+static GsPlan gs_plan(int N, int K, int fuse_swiglu, int sms) {
+    GsPlan p;
+    p.tiles = fuse_swiglu ? (N + 7) / 8 : (N + 15) / 16;
+    p.cpt = (K + GS_BK - 1) / GS_BK;
+    p.total = p.tiles * p.cpt;
+    const int per_block = GS_CONSUMERS * 4;                  // at least about four chunks per warp
+    p.blocks = (p.total + per_block - 1) / per_block;
+    if (p.blocks > sms) p.blocks = sms;
+    if (p.blocks < 1) p.blocks = 1;
+    const int warps = p.blocks * GS_CONSUMERS;
+    p.share = (p.total + warps - 1) / warps;
+    return p;
+}
+
+// Scratch the product needs: float32 partial sums and int32 arrival counters (zero before the first
+// launch; every launch leaves them zero).
+extern "C" int dl_gemm_skinny_scratch(int M, int N, int K, int fuse_swiglu, int sms, int* partial_floats,
+                                      int* n_counters) {
+    const GsPlan p = gs_plan(N, K, fuse_swiglu, sms);
+    const int nt = M <= 8 ? 1 : 2;
+    *partial_floats = p.blocks * GS_CONSUMERS * 2 * nt * 4 * 32;
+    *n_counters = p.tiles;
+    return DL_OK;
+}
+
 template <int NT, typename TOut, bool FUSE>
-static void gs_launch(dim3 grid, cudaStream_t s, const __nv_bfloat16* x, int x_stride, const __nv_bfloat16* w,
-                      void* out, int out_stride, int M, int N, int K, int up_offset, int cpb, float* partials,
-                      int* counters) {
-    gemm_skinny_kernel<NT, TOut, FUSE><<<grid, 32 * GS_WARPS, 0, s>>>(x, x_stride, w, (TOut*)out, out_stride, M, N,
-                                                                     K, up_offset, cpb, partials, counters);
+static int gs_launch(const GsPlan& p, cudaStream_t s, const __nv_bfloat16* x, int x_stride, const __nv_bfloat16* w,
+                     void* out, int out_stride, int M, int N, int K, int up_offset, float* partials, int* counters,
+                     int* status) {
+    const size_t smem = (size_t)GS_CONSUMERS * GS_SLOTS * GS_STAGE_ELEMS * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NT, TOut, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    // Tensor map of W: rows of K bfloat16, boxes of 16 rows (8 for gate + up) by 256 columns.  Encoding
+    // costs a driver call, so maps are kept per (matrix, shape).
+    struct Key {
+        const void* w;
+        int rows, k, box;
+        bool operator==(const Key& o) const { return w == o.w && rows == o.rows && k == o.k && box == o.box; }
+    };
+    struct KeyHash {
+        size_t operator()(const Key& k) const {
+            return std::hash<const void*>()(k.w) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.k * 10007u) ^ (size_t)k.box;
+        }
+    };
+    static std::unordered_map<Key, CUtensorMap, KeyHash> maps;
+    static std::mutex maps_mutex;
+    const int rows = FUSE ? 2 * N : N, box = FUSE ? 8 : 16;
+    CUtensorMap tmap;
+    {
+        std::lock_guard<std::mutex> lock(maps_mutex);
+        const Key key{(const void*)w, rows, K, box};
+        auto it = maps.find(key);
+        if (it == maps.end()) {
+            CUtensorMap fresh;
+            if (dl_tmap_encode_2d_bf16(&fresh, w, (uint64_t)rows, (uint64_t)K, (uint64_t)K * 2, box, GS_BK, DL_TMAP_SWIZZLE_NONE) != 0)
+                return DL_ERR_LAUNCH;
+            if (maps.size() > 4096) maps.clear();
+            it = maps.emplace(key, fresh).first;
+        }
+        tmap = it->second;
+    }
+    gemm_skinny_kernel<NT, TOut, FUSE><<<p.blocks, GS_THREADS, smem, s>>>(tmap, x, x_stride, (TOut*)out, out_stride, M, N, K,
+                                                                          up_offset, p.cpt, p.total, p.share, partials,
+                                                                          counters, status);
+    DL_CHECK_LAUNCH("gemm_skinny");
+    return DL_OK;
 }
 
-// Number of k-splits this kernel uses for (tiles, K) on a device with `sms` multiprocessors.
-// It depends on the weight's shape only, never on the number of rows of x.
-extern "C" int dl_gemm_skinny_splits(int tiles, int K, int sms) {
-    const int n_chunks = (K + 31) / 32;
-    const int target = sms * 8;                              // blocks wanted in flight
-    int ksplit = (target + tiles - 1) / tiles;
-    const int max_split = n_chunks / (GS_WARPS * 4) > 1 ? n_chunks / (GS_WARPS * 4) : 1;
-    if (ksplit > max_split) ksplit = max_split;
-    if (ksplit < 1) ksplit = 1;
-    if (ksplit > 16) ksplit = 16;
-    return ksplit;
-}
-
-// x: bf16 [M, K] rows x_stride apart, M <= 64.  w: bf16, contiguous rows of K.
+// x: bf16 [M, K] rows x_stride apart, M <= 16.  w: bf16, contiguous rows of K.
 // fuse_swiglu == 0: w is [N, K], out [M, N].  fuse_swiglu == 1: w is [2N, K] (N gate rows, then N
 // up rows), out [M, N] = silu(x Wg^T) * (x Wu^T).
-// partials: float32 scratch of at least tiles * ksplit * nt * 128 floats when ksplit > 1
-// (nt = number of 8-token groups rounded up to 1, 2, 4 or 8); counters: int32, zero, >= tiles.
+// partials / counters: scratch of the sizes dl_gemm_skinny_scratch gives; status: int32, set
+// non-zero if a wait expired.
 extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype,
-                                   int out_stride, int M, int N, int K, int fuse_swiglu, int ksplit,
-                                   float* partials, int* counters, void* stream) {
-    DL_REQUIRE(M >= 1 && M <= 64, "gemm_skinny: takes 1 to 64 rows, got %d", M);
+                                   int out_stride, int M, int N, int K, int fuse_swiglu, float* partials,
+                                   int partial_floats, int* counters, int n_counters, int* status, void* stream) {
+    DL_REQUIRE(M >= 1 && M <= GS_MAX_ROWS, "gemm_skinny: takes 1 to %d rows, got %d", GS_MAX_ROWS, M);
     DL_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gemm_skinny: K=%d must be a positive multiple of 8", K);
     DL_REQUIRE(x_stride % 8 == 0 && x_stride >= K, "gemm_skinny: row stride of x (%d) must be a multiple of 8", x_stride);
     DL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_skinny: x and W must be 16-byte aligned");
     DL_REQUIRE(out_stride >= N, "gemm_skinny: out stride shorter than N");
     DL_REQUIRE(out_dtype == DL_F32 || out_dtype == DL_BF16, "gemm_skinny: out dtype %d", out_dtype);
-    const int tiles = fuse_swiglu ? (N + 7) / 8 : (N + 15) / 16;
-    DL_REQUIRE(ksplit >= 1 && ksplit <= 16, "gemm_skinny: ksplit %d", ksplit);
-    DL_REQUIRE(ksplit == 1 || (partials && counters), "gemm_skinny: split k needs scratch");
-    const int n_chunks = (K + 31) / 32;
-    const int cpb = (n_chunks + ksplit - 1) / ksplit;
-    dim3 grid(tiles, ksplit);
+    DL_REQUIRE(status != nullptr && partials != nullptr && counters != nullptr, "gemm_skinny: needs scratch and a status word");
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return dl_fail(DL_ERR_LAUNCH, "gemm_skinny: cannot query the device");
+    const GsPlan p = gs_plan(N, K, fuse_swiglu, sms);
+    const int nt = M <= 8 ? 1 : 2;
+    DL_REQUIRE(partial_floats >= p.blocks * GS_CONSUMERS * 2 * nt * 4 * 32 && n_counters >= p.tiles,
+               "gemm_skinny: scratch too small (%d floats, %d counters)", partial_floats, n_counters);
     cudaStream_t s = (cudaStream_t)stream;
     const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
-    const int nt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
-#define GS_CASE(NTV)                                                                                                \
-    if (nt == NTV) {                                                                                                \
-        if (fuse_swiglu) {                                                                                          \
-            if (out_dtype == DL_F32) gs_launch<NTV, float, true>(grid, s, xb, x_stride, wb, out, out_stride, M, N, K, N, cpb, partials, counters); \
-            else gs_launch<NTV, __nv_bfloat16, true>(grid, s, xb, x_stride, wb, out, out_stride, M, N, K, N, cpb, partials, counters);             \
-        } else {                                                                                                    \
-            if (out_dtype == DL_F32) gs_launch<NTV, float, false>(grid, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, cpb, partials, counters); \
-            else gs_launch<NTV, __nv_bfloat16, false>(grid, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, cpb, partials, counters);             \
-        }                                                                                                           \
+#define GS_CASE(NTV)                                                                                                   \
+    if (nt == NTV) {                                                                                                   \
+        if (fuse_swiglu) {                                                                                             \
+            if (out_dtype == DL_F32) return gs_launch<NTV, float, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, partials, counters, status); \
+            return gs_launch<NTV, __nv_bfloat16, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, partials, counters, status);                \
+        }                                                                                                              \
+        if (out_dtype == DL_F32) return gs_launch<NTV, float, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, partials, counters, status);    \
+        return gs_launch<NTV, __nv_bfloat16, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, partials, counters, status);                   \
     }
-    GS_CASE(1) GS_CASE(2) GS_CASE(4) GS_CASE(8)
+    GS_CASE(1) GS_CASE(2)
 #undef GS_CASE
-    DL_CHECK_LAUNCH("gemm_skinny");
-    return DL_OK;
+    return dl_fail(DL_ERR_UNSUPPORTED, "gemm_skinny: %d rows", M);
 }
 
 // ---------------------------------------------------------------------------------------------
 // The same product for callers that must not allocate (declared in gemm_skinny_static.h).
 //
-// dl_gemm_skinny_bf16 above takes its split-k scratch from the caller, who normally gets it from
-// an allocator.  Some callers have no allocator to ask: code that runs between a framework's
+// dl_gemm_skinny_bf16 above takes its scratch from the caller, who normally gets it from an
+// allocator.  Some callers have no allocator to ask: code that runs between a framework's
 // allocation phases, a host process whose device memory is handed out once at start-up and then
 // frozen, a real-time loop that may not take the allocator's lock.  For them the scratch lives in
 // this library's own image: a file-scope __device__ array of a fixed, modest size that every GPU
@@ -239,11 +419,12 @@ extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, v
 // The array's name is only a host-side handle for the device object; its device address is asked
 // for once per device, with that device current, through cudaGetSymbolAddress.
 #include "gemm_skinny_static.h"
-#include <mutex>
 
-#define GS_STATIC_PARTIAL_FLOATS (DL_GEMM_SKINNY_STATIC_SCRATCH_BYTES / 4 - DL_GEMM_SKINNY_STATIC_MAX_TILES)
+#define GS_STATIC_PARTIAL_FLOATS ((DL_GEMM_SKINNY_STATIC_SCRATCH_BYTES - 256) / 4 - DL_GEMM_SKINNY_STATIC_MAX_TILES)
 
 struct GsStaticScratch {
+    int status;
+    int pad[63];
     int counters[DL_GEMM_SKINNY_STATIC_MAX_TILES];
     float partials[GS_STATIC_PARTIAL_FLOATS];
 };
@@ -273,28 +454,25 @@ static int gs_static_address(GsStaticScratch** out) {
 
 extern "C" int dl_gemm_skinny_bf16_static(const void* x, int x_stride, const void* w, void* out, int out_dtype,
                                           int out_stride, int M, int N, int K, int fuse_swiglu, void* stream) {
-    DL_REQUIRE(M >= 1 && M <= 64 && N > 0 && K > 0, "gemm_skinny_static: bad sizes M=%d N=%d K=%d", M, N, K);
+    DL_REQUIRE(M >= 1 && M <= GS_MAX_ROWS && N > 0 && K > 0, "gemm_skinny_static: bad sizes M=%d N=%d K=%d (1 to %d rows)", M, N,
+               K, GS_MAX_ROWS);
     int sms = 0, dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static: cannot query the device");
-    const int tiles = fuse_swiglu ? (N + 7) / 8 : (N + 15) / 16;
-    const int ksplit = dl_gemm_skinny_splits(tiles, K, sms);
-    const int nt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
-    const size_t need = ksplit > 1 ? (size_t)tiles * ksplit * nt * 128 : 0;
-    if (tiles > DL_GEMM_SKINNY_STATIC_MAX_TILES || need > (size_t)GS_STATIC_PARTIAL_FLOATS)
+    int need_floats = 0, need_counters = 0;
+    dl_gemm_skinny_scratch(M, N, K, fuse_swiglu, sms, &need_floats, &need_counters);
+    if (need_counters > DL_GEMM_SKINNY_STATIC_MAX_TILES || need_floats > (int)GS_STATIC_PARTIAL_FLOATS)
         return dl_fail(DL_ERR_UNSUPPORTED,
-                       "gemm_skinny_static: M=%d N=%d K=%d needs %d row tiles and %zu scratch floats; the built-in "
+                       "gemm_skinny_static: M=%d N=%d K=%d needs %d row tiles and %d scratch floats; the built-in "
                        "scratch holds %d tiles and %d floats - use dl_gemm_skinny_bf16 with your own scratch",
-                       M, N, K, tiles, need, DL_GEMM_SKINNY_STATIC_MAX_TILES, (int)GS_STATIC_PARTIAL_FLOATS);
+                       M, N, K, need_counters, need_floats, DL_GEMM_SKINNY_STATIC_MAX_TILES, (int)GS_STATIC_PARTIAL_FLOATS);
     GsStaticScratch* scratch = nullptr;
     const int rc = gs_static_address(&scratch);
     if (rc != DL_OK) return rc;
-    if (ksplit > 1) {
-        // The array keeps whatever the last call left; the arrival counters must start at zero.
-        cudaError_t e = cudaMemsetAsync(scratch->counters, 0, sizeof(int) * tiles, (cudaStream_t)stream);
-        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static: memset: %s", cudaGetErrorString(e));
-    }
-    return dl_gemm_skinny_bf16(x, x_stride, w, out, out_dtype, out_stride, M, N, K, fuse_swiglu, ksplit,
-                               scratch->partials, scratch->counters, stream);
+    // The array keeps whatever the last call left; the arrival counters must start at zero.
+    cudaError_t e = cudaMemsetAsync(scratch->counters, 0, sizeof(int) * need_counters, (cudaStream_t)stream);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static: memset: %s", cudaGetErrorString(e));
+    return dl_gemm_skinny_bf16(x, x_stride, w, out, out_dtype, out_stride, M, N, K, fuse_swiglu, scratch->partials,
+                               need_floats, scratch->counters, need_counters, &scratch->status, stream);
 }

@@ -21,7 +21,7 @@ extern "C" {
 // the same arithmetic, in the same order, as dl_gemm_skinny_bf16, with the split-k scratch taken
 // from a fixed array inside the library instead of from the caller.
 //
-//   x    bfloat16 [M, K], rows x_stride elements apart, 1 <= M <= 64, K a multiple of 8
+//   x    bfloat16 [M, K], rows x_stride elements apart, 1 <= M <= 16, K a multiple of 8
 //   w    bfloat16, contiguous rows of K
 //   out  [M, N] rows out_stride apart; out_dtype 0 = float32, 1 = bfloat16
 //

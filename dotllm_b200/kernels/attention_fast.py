@@ -13,23 +13,42 @@ from . import library as _library
 _P, _I, _F = _library._P, _library._I, _library._F
 _library.register_signatures({
     "dl_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I,
-                                 _P, _P, _P, _P, _P],
+                                 _P, _P, _P, _P],
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                  _F, _I, _P],
+                                  _F, _I, _P, _P],
 })
 
-PREFILL_ROWS = 64        # query rows per block of the prefill kernel (AP_ROWS)
+PREFILL_ROWS = 128       # query rows per block of the prefill kernel (AP_ROWS)
 
 DECODE_HEAD_DIMS = (32, 64, 96, 128)
-_counters = {}
+RUNS_PER_BLOCK = 0       # > 0: force this many runs per persistent decode block (tuning and tests)
 
 
 def keys_per_split(longest, pairs, sms=148):
-    """Keys one block streams: long runs amortise a block's start-up, but there must be about two
-    blocks per multiprocessor.  ``pairs`` is sequences x KV heads."""
-    want_splits = max(1, (2 * sms + pairs - 1) // pairs)
-    kps = (longest // want_splits) // 64 * 64
-    return max(64, min(512, kps))
+    """Keys in one run of a (sequence, KV head).  The decode kernel is persistent, one block per
+    multiprocessor taking runs in turn: several runs per block even out the load, runs of a few
+    pages keep all of a block's warps busy.  ``pairs`` is sequences x KV heads."""
+    if RUNS_PER_BLOCK:                       # explicit override (tuning and tests)
+        want_splits = max(1, (RUNS_PER_BLOCK * sms + pairs - 1) // pairs)
+        kps = (longest + want_splits - 1) // want_splits
+        return max(128, min(2048, (kps + 63) // 64 * 64))
+    # Cost model: blocks work in rounds of `sms` runs; a run costs its pages plus about three pages'
+    # worth of start-up and merging.  Pick the run length with the cheapest total.
+    best, best_cost = 2048, None
+    pages_total = (longest + 63) // 64
+    for pages in range(2, min(32, pages_total) + 1):
+        n_splits = (pages_total + pages - 1) // pages
+        rounds = (pairs * n_splits + sms - 1) // sms
+        cost = rounds * (pages + 3)
+        if best_cost is None or cost < best_cost or (cost == best_cost and pages * 64 > best):
+            best, best_cost = pages * 64, cost
+    return best
+
+
+def decode_fits(group, head_dim):
+    """Whether at least two ring stages and the merge buffers of the decode kernel fit in shared
+    memory (it takes up to six stages when they fit)."""
+    return 2 * 2 * 64 * head_dim * 2 + 4 * group * (head_dim + 4) * 4 + 4096 <= 227 * 1024
 
 
 def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads, head_dim,
@@ -45,16 +64,11 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
             torch.empty(B * n_kv_heads * max_splits * group * head_dim, dtype=torch.float32, device=q.device),
             torch.empty(B * n_kv_heads * max_splits * group * 2, dtype=torch.float32, device=q.device))
     part_o, part_ml = plan.scratch[key]
-    counters = _counters.get(q.device.index)
-    if counters is None or counters.numel() < B * n_kv_heads:
-        counters = torch.zeros(max(4096, B * n_kv_heads), dtype=torch.int32, device=q.device)
-        _counters[q.device.index] = counters
     _library.call("dl_attention_decode_bf16", q.data_ptr(), q_stride, out.data_ptr(), out.stride(0),
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, plan.seq_total.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim,
                   scale, window, kps, max_splits, part_o.data_ptr(), part_ml.data_ptr(),
-                  counters.data_ptr(), _library.status_word(q.device).data_ptr(),
-                  torch.cuda.current_stream().cuda_stream)
+                  _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     return True
 
 
@@ -74,7 +88,7 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),
                   n_tiles, plan.seq_start.data_ptr(), plan.seq_new.data_ptr(), plan.cu_new.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], n_heads, n_kv_heads, head_dim, scale, window,
-                  torch.cuda.current_stream().cuda_stream)
+                  _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     return True
 
 
@@ -85,7 +99,7 @@ def run(q, q_stride, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_t
     if q.dtype != torch.bfloat16 or q_stride % 8 or q.data_ptr() % 16 or head_dim not in DECODE_HEAD_DIMS:
         return False
     if plan.all_single and q.shape[0] == plan.n_seqs:
-        if n_heads // n_kv_heads > 16:
+        if n_heads // n_kv_heads > 16 or not decode_fits(n_heads // n_kv_heads, head_dim):
             return False
         return _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads,
                        head_dim, scale, window, plan)

@@ -28,6 +28,10 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # --use_fast_math is left off on purpose: softmax, norms and sampling use exact expf/sqrtf.
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=default"]
+# Extra compiler flags for debugging builds, e.g. DOTLLM_NVCC_EXTRA="-DDL_SELF_CHECK=1" makes the
+# kernels that support it verify their own shared-memory addresses and record a status code
+# instead of touching memory outside their buffers.
+NVCC_FLAGS += os.environ.get("DOTLLM_NVCC_EXTRA", "").split()
 
 
 def _log(msg):

@@ -1,10 +1,12 @@
 """Dispatch to the weight-streaming product for steps of a few rows (decode).
 
-The kernel splits k over blocks for matrices with few rows and adds the partial sums through a
-scratch buffer; the per-device counter array it synchronises on is kept here.  Launches that
-share the counters must be on one stream.
+The kernel cuts its work into equal shares per warp; tiles that straddle two shares are summed
+through a scratch buffer with arrival counters.  Both are kept here per device (they are small
+and every launch leaves the counters zero).  Launches that share them must be on one stream.
 """
 from __future__ import annotations
+
+import ctypes
 
 import torch
 
@@ -12,29 +14,31 @@ from . import library as _library
 
 _P, _I = _library._P, _library._I
 _library.register_signatures({
-    "dl_gemm_skinny_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
-    "dl_gemm_skinny_splits": [_I, _I, _I],
+    "dl_gemm_skinny_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P],
+    "dl_gemm_skinny_scratch": [_I, _I, _I, _I, _I, _P, _P],
 })
 
-MAX_ROWS = 16            # beyond this the library product is used
+MAX_ROWS = 16            # rows the kernel takes; beyond this the library product is used
 _MAX_TILES = 1 << 16
-_counters = {}
-_sms = {}
+_state = {}
 
 
 def _device_state(device):
     key = device.index
-    if key not in _counters:
-        _counters[key] = torch.zeros(_MAX_TILES, dtype=torch.int32, device=device)
-        _sms[key] = _library.library().dl_sm_count()
-    return _counters[key], _sms[key]
+    if key not in _state:
+        sms = _library.library().dl_sm_count()
+        counters = torch.zeros(_MAX_TILES, dtype=torch.int32, device=device)
+        partials = torch.empty(max(sms, 1) * 6 * 2 * 2 * 128, dtype=torch.float32, device=device)
+        _state[key] = (counters, partials, sms)
+    return _state[key]
 
 
 def takes(x, w, fuse_swiglu=False, max_rows=None):
     M, K = x.shape
     n_out = w.shape[0] // 2 if fuse_swiglu else w.shape[0]
     tiles = (n_out + 7) // 8 if fuse_swiglu else (n_out + 15) // 16
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 <= M <= (max_rows or MAX_ROWS)
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and 1 <= M <= min(MAX_ROWS, max_rows or MAX_ROWS)
             and K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0 and tiles <= _MAX_TILES)
 
@@ -42,18 +46,21 @@ def takes(x, w, fuse_swiglu=False, max_rows=None):
 def run(x, w, out_dtype, fuse_swiglu=False):
     M, K = x.shape
     n_out = w.shape[0] // 2 if fuse_swiglu else w.shape[0]
-    counters, sms = _device_state(x.device)
-    tiles = (n_out + 7) // 8 if fuse_swiglu else (n_out + 15) // 16
-    lib = _library.library()
-    ksplit = lib.dl_gemm_skinny_splits(tiles, K, sms)
-    nt = 1 if M <= 8 else 2 if M <= 16 else 4 if M <= 32 else 8
-    partials = torch.empty(tiles * ksplit * nt * 128, dtype=torch.float32, device=x.device) if ksplit > 1 else None
+    counters, partials, sms = _device_state(x.device)
     out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     _library.call("dl_gemm_skinny_bf16", x.data_ptr(), x.stride(0) if M > 1 else max(K, x.stride(0)),
                   w.data_ptr(), out.data_ptr(), 0 if out_dtype == torch.float32 else 1, n_out, M, n_out, K,
-                  1 if fuse_swiglu else 0, ksplit, None if partials is None else partials.data_ptr(),
-                  counters.data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  1 if fuse_swiglu else 0, partials.data_ptr(), partials.numel(), counters.data_ptr(),
+                  counters.numel(), _library.status_word(x.device).data_ptr(),
+                  torch.cuda.current_stream().cuda_stream)
     return out
+
+
+def scratch_need(M, N, K, fuse_swiglu=False, sms=148):
+    """(partial floats, counters) the product of these sizes needs."""
+    a, b = ctypes.c_int(0), ctypes.c_int(0)
+    _library.library().dl_gemm_skinny_scratch(M, N, K, 1 if fuse_swiglu else 0, sms, ctypes.byref(a), ctypes.byref(b))
+    return a.value, b.value
 
 
 def maybe_run(x, w, out_dtype, fuse_swiglu=False):

@@ -48,12 +48,16 @@ def _time(fn, iters, flush):
     return times[len(times) // 2], times[0]
 
 
+SCATTER_PAGES = True       # pages of a sequence in random order (False: in the order they were taken)
+
+
 def _paged(batch, context, nkv, hd, dev):
     pages_per = (context + 63) // 64
     n_pages = batch * pages_per
     k_pool = torch.randn(n_pages, nkv, 64, hd, device=dev, dtype=torch.bfloat16)
     v_pool = torch.randn(n_pages, nkv, hd, 64, device=dev, dtype=torch.bfloat16)
-    table = torch.randperm(n_pages, device=dev).to(torch.int32).view(batch, pages_per).contiguous()
+    order = torch.randperm(n_pages, device=dev) if SCATTER_PAGES else torch.arange(n_pages, device=dev)
+    table = order.to(torch.int32).view(batch, pages_per).contiguous()
     return k_pool, v_pool, table
 
 
@@ -74,7 +78,12 @@ def main(argv=None):
     ap.add_argument("--out-f32", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--runs-per-block", type=int, default=0, help="attention_decode: override the run-size heuristic")
+    ap.add_argument("--sequential-pages", action="store_true", help="pages of a sequence lie one after another")
     args = ap.parse_args(argv)
+    if args.sequential_pages:
+        global SCATTER_PAGES
+        SCATTER_PAGES = False
 
     from ..engine.step import AttentionPlan
     from . import gemm_skinny, ops
@@ -87,6 +96,9 @@ def main(argv=None):
     result = {"kernel": args.kernel}
 
     if args.kernel == "attention_decode":
+        if args.runs_per_block:
+            from . import attention_fast
+            attention_fast.RUNS_PER_BLOCK = args.runs_per_block
         b, ctx = args.batch, args.context
         k_pool, v_pool, table = _paged(b, ctx, nkv, hd, dev)
         q = torch.randn(b, nh * hd, device=dev, dtype=torch.bfloat16)

@@ -340,7 +340,7 @@ def test_kernels_refuse_what_they_cannot_take():
 
 
 # ----------------------------------------------------------------- tensor-core kernels (bfloat16)
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(64, 64), (200, 176), (1000, 320), (4096, 4096), (6144, 512)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_skinny(M, N, K, out_dtype):
@@ -348,7 +348,7 @@ def test_gemm_skinny(M, N, K, out_dtype):
     g = torch.Generator().manual_seed(20)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
-    assert gemm_skinny.takes(x.to(DEV), w.to(DEV), max_rows=64)
+    assert gemm_skinny.takes(x.to(DEV), w.to(DEV))
     y = gemm_skinny.run(x.to(DEV), w.to(DEV), out_dtype)
     ref = (x.double() @ w.double().T).float()
     close(y, ref, 2e-4 * math.sqrt(K / 64), 2 ** -8 if out_dtype == torch.bfloat16 else 1e-5)
@@ -366,11 +366,12 @@ def test_gemm_skinny_gated(M, I, K):
     g = torch.Generator().manual_seed(21)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(2 * I, K, generator=g) * 0.1).to(torch.bfloat16)
-    y = gemm_skinny.run(x.to(DEV), w.to(DEV), torch.bfloat16, fuse_swiglu=True)
     gu = x.double() @ w.double().T
     ref = plain_llama.swiglu(gu[:, :I].float(), gu[:, I:].float())
-    assert y.shape == (M, I)
-    close(y, ref, 2e-4, 2 ** -8)
+    if M <= gemm_skinny.MAX_ROWS:
+        y = gemm_skinny.run(x.to(DEV), w.to(DEV), torch.bfloat16, fuse_swiglu=True)
+        assert y.shape == (M, I)
+        close(y, ref, 2e-4, 2 ** -8)
     # the op picks the fused kernel for few rows and the two-kernel path otherwise; both agree
     # The two-kernel path rounds gate and up to bfloat16 (relative step 2^-8) before the gating:
     # |d silu(g)u| <= 2^-8 (|g silu'(g) u| + |silu(g) u|), plus the output's own rounding.
@@ -468,3 +469,25 @@ def test_attention_prefill_packed_unequal(nh, nkv, hd, window):
     # rounding to nearest) for the P V product: |error| <= 2^-9 max|v|, plus the output's rounding.
     v_max = max(float(v.abs().max()) for _, v in dense)
     close(fast, ref, 2 ** -9 * v_max + 1e-3, 2 ** -8)
+
+
+def test_attention_decode_long_runs(monkeypatch):
+    """Few sequences and long caches: every warp of the decode kernel takes several pages of a run
+    and a block takes several runs."""
+    from dotllm_b200.kernels import attention_fast
+    monkeypatch.setattr(attention_fast, "RUNS_PER_BLOCK", 1)
+    nh, nkv, hd = 32, 8, 128
+    lengths = [8192, 5001, 64]
+    k_pool, v_pool, table, dense = make_paged(len(lengths), lengths, nkv, hd, torch.bfloat16, seed=25)
+    q = torch.randn(len(lengths), nh * hd, generator=torch.Generator().manual_seed(26)).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    seqs = torch.arange(len(lengths), dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    args = (q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), seqs, pos, table.to(DEV), nh, nkv, hd, scale, 0)
+    fast = ops().attention(*args, plan=_decode_plan(lengths))
+    generic = ops().attention(*args)
+    assert bool(torch.isfinite(fast).all())
+    v_max = max(float(v.abs().max()) for _, v in dense)
+    close(fast, generic, 2 ** -9 * v_max + 1e-3, 2 ** -7)
+    from dotllm_b200.kernels import library
+    library.check_status()

@@ -49,7 +49,7 @@ def test_static_scratch_product_matches_the_ordinary_one(M, N, K, fuse):
 def test_static_scratch_refuses_what_does_not_fit():
     lib, fn = _symbol()
     dev = torch.device("cuda", 0)
-    M, N, K = 64, 16 * 20000, 64                             # more row tiles than the fixed scratch covers
+    M, N, K = 16, 16 * 20000, 64                             # more row tiles than the fixed scratch covers
     x = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
     w = torch.zeros(N, K, dtype=torch.bfloat16, device=dev)
     out = torch.zeros(M, N, dtype=torch.float32, device=dev)
