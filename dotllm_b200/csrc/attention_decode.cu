@@ -7,14 +7,18 @@
 // and value that is loaded: the group's heads are the rows of mma.sync.m16n8k16 tiles (rows beyond
 // the group are zero).
 //
-// Shape: persistent and warp-specialised.  One block per multiprocessor walks the runs
-// it % gridDim.x == blockIdx.x.  A cache page of one KV head is two contiguous pieces (K [64][hd],
-// V [hd][64]); one producer thread copies them with cp.async.bulk (the bulk-copy engine) into a ring
-// of shared-memory stages, signalling an mbarrier per stage, and runs ahead of the arithmetic by the
-// depth of the ring, across run boundaries, at no cost in registers.  Consumer warp w takes pages
-// w, w + C, ... of the stream; at the end of a run the warps merge their partial results in shared
-// memory and the block writes either the output or the run's partial (max, sum, weighted values).
-// A second small kernel merges the runs of a (sequence, head) in a fixed order.
+// Shape: persistent, warp-specialised, stream-K.  The step's work is the list of all visible cache
+// pages ordered by (sequence, KV head, page); it is cut into equal contiguous shares, one per block
+// (one block per multiprocessor), whatever the lengths of the sequences are - the kernel computes
+// the cut itself from the lengths on the device, so a captured launch serves any lengths.  A share
+// is a few segments, each a run of pages of one (sequence, KV head).  A cache page of one KV head
+// is two contiguous pieces (K [64][hd], V [hd][64]); one producer thread copies them with
+// cp.async.bulk (the bulk-copy engine) into a ring of shared-memory stages, signalling an mbarrier
+// per stage, and runs ahead of the arithmetic by the depth of the ring, across segment boundaries,
+// at no cost in registers.  Consumer warp w takes pages w, w + C, ... of the stream; at the end of a
+// segment the warps merge their partial results in shared memory and the block writes either the
+// output (the segment was the whole pair) or the segment's partial (max, sum, weighted values).  A
+// second small kernel merges the segments of a (sequence, head) in block order.
 //
 // Arithmetic: lane (g, t) reads 16-byte pieces of K rows: dims 8t..8t+7 of a 32-dim slice are a
 // consistent permutation of k for Q and K in two MMAs; the 8 key columns of score tile j are keys
@@ -99,27 +103,120 @@ __device__ __forceinline__ uint4 ad_lds128(uint32_t addr) {
     return v;
 }
 
-// One (sequence, KV head, run of pages) and where its pages are.
-struct AdItem {
-    int b, kvh, split, n_splits, len, first, run_begin, page0, n_pages;
+// Pages of a sequence that its newest token sees (from the page of the first visible key).
+__device__ __forceinline__ int ad_first_key(int len, int window) { return (window > 0 && len - window > 0) ? len - window : 0; }
+__device__ __forceinline__ int ad_pages_of(int len, int window) {
+    if (len <= 0) return 0;
+    return (len - 1) / DL_PAGE - ad_first_key(len, window) / DL_PAGE + 1;
+}
+
+// The work of a step is the list of all visible pages, ordered by (sequence, KV head, page), cut into
+// equal contiguous shares, one per block.  AdCut is that cut, computed by every warp for itself.
+struct AdCut {
+    int total, share;        // pages in the step, pages per block
 };
 
-__device__ __forceinline__ AdItem ad_item(int it, int max_splits, int nkv, const int32_t* seq_len, int window,
-                                          int keys_per_split) {
-    AdItem w;
-    w.split = it % max_splits;
-    const int pair = it / max_splits;
-    w.kvh = pair % nkv;
-    w.b = pair / nkv;
-    w.len = seq_len[w.b];                                  // keys 0..len-1; the query sits at len-1
-    w.first = (window > 0 && w.len - window > 0) ? w.len - window : 0;
-    const int origin = (w.first / DL_PAGE) * DL_PAGE;      // runs start at the first visible key's page
-    w.n_splits = (w.len - origin + keys_per_split - 1) / keys_per_split;
-    w.run_begin = origin + w.split * keys_per_split;
-    const int run_end = min(w.len, w.run_begin + keys_per_split);
-    w.page0 = w.run_begin / DL_PAGE;
-    w.n_pages = w.split < w.n_splits ? (run_end - w.run_begin + DL_PAGE - 1) / DL_PAGE : 0;
+__device__ __forceinline__ AdCut ad_cut(const int32_t* seq_len, int n_seqs, int nkv, int window, int n_blocks, int lane) {
+    int sum = 0;
+    for (int b0 = 0; b0 < n_seqs; b0 += 32)
+        if (b0 + lane < n_seqs) sum += ad_pages_of(seq_len[b0 + lane], window);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    AdCut c;
+    c.total = sum * nkv;
+    c.share = max(1, (c.total + n_blocks - 1) / n_blocks);
+    return c;
+}
+
+// The sequence that holds page r of the list (r < total), and the pages of the list before it.
+__device__ __forceinline__ void ad_locate(const int32_t* seq_len, int n_seqs, int nkv, int window, int r, int lane,
+                                          int* b_out, int* before_out) {
+    int before = 0, b = n_seqs, b_before = 0;
+    for (int b0 = 0; b0 < n_seqs; b0 += 32) {
+        const int np = (b0 + lane < n_seqs) ? ad_pages_of(seq_len[b0 + lane], window) * nkv : 0;
+        int incl = np;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, before + incl > r);
+        if (hit) {
+            const int src = __ffs(hit) - 1;
+            b = b0 + src;
+            b_before = before + __shfl_sync(0xffffffffu, incl - np, src);
+            break;
+        }
+        before += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    *b_out = b;
+    *before_out = b_before;
+}
+
+// A block's walk over its share: segments of one (sequence, KV head) each.
+struct AdWalk {
+    int r, r_end;            // next page of the list, end of the share
+    int b, kvh, pg;          // where r lies: sequence, KV head, page among the sequence's visible pages
+    int len, np;             // of sequence b: keys, visible pages
+    bool first;              // the next segment is the block's first
+};
+struct AdSeg {
+    int b, kvh, len, first_key, run_begin, page0, n_pages, slot;
+    bool whole;
+};
+
+__device__ __forceinline__ AdWalk ad_walk_begin(const AdCut& c, const int32_t* seq_len, int n_seqs, int nkv, int window,
+                                                int block, int lane) {
+    AdWalk w;
+    w.r = min(c.total, block * c.share);
+    w.r_end = min(c.total, w.r + c.share);
+    w.first = true;
+    w.b = n_seqs;
+    w.kvh = w.pg = w.len = w.np = 0;
+    if (w.r < w.r_end) {
+        int before;
+        ad_locate(seq_len, n_seqs, nkv, window, w.r, lane, &w.b, &before);
+        if (w.b >= n_seqs) {                                 // cannot happen while r < total
+            w.r = w.r_end;
+            return w;
+        }
+        w.len = seq_len[w.b];
+        w.np = ad_pages_of(w.len, window);
+        const int off = w.r - before;
+        w.kvh = off / w.np;
+        w.pg = off - w.kvh * w.np;
+    }
     return w;
+}
+
+// The next segment of the walk; false when the share is used up.
+__device__ __forceinline__ bool ad_walk_next(AdWalk& w, AdSeg& s, const int32_t* seq_len, int n_seqs, int nkv, int window) {
+    if (w.r >= w.r_end || w.b >= n_seqs) return false;
+    const int n = min(w.np - w.pg, w.r_end - w.r);
+    s.b = w.b;
+    s.kvh = w.kvh;
+    s.len = w.len;
+    s.first_key = ad_first_key(w.len, window);
+    s.page0 = s.first_key / DL_PAGE + w.pg;
+    s.run_begin = s.page0 * DL_PAGE;
+    s.n_pages = n;
+    s.whole = (w.pg == 0 && n == w.np);
+    s.slot = w.first ? 0 : 1;
+    w.first = false;
+    w.r += n;
+    w.pg += n;
+    if (w.pg == w.np) {
+        w.pg = 0;
+        if (++w.kvh == nkv) {
+            w.kvh = 0;
+            do {                                             // the next sequence that has pages
+                ++w.b;
+                w.len = w.b < n_seqs ? seq_len[w.b] : 0;
+                w.np = ad_pages_of(w.len, window);
+            } while (w.b < n_seqs && w.np == 0);
+        }
+    }
+    return true;
 }
 
 // WIDE: the group has more than 8 query heads, so fragment rows 8..15 carry data too.
@@ -129,8 +226,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         int out_stride, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, int n_pages,
                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_table,
-                        int bt_stride, int n_items, int max_splits, int nh, int nkv, float scale, int window,
-                        int keys_per_split, int n_stages, float* __restrict__ part_o,
+                        int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int n_stages,
+                        float* __restrict__ part_o,
                         float* __restrict__ part_ml, int* __restrict__ status) {
     constexpr int DC = HD / 32;          // 32-dim slices of a head
     constexpr int DT = HD / 8;           // 8-dim output tiles
@@ -166,14 +263,18 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    dl_launch_dependents();
+    dl_grid_dependency_wait();       // q and the newest cache page come from the kernel before this one
 
     if (warp == AD_MAX_STAGES) {
         // ------------------------------------------------------------ producer
         // The warp reads 32 page ids at a time (one coalesced load); lane 0 issues the copies.
         int n = 0;                                           // pages issued so far, over all runs
         bool stop = false;
-        for (int it = blockIdx.x; it < n_items && !stop; it += gridDim.x) {
-            const AdItem w = ad_item(it, max_splits, nkv, seq_len, window, keys_per_split);
+        const AdCut cut = ad_cut(seq_len, n_seqs, nkv, window, gridDim.x, lane);
+        AdWalk walk = ad_walk_begin(cut, seq_len, n_seqs, nkv, window, blockIdx.x, lane);
+        AdSeg w;
+        while (!stop && ad_walk_next(walk, w, seq_len, n_seqs, nkv, window)) {
             const int32_t* pages = block_table + (size_t)w.b * bt_stride + w.page0;
             for (int i0 = 0; i0 < w.n_pages && !stop; i0 += 32) {
                 const int mine = (i0 + lane < w.n_pages) ? pages[i0 + lane] : 0;
@@ -215,9 +316,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
         float* my_o = merge_o + (size_t)warp * group * (HD + 4);
         const float scale2 = scale * 1.4426950408889634f;    // scores in units of log2
         int n0 = 0;                                          // pages of the runs before this one
-        for (int it = blockIdx.x; it < n_items; it += gridDim.x) {
-            const AdItem w = ad_item(it, max_splits, nkv, seq_len, window, keys_per_split);
-            if (w.n_pages == 0) continue;                    // the same for every warp of the block
+        const AdCut cut = ad_cut(seq_len, n_seqs, nkv, window, gridDim.x, lane);
+        AdWalk walk = ad_walk_begin(cut, seq_len, n_seqs, nkv, window, blockIdx.x, lane);
+        AdSeg w;
+        while (ad_walk_next(walk, w, seq_len, n_seqs, nkv, window)) {      // the same segments in every warp
             // Q rows g and g+8 of the group (zero beyond the group)
             uint4 qf_lo[DC], qf_hi[DC];
             {
@@ -249,13 +351,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                 const int base = w.run_begin + i * DL_PAGE;  // first key of the page
                 __nv_bfloat16* kp = stage_mem + (size_t)s * 2 * PAGE_ELEMS;
                 __nv_bfloat16* vp = kp + PAGE_ELEMS;
-                const bool ragged = (base + DL_PAGE > w.len) || (base < w.first);
+                const bool ragged = (base + DL_PAGE > w.len) || (base < w.first_key);
                 if (ragged) {
                     // Keys outside [first, len) may hold anything (even NaN): make their values exact
                     // zeros in the stage once, so that the product below needs no special case.
                     for (int idx = lane; idx < HD * DL_PAGE; idx += 32) {
                         const int key = base + (idx & (DL_PAGE - 1));
-                        if (key < w.first || key >= w.len) vp[idx] = __float2bfloat16_rn(0.f);
+                        if (key < w.first_key || key >= w.len) vp[idx] = __float2bfloat16_rn(0.f);
                     }
                     __syncwarp();
                 }
@@ -311,7 +413,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int key = base + 32 * h + 8 * t + 2 * j + e;
-                                if (key < w.first || key >= w.len) {
+                                if (key < w.first_key || key >= w.len) {
                                     sc[h][j][e] = -INFINITY;
                                     sc[h][j][2 + e] = -INFINITY;
                                 }
@@ -422,7 +524,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
             ad_consumer_sync(n_stages);
 
             const int tid = threadIdx.x;                     // 0 .. 32*n_stages-1
-            const size_t part_row = ((size_t)(w.b * nkv + w.kvh) * max_splits + w.split) * group;
+            const size_t part_row = ((size_t)blockIdx.x * 2 + w.slot) * group;
             for (int idx = tid; idx < group * HD; idx += 32 * n_stages) {
                 const int r = idx / HD, d = idx - r * HD;
                 float m = -INFINITY;
@@ -433,7 +535,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                     acc += merge_o[((size_t)cw * group + r) * (HD + 4) + d] * f;
                     l += sm_l[cw][r] * f;
                 }
-                if (w.n_splits == 1) {
+                if (w.whole) {
                     out[(size_t)w.b * out_stride + (size_t)(w.kvh * group + r) * HD + d] = __float2bfloat16_rn(acc / l);
                 } else {
                     part_o[(part_row + r) * HD + d] = acc;
@@ -449,41 +551,87 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     __syncthreads();                                         // nobody leaves while copies may still land
 }
 
-// Merge the runs of every (sequence, head) that was cut into more than one, in run order.
-// One block per (sequence, KV head); thread -> (head of the group, dim).
-__global__ void __launch_bounds__(256)
+// Merge the segments of every (sequence, KV head) that the cut spread over more than one block, in
+// block order.  One block per (sequence, KV head); thread -> (head of the group, four dims).  The
+// cut is recomputed from the lengths exactly as the main kernel computed it; the loads of up to
+// eight segments are issued together.
+__global__ void __launch_bounds__(128)
 attention_decode_combine_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const int32_t* __restrict__ seq_len,
-                                int nh, int nkv, int hd, int window, int keys_per_split, int max_splits,
+                                int n_seqs, int nh, int nkv, int hd, int window, int n_blocks,
                                 const float* __restrict__ part_o, const float* __restrict__ part_ml) {
+    dl_launch_dependents();
     const int kvh = blockIdx.x, b = blockIdx.y;
     const int group = nh / nkv;
-    const int len = seq_len[b];
-    const int first = (window > 0 && len - window > 0) ? len - window : 0;
-    const int origin = (first / DL_PAGE) * DL_PAGE;
-    const int n_splits = (len - origin + keys_per_split - 1) / keys_per_split;
-    if (n_splits <= 1) return;                               // the main kernel wrote the output itself
-    const size_t row0 = ((size_t)(b * nkv + kvh) * max_splits) * group;
-    for (int idx = threadIdx.x; idx < group * hd; idx += blockDim.x) {
-        const int r = idx / hd, d = idx - r * hd;
-        float m = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, part_ml[(row0 + (size_t)sp * group + r) * 2]);
-        float acc = 0.f, l = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const size_t row = row0 + (size_t)sp * group + r;
-            const float ms = part_ml[row * 2];
-            const float f = (ms == -INFINITY) ? 0.f : ad_ex2(ms - m);
-            acc += part_o[row * hd + d] * f;
-            l += part_ml[row * 2 + 1] * f;
+    const int hd4 = hd >> 2;
+    const int lane = threadIdx.x & 31;
+    dl_grid_dependency_wait();
+    int sum = 0, before = 0;
+    for (int b0 = 0; b0 < n_seqs; b0 += 32)
+        if (b0 + lane < n_seqs) {
+            const int np = ad_pages_of(seq_len[b0 + lane], window);
+            sum += np;
+            if (b0 + lane < b) before += np;
         }
-        out[(size_t)b * out_stride + (size_t)(kvh * group + r) * hd + d] = __float2bfloat16_rn(acc / l);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        before += __shfl_xor_sync(0xffffffffu, before, o);
+    }
+    const int total = sum * nkv;
+    const int share = max(1, (total + n_blocks - 1) / n_blocks);
+    const int np_b = ad_pages_of(seq_len[b], window);
+    if (np_b == 0) return;
+    const int begin = before * nkv + kvh * np_b;             // this pair's place in the list of pages
+    const int i0 = begin / share, i1 = (begin + np_b - 1) / share;
+    if (i0 == i1) return;                                    // one block had it all and wrote the output itself
+    const int slot_first = (begin == i0 * share) ? 0 : 1;    // the pair's first segment is its block's first or last
+    const int n_seg = i1 - i0 + 1;
+    for (int idx = threadIdx.x; idx < group * hd4; idx += blockDim.x) {
+        const int r = idx / hd4, d = (idx - r * hd4) * 4;
+        float m = -INFINITY, l = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp0 = 0; sp0 < n_seg; sp0 += 8) {
+            float2 ml[8];
+            float4 o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (sp0 + j < n_seg) {
+                    const int slot = (sp0 + j == 0) ? slot_first : 0;
+                    const size_t row = ((size_t)(i0 + sp0 + j) * 2 + slot) * group + r;
+                    ml[j] = *reinterpret_cast<const float2*>(part_ml + row * 2);
+                    o[j] = *reinterpret_cast<const float4*>(part_o + row * hd + d);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (sp0 + j < n_seg) {
+                    const float mn = fmaxf(m, ml[j].x);
+                    const float f_old = (m == -INFINITY) ? 0.f : ad_ex2(m - mn);
+                    const float f_new = (ml[j].x == -INFINITY) ? 0.f : ad_ex2(ml[j].x - mn);
+                    acc.x = acc.x * f_old + o[j].x * f_new;
+                    acc.y = acc.y * f_old + o[j].y * f_new;
+                    acc.z = acc.z * f_old + o[j].z * f_new;
+                    acc.w = acc.w * f_old + o[j].w * f_new;
+                    l = l * f_old + ml[j].y * f_new;
+                    m = mn;
+                }
+            }
+        }
+        const float inv = 1.f / l;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(out + (size_t)b * out_stride + (size_t)(kvh * group + r) * hd + d) = packed;
     }
 }
 
 template <int HD, bool WIDE>
 static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                      const void* v_pool, int n_pages, const int32_t* seq_len, const int32_t* block_table,
-                     int bt_stride, int n_seqs, int max_splits, int nh, int nkv, float scale, int window,
-                     int keys_per_split, float* part_o, float* part_ml, int* status) {
+                     int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int blocks, float* part_o,
+                     float* part_ml, int part_slots, int* status) {
     const int group = nh / nkv;
     int dev = 0, sms = 0, max_smem = 0;
     cudaGetDevice(&dev);
@@ -502,41 +650,47 @@ static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int
         if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "attention_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
         configured = (int)smem;
     }
-    const int n_items = n_seqs * nkv * max_splits;
-    const int blocks = n_items < sms ? n_items : sms;
-    attention_decode_kernel<HD, WIDE><<<blocks, AD_THREADS, smem, s>>>(
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
-        (const __nv_bfloat16*)v_pool, n_pages, seq_len, block_table, bt_stride, n_items, max_splits, nh, nkv, scale,
-        window, keys_per_split, n_stages, part_o, part_ml, status);
-    DL_CHECK_LAUNCH("attention_decode");
-    if (max_splits > 1) {
-        attention_decode_combine_kernel<<<dim3(nkv, n_seqs), 256, 0, s>>>((__nv_bfloat16*)out, out_stride, seq_len, nh, nkv,
-                                                                        HD, window, keys_per_split, max_splits, part_o,
-                                                                        part_ml);
-        DL_CHECK_LAUNCH("attention_decode_combine");
+    // One block per multiprocessor unless the caller asks for fewer, and never more than there can be pages.
+    if (blocks <= 0 || blocks > sms) blocks = sms;
+    const long long most_pages = (long long)n_seqs * nkv * bt_stride;
+    if (blocks > most_pages) blocks = (int)most_pages;
+    if (part_slots < 2 * blocks)
+        return dl_fail(DL_ERR_ARGUMENT, "attention_decode: scratch for %d segments, %d blocks need %d", part_slots, blocks, 2 * blocks);
+    cudaError_t le = dl_launch_dependent(
+        attention_decode_kernel<HD, WIDE>, dim3(blocks), dim3(AD_THREADS), smem, s, (const __nv_bfloat16*)q, q_stride,
+        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, n_pages, seq_len,
+        block_table, bt_stride, n_seqs, nh, nkv, scale, window, n_stages, part_o, part_ml, status);
+    if (le != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "attention_decode: %s", cudaGetErrorString(le));
+    if (blocks > 1) {
+        cudaError_t e = dl_launch_dependent(attention_decode_combine_kernel, dim3(nkv, n_seqs), dim3(128), 0, s,
+                                            (__nv_bfloat16*)out, out_stride, seq_len, n_seqs, nh, nkv, HD, window, blocks,
+                                            (const float*)part_o, (const float*)part_ml);
+        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "attention_decode_combine: %s", cudaGetErrorString(e));
     }
     return DL_OK;
 }
 
 // q: bf16 [B, nh*hd] rows q_stride apart (one token per sequence); out likewise.
-// seq_len[b]: keys of sequence b including the new token.  max_splits: runs a (sequence, KV head) may
-// be cut into, at least ceil(longest visible span / keys_per_split).
-// part_o: float32 [B, nkv, max_splits, group, hd]; part_ml: float32 [B, nkv, max_splits, group, 2]
-// (scratch, needed when max_splits > 1); status: int32, set non-zero if a wait expired.
+// seq_len[b]: keys of sequence b including the new token; block_table: int32 [B, bt_stride] page ids.
+// blocks: persistent blocks to use (<= 0: one per multiprocessor).
+// part_o: float32 [part_slots, group, hd]; part_ml: float32 [part_slots, group, 2]: scratch for the
+// segments of (sequence, head) pairs that the cut spreads over several blocks, two per block.
+// status: int32, set non-zero if a wait expired.
 extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                         const void* v_pool, int n_pages, const int32_t* seq_len,
                                         const int32_t* block_table, int bt_stride, int n_seqs, int nh, int nkv,
-                                        int hd, float scale, int window, int keys_per_split, int max_splits,
-                                        float* part_o, float* part_ml, int* status, void* stream) {
+                                        int hd, float scale, int window, int blocks, float* part_o, float* part_ml,
+                                        int part_slots, int* status, void* stream) {
     DL_REQUIRE(n_seqs >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad head counts");
     DL_REQUIRE(nh / nkv <= 16, "attention_decode: groups of more than 16 query heads are not supported (%d)", nh / nkv);
     DL_REQUIRE(scale > 0.f, "attention_decode: the score scale must be positive");
-    DL_REQUIRE(keys_per_split >= DL_PAGE && keys_per_split % DL_PAGE == 0, "attention_decode: keys_per_split %d must be a multiple of %d", keys_per_split, DL_PAGE);
-    DL_REQUIRE(max_splits >= 1 && (max_splits == 1 || (part_o && part_ml)), "attention_decode: split runs need scratch");
+    DL_REQUIRE(part_o && part_ml && part_slots >= 2, "attention_decode: needs scratch for the cut segments");
     DL_REQUIRE(status != nullptr, "attention_decode: needs a status word");
+    DL_REQUIRE(bt_stride >= 1 && window >= 0, "attention_decode: bad block table stride or window");
+    DL_REQUIRE(out_stride % 4 == 0 && ((uintptr_t)out % 8) == 0, "attention_decode: out must be 8-byte aligned");
     DL_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0,
                "attention_decode: q and the pools must be 16-byte aligned");
-    DL_REQUIRE((long long)n_seqs * nkv * max_splits < (1ll << 30) && n_seqs <= 65535, "attention_decode: too many runs");
+    DL_REQUIRE((long long)n_seqs * nkv * bt_stride < (1ll << 30) && n_seqs <= 65535, "attention_decode: too many pages");
     if (n_seqs == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const bool wide = nh / nkv > 8;
@@ -544,11 +698,11 @@ extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, 
     if (hd == HDV) {                                                                                                   \
         if (wide)                                                                                                      \
             return ad_launch<HDV, true>(s, q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table, \
-                                        bt_stride, n_seqs, max_splits, nh, nkv, scale, window, keys_per_split, part_o, \
-                                        part_ml, status);                                                              \
+                                        bt_stride, n_seqs, nh, nkv, scale, window, blocks, part_o, part_ml, part_slots, \
+                                        status);                                                                       \
         return ad_launch<HDV, false>(s, q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table,   \
-                                     bt_stride, n_seqs, max_splits, nh, nkv, scale, window, keys_per_split, part_o,    \
-                                     part_ml, status);                                                                 \
+                                     bt_stride, n_seqs, nh, nkv, scale, window, blocks, part_o, part_ml, part_slots,   \
+                                     status);                                                                          \
     }
     AD_CASE(32) AD_CASE(64) AD_CASE(96) AD_CASE(128)
 #undef AD_CASE

@@ -32,6 +32,36 @@ int dl_fail(int status, const char* fmt, ...);
             return dl_fail(DL_ERR_LAUNCH, "%s: %s", name, cudaGetErrorString(e__));   \
     } while (0)
 
+// Programmatic dependent launch.  A kernel launched through dl_launch_dependent may begin while its
+// predecessor on the stream is still running: its blocks start as soon as every block of the
+// predecessor has called dl_launch_dependents() (or exited) and there is room on a multiprocessor.
+// Such a kernel must call dl_grid_dependency_wait() before it reads anything an earlier kernel
+// wrote and before it writes any global memory (an earlier kernel may still be reading it); what
+// it does before the wait may touch only memory that no kernel of the stream writes (weights).
+// dl_launch_dependents() is harmless in a kernel that nothing depends on.
+bool dl_dependent_launch_enabled();          // false when DOTLLM_DEPENDENT_LAUNCH=0 is set
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void dl_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t dl_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                              cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = dl_dependent_launch_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 template <typename T> __device__ __forceinline__ float dl_to_f32(T v);
 template <> __device__ __forceinline__ float dl_to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float dl_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -10,6 +10,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
                    float* __restrict__ out, int width, int n_table_rows) {
+    dl_launch_dependents();
     const int row = blockIdx.x;
     const int id = ids[row];
     float* dst = out + (size_t)row * width;

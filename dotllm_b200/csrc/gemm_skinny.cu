@@ -10,9 +10,10 @@
 // Shape: persistent, warp-specialised, stream-K.  The work is the list of (16-row tile, 256-wide
 // chunk of k) pairs in tile-major order, cut into equal contiguous shares, one per consumer warp of
 // the whole grid, so every warp streams the same number of bytes whatever N and K are.  One producer
-// warp per block copies chunks with cp.async.bulk (16 row pieces of 512 bytes) into a private ring
-// of shared-memory stages for each consumer warp, signalling an mbarrier per stage; copies run ahead
-// of the arithmetic by the depth of the ring.  A consumer never synchronises with another warp of
+// warp per block (lane c serving consumer warp c) copies chunks as tiled boxes of a tensor map over W
+// (cp.async.bulk.tensor.2d, 16 rows by 256 k) into a private ring of shared-memory stages for each
+// consumer warp, signalling an mbarrier per stage; copies run ahead of the arithmetic by the depth
+// of the ring.  A consumer never synchronises with another warp of
 // its block.  A tile that lies wholly inside one share is finished by that warp; a tile cut between
 // shares is summed, in share order, by whichever of its warps arrives last, so the result is
 // deterministic and does not depend on the number of rows of x.  With FUSE_SWIGLU a tile's rows
@@ -68,12 +69,6 @@ __device__ __forceinline__ bool gs_mbar_wait(uint64_t* bar, uint32_t parity, vol
     }
     return true;
 }
-__device__ __forceinline__ void gs_bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(gs_smem(dst)),
-                 "l"(src), "r"(bytes), "r"(gs_smem(bar))
-                 : "memory");
-}
-
 __device__ __forceinline__ uint4 gs_lds128(uint32_t addr) {     // 16 bytes from a shared-space byte address
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
@@ -84,19 +79,6 @@ template <typename TOut> __device__ __forceinline__ void gs_store(TOut* p, float
 template <> __device__ __forceinline__ void gs_store<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void gs_store<__nv_bfloat16>(__nv_bfloat16* p, float v) {
     *p = __float2bfloat16_rn(v);
-}
-
-// Row of W behind fragment row r (0..15) of a tile, and whether it exists.
-template <bool FUSE_SWIGLU>
-__device__ __forceinline__ int gs_row(int tile, int r, int N, int up_offset, bool* ok) {
-    if (FUSE_SWIGLU) {
-        const int i = tile * 8 + (r & 7);
-        *ok = i < N;
-        return r < 8 ? i : up_offset + i;
-    }
-    const int row = tile * 16 + r;
-    *ok = row < N;
-    return row;
 }
 
 // acc[j] = {(row g, tok 2t), (row g, tok 2t+1), (row g+8, tok 2t), (row g+8, tok 2t+1)} of 8-token group j
@@ -131,8 +113,8 @@ template <int NT, typename TOut, bool FUSE_SWIGLU>
 __global__ void __launch_bounds__(GS_THREADS, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const __nv_bfloat16* __restrict__ x, int x_stride,
                    TOut* __restrict__ out, int out_stride, int M, int N, int K, int up_offset, int cpt,
-                   int total_chunks, int share, float* __restrict__ partials, int* __restrict__ counters,
-                   int* __restrict__ status) {
+                   int total_chunks, int share, int early_weights, float* __restrict__ partials,
+                   int* __restrict__ counters, int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char gs_smem_raw[];
     __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(gs_smem_raw);   // [consumer][slot][16][GS_PITCH]
     __shared__ uint64_t full_bar[GS_CONSUMERS][GS_SLOTS], empty_bar[GS_CONSUMERS][GS_SLOTS];
@@ -149,9 +131,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const __nv_bfloat16
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    dl_launch_dependents();
 
     if (warp == GS_CONSUMERS) {
         // ------------------------------------------------------------ producer warp
+        // When the caller vouches that no pending work writes the weights (early_weights), the
+        // producer does not wait for the kernel before this one: while that kernel finishes, the
+        // rings fill.
+        if (!early_weights) dl_grid_dependency_wait();
         // Lane c (< GS_CONSUMERS) feeds consumer c: it walks that warp's share chunk by chunk, waits for
         // the ring slot to be free, and issues one tiled copy (two for gate + up) per chunk.
         if (lane < GS_CONSUMERS) {
@@ -192,6 +179,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const __nv_bfloat16
         const int g = lane >> 2, t = lane & 3;
         const int gw = blockIdx.x * GS_CONSUMERS + warp;
         const int begin = min(total_chunks, gw * share), end = min(total_chunks, (gw + 1) * share);
+        dl_grid_dependency_wait();       // x comes from the kernel before this one; out, partials and counters may be in use by it
         float acc[NT][4];
 #pragma unroll
         for (int j = 0; j < NT; ++j)
@@ -322,8 +310,8 @@ extern "C" int dl_gemm_skinny_scratch(int M, int N, int K, int fuse_swiglu, int 
 
 template <int NT, typename TOut, bool FUSE>
 static int gs_launch(const GsPlan& p, cudaStream_t s, const __nv_bfloat16* x, int x_stride, const __nv_bfloat16* w,
-                     void* out, int out_stride, int M, int N, int K, int up_offset, float* partials, int* counters,
-                     int* status) {
+                     void* out, int out_stride, int M, int N, int K, int up_offset, int early_weights, float* partials,
+                     int* counters, int* status) {
     const size_t smem = (size_t)GS_CONSUMERS * GS_SLOTS * GS_STAGE_ELEMS * 2;
     static bool configured = false;
     if (!configured) {
@@ -360,21 +348,25 @@ static int gs_launch(const GsPlan& p, cudaStream_t s, const __nv_bfloat16* x, in
         }
         tmap = it->second;
     }
-    gemm_skinny_kernel<NT, TOut, FUSE><<<p.blocks, GS_THREADS, smem, s>>>(tmap, x, x_stride, (TOut*)out, out_stride, M, N, K,
-                                                                          up_offset, p.cpt, p.total, p.share, partials,
-                                                                          counters, status);
-    DL_CHECK_LAUNCH("gemm_skinny");
+    cudaError_t le = dl_launch_dependent(gemm_skinny_kernel<NT, TOut, FUSE>, dim3(p.blocks), dim3(GS_THREADS), smem, s, tmap, x,
+                                         x_stride, (TOut*)out, out_stride, M, N, K, up_offset, p.cpt, p.total, p.share,
+                                         early_weights, partials, counters, status);
+    if (le != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny: %s", cudaGetErrorString(le));
     return DL_OK;
 }
 
 // x: bf16 [M, K] rows x_stride apart, M <= 16.  w: bf16, contiguous rows of K.
-// fuse_swiglu == 0: w is [N, K], out [M, N].  fuse_swiglu == 1: w is [2N, K] (N gate rows, then N
-// up rows), out [M, N] = silu(x Wg^T) * (x Wu^T).
+// flags bit 0 (gated) clear: w is [N, K], out [M, N].  Set: w is [2N, K] (N gate rows, then N up
+// rows), out [M, N] = silu(x Wg^T) * (x Wu^T).
+// flags bit 1 (resident weights): the caller vouches that nothing still pending on the stream
+// writes w, so the kernel may start reading w before the kernel launched before it has finished.
 // partials / counters: scratch of the sizes dl_gemm_skinny_scratch gives; status: int32, set
 // non-zero if a wait expired.
 extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype,
-                                   int out_stride, int M, int N, int K, int fuse_swiglu, float* partials,
+                                   int out_stride, int M, int N, int K, int flags, float* partials,
                                    int partial_floats, int* counters, int n_counters, int* status, void* stream) {
+    const int fuse_swiglu = flags & 1, early = (flags >> 1) & 1;
+    DL_REQUIRE((flags & ~3) == 0, "gemm_skinny: unknown flags %d", flags);
     DL_REQUIRE(M >= 1 && M <= GS_MAX_ROWS, "gemm_skinny: takes 1 to %d rows, got %d", GS_MAX_ROWS, M);
     DL_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gemm_skinny: K=%d must be a positive multiple of 8", K);
     DL_REQUIRE(x_stride % 8 == 0 && x_stride >= K, "gemm_skinny: row stride of x (%d) must be a multiple of 8", x_stride);
@@ -395,11 +387,11 @@ extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, v
 #define GS_CASE(NTV)                                                                                                   \
     if (nt == NTV) {                                                                                                   \
         if (fuse_swiglu) {                                                                                             \
-            if (out_dtype == DL_F32) return gs_launch<NTV, float, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, partials, counters, status); \
-            return gs_launch<NTV, __nv_bfloat16, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, partials, counters, status);                \
+            if (out_dtype == DL_F32) return gs_launch<NTV, float, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, early, partials, counters, status); \
+            return gs_launch<NTV, __nv_bfloat16, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, early, partials, counters, status);                \
         }                                                                                                              \
-        if (out_dtype == DL_F32) return gs_launch<NTV, float, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, partials, counters, status);    \
-        return gs_launch<NTV, __nv_bfloat16, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, partials, counters, status);                   \
+        if (out_dtype == DL_F32) return gs_launch<NTV, float, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, early, partials, counters, status);    \
+        return gs_launch<NTV, __nv_bfloat16, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, early, partials, counters, status);                   \
     }
     GS_CASE(1) GS_CASE(2)
 #undef GS_CASE
@@ -473,6 +465,6 @@ extern "C" int dl_gemm_skinny_bf16_static(const void* x, int x_stride, const voi
     // The array keeps whatever the last call left; the arrival counters must start at zero.
     cudaError_t e = cudaMemsetAsync(scratch->counters, 0, sizeof(int) * need_counters, (cudaStream_t)stream);
     if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static: memset: %s", cudaGetErrorString(e));
-    return dl_gemm_skinny_bf16(x, x_stride, w, out, out_dtype, out_stride, M, N, K, fuse_swiglu, scratch->partials,
+    return dl_gemm_skinny_bf16(x, x_stride, w, out, out_dtype, out_stride, M, N, K, fuse_swiglu ? 1 : 0, scratch->partials,
                                need_floats, scratch->counters, need_counters, &scratch->status, stream);
 }

@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_vec_kernel(float* __restrict__ residual, const TDelta* __restrict__ delta,
                    const float* __restrict__ gain, TOut* __restrict__ out, int width, float eps) {
     __shared__ float scratch[33];
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
     const size_t base = (size_t)blockIdx.x * width;
     const int n_vec = width / 4;
     float4 v[NORM_MAX_VEC];
@@ -84,6 +86,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(float* __restrict__ residual, const TDelta* __restrict__ delta,
                const float* __restrict__ gain, TOut* __restrict__ out, int width, float eps) {
     __shared__ float scratch[33];
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
     const size_t base = (size_t)blockIdx.x * width;
     float ss = 0.f;
     for (int c = threadIdx.x; c < width; c += NORM_THREADS) {
@@ -108,14 +112,17 @@ static int launch_norm(float* residual, const void* delta, const float* gain, vo
     const bool vec = aligned && width % 4 == 0 && width <= 4 * NORM_THREADS * NORM_MAX_VEC;
     const TDelta* d = (const TDelta*)delta;
     TOut* o = (TOut*)out;
+    cudaError_t e;
+    const dim3 grid(rows), block(NORM_THREADS);
+    const TDelta* none = nullptr;
     if (vec) {
-        if (delta) rmsnorm_vec_kernel<TDelta, TOut, true><<<rows, NORM_THREADS, 0, s>>>(residual, d, gain, o, width, eps);
-        else rmsnorm_vec_kernel<TDelta, TOut, false><<<rows, NORM_THREADS, 0, s>>>(residual, nullptr, gain, o, width, eps);
+        if (delta) e = dl_launch_dependent(rmsnorm_vec_kernel<TDelta, TOut, true>, grid, block, 0, s, residual, d, gain, o, width, eps);
+        else e = dl_launch_dependent(rmsnorm_vec_kernel<TDelta, TOut, false>, grid, block, 0, s, residual, none, gain, o, width, eps);
     } else {
-        if (delta) rmsnorm_kernel<TDelta, TOut, true><<<rows, NORM_THREADS, 0, s>>>(residual, d, gain, o, width, eps);
-        else rmsnorm_kernel<TDelta, TOut, false><<<rows, NORM_THREADS, 0, s>>>(residual, nullptr, gain, o, width, eps);
+        if (delta) e = dl_launch_dependent(rmsnorm_kernel<TDelta, TOut, true>, grid, block, 0, s, residual, d, gain, o, width, eps);
+        else e = dl_launch_dependent(rmsnorm_kernel<TDelta, TOut, false>, grid, block, 0, s, residual, none, gain, o, width, eps);
     }
-    DL_CHECK_LAUNCH("rmsnorm");
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "rmsnorm: %s", cudaGetErrorString(e));
     return DL_OK;
 }
 

@@ -19,6 +19,8 @@ rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
                         const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
                         const int32_t* __restrict__ block_table, int bt_stride, T* __restrict__ k_pool,
                         T* __restrict__ v_pool, int n_pages, int nh, int nkv, int hd, int write_cache) {
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
     const int t = blockIdx.x;
     const int pos = token_pos[t];
     const int half = rotary_dim / 2;
@@ -78,18 +80,19 @@ extern "C" int dl_rope_cache_write(void* q, int q_stride, const void* k, int k_s
     cudaStream_t s = (cudaStream_t)stream;
     DL_REQUIRE(nh + nkv <= 65535, "rope_cache_write: too many heads");
     dim3 grid(n_tokens, write_cache ? nh + nkv : nh);
+    cudaError_t e;
     if (dtype == DL_F32)
-        rope_cache_write_kernel<float><<<grid, 128, 0, s>>>(
-            (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, cos_t, sin_t, rotary_dim,
-            table_rows, token_seq, token_pos, block_table, bt_stride, (float*)k_pool, (float*)v_pool, n_pages, nh,
-            nkv, hd, write_cache);
+        e = dl_launch_dependent(rope_cache_write_kernel<float>, grid, dim3(128), 0, s, (float*)q, q_stride, (const float*)k,
+                                k_stride, (const float*)v, v_stride, cos_t, sin_t, rotary_dim, table_rows, token_seq,
+                                token_pos, block_table, bt_stride, (float*)k_pool, (float*)v_pool, n_pages, nh, nkv, hd,
+                                write_cache);
     else if (dtype == DL_BF16)
-        rope_cache_write_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(
-            (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride,
-            cos_t, sin_t, rotary_dim, table_rows, token_seq, token_pos, block_table, bt_stride,
-            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, nh, nkv, hd, write_cache);
+        e = dl_launch_dependent(rope_cache_write_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, (__nv_bfloat16*)q, q_stride,
+                                (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, cos_t, sin_t,
+                                rotary_dim, table_rows, token_seq, token_pos, block_table, bt_stride,
+                                (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, nh, nkv, hd, write_cache);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "rope_cache_write: dtype %d", dtype);
-    DL_CHECK_LAUNCH("rope_cache_write");
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "rope_cache_write: %s", cudaGetErrorString(e));
     return DL_OK;
 }

@@ -1,8 +1,9 @@
 """Dispatch to the tensor-core attention kernels for the sizes they take.
 
-Decode steps (one new token per sequence) go to the split-key kernel of csrc/attention_decode.cu.
-Its scratch (per-run partial sums) is allocated once per step and shared by the layers, which run
-one after another on one stream; the counters it synchronises on are kept per device.
+Decode steps (one new token per sequence) go to the stream-K kernel of csrc/attention_decode.cu,
+which cuts the step's cache pages into equal shares per block on the device.  Its scratch (the
+partial results of cut segments, two per block) is allocated once per step and shared by the
+layers, which run one after another on one stream.
 """
 from __future__ import annotations
 
@@ -12,8 +13,8 @@ from . import library as _library
 
 _P, _I, _F = _library._P, _library._I, _library._F
 _library.register_signatures({
-    "dl_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I,
-                                 _P, _P, _P, _P],
+    "dl_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I,
+                                 _P, _P, _I, _P, _P],
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                   _F, _I, _P, _P],
 })
@@ -21,28 +22,7 @@ _library.register_signatures({
 PREFILL_ROWS = 128       # query rows per block of the prefill kernel (AP_ROWS)
 
 DECODE_HEAD_DIMS = (32, 64, 96, 128)
-RUNS_PER_BLOCK = 0       # > 0: force this many runs per persistent decode block (tuning and tests)
-
-
-def keys_per_split(longest, pairs, sms=148):
-    """Keys in one run of a (sequence, KV head).  The decode kernel is persistent, one block per
-    multiprocessor taking runs in turn: several runs per block even out the load, runs of a few
-    pages keep all of a block's warps busy.  ``pairs`` is sequences x KV heads."""
-    if RUNS_PER_BLOCK:                       # explicit override (tuning and tests)
-        want_splits = max(1, (RUNS_PER_BLOCK * sms + pairs - 1) // pairs)
-        kps = (longest + want_splits - 1) // want_splits
-        return max(128, min(2048, (kps + 63) // 64 * 64))
-    # Cost model: blocks work in rounds of `sms` runs; a run costs its pages plus about three pages'
-    # worth of start-up and merging.  Pick the run length with the cheapest total.
-    best, best_cost = 2048, None
-    pages_total = (longest + 63) // 64
-    for pages in range(2, min(32, pages_total) + 1):
-        n_splits = (pages_total + pages - 1) // pages
-        rounds = (pairs * n_splits + sms - 1) // sms
-        cost = rounds * (pages + 3)
-        if best_cost is None or cost < best_cost or (cost == best_cost and pages * 64 > best):
-            best, best_cost = pages * 64, cost
-    return best
+DECODE_BLOCKS = 0        # > 0: persistent blocks of the decode kernel (tuning and tests); 0: one per multiprocessor
 
 
 def decode_fits(group, head_dim):
@@ -55,19 +35,16 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
             scale, window, plan):
     B = plan.n_seqs
     group = n_heads // n_kv_heads
-    longest = min(plan.max_total, window + 64) if window else plan.max_total
-    kps = keys_per_split(longest, B * n_kv_heads)
-    max_splits = max(1, (longest + kps - 1) // kps)
-    key = ("decode", n_kv_heads, group, head_dim, max_splits)
+    slots = 2 * max(1, _library.library().dl_sm_count())
+    key = ("decode", group, head_dim)
     if key not in plan.scratch:
-        plan.scratch[key] = (
-            torch.empty(B * n_kv_heads * max_splits * group * head_dim, dtype=torch.float32, device=q.device),
-            torch.empty(B * n_kv_heads * max_splits * group * 2, dtype=torch.float32, device=q.device))
+        plan.scratch[key] = (torch.empty(slots * group * head_dim, dtype=torch.float32, device=q.device),
+                             torch.empty(slots * group * 2, dtype=torch.float32, device=q.device))
     part_o, part_ml = plan.scratch[key]
     _library.call("dl_attention_decode_bf16", q.data_ptr(), q_stride, out.data_ptr(), out.stride(0),
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, plan.seq_total.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim,
-                  scale, window, kps, max_splits, part_o.data_ptr(), part_ml.data_ptr(),
+                  scale, window, DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots,
                   _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     return True
 

@@ -43,14 +43,14 @@ def takes(x, w, fuse_swiglu=False, max_rows=None):
             and w.data_ptr() % 16 == 0 and tiles <= _MAX_TILES)
 
 
-def run(x, w, out_dtype, fuse_swiglu=False):
+def run(x, w, out_dtype, fuse_swiglu=False, resident=False):
     M, K = x.shape
     n_out = w.shape[0] // 2 if fuse_swiglu else w.shape[0]
     counters, partials, sms = _device_state(x.device)
     out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     _library.call("dl_gemm_skinny_bf16", x.data_ptr(), x.stride(0) if M > 1 else max(K, x.stride(0)),
                   w.data_ptr(), out.data_ptr(), 0 if out_dtype == torch.float32 else 1, n_out, M, n_out, K,
-                  1 if fuse_swiglu else 0, partials.data_ptr(), partials.numel(), counters.data_ptr(),
+                  (1 if fuse_swiglu else 0) | (2 if resident else 0), partials.data_ptr(), partials.numel(), counters.data_ptr(),
                   counters.numel(), _library.status_word(x.device).data_ptr(),
                   torch.cuda.current_stream().cuda_stream)
     return out
@@ -63,8 +63,9 @@ def scratch_need(M, N, K, fuse_swiglu=False, sms=148):
     return a.value, b.value
 
 
-def maybe_run(x, w, out_dtype, fuse_swiglu=False):
-    """y = x W^T (or the gated form) by the skinny kernel when it takes the sizes, else None."""
+def maybe_run(x, w, out_dtype, fuse_swiglu=False, resident=False):
+    """y = x W^T (or the gated form) by the skinny kernel when it takes the sizes, else None.
+    ``resident``: no work still pending on the stream writes W."""
     if not takes(x, w, fuse_swiglu):
         return None
-    return run(x, w, out_dtype, fuse_swiglu)
+    return run(x, w, out_dtype, fuse_swiglu, resident)

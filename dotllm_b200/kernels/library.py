@@ -61,6 +61,8 @@ def library():
         lib.dl_last_error.argtypes = []
         lib.dl_device_arch.restype = ctypes.c_int
         lib.dl_sm_count.restype = ctypes.c_int
+        lib.dl_set_dependent_launch.restype = ctypes.c_int
+        lib.dl_set_dependent_launch.argtypes = [ctypes.c_int]
         _lib = lib
         return lib
 
@@ -86,6 +88,13 @@ def require_device():
         raise KernelError(f"the kernels are compiled for sm_100a; the current device reports "
                           f"compute capability {arch / 10:.1f}")
     _checked_device = True
+
+
+def set_dependent_launch(on):
+    """Switch programmatic dependent launch for later launches: kernels may begin, up to their
+    first read of an earlier kernel's output, while that kernel is still finishing.  On unless
+    the environment sets DOTLLM_DEPENDENT_LAUNCH=0; results are the same either way."""
+    library().dl_set_dependent_launch(1 if on else 0)
 
 
 def call(name, *args):

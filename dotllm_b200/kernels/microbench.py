@@ -78,7 +78,7 @@ def main(argv=None):
     ap.add_argument("--out-f32", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--runs-per-block", type=int, default=0, help="attention_decode: override the run-size heuristic")
+    ap.add_argument("--decode-blocks", type=int, default=0, help="attention_decode: persistent blocks (0: one per multiprocessor)")
     ap.add_argument("--sequential-pages", action="store_true", help="pages of a sequence lie one after another")
     args = ap.parse_args(argv)
     if args.sequential_pages:
@@ -96,9 +96,9 @@ def main(argv=None):
     result = {"kernel": args.kernel}
 
     if args.kernel == "attention_decode":
-        if args.runs_per_block:
+        if args.decode_blocks:
             from . import attention_fast
-            attention_fast.RUNS_PER_BLOCK = args.runs_per_block
+            attention_fast.DECODE_BLOCKS = args.decode_blocks
         b, ctx = args.batch, args.context
         k_pool, v_pool, table = _paged(b, ctx, nkv, hd, dev)
         q = torch.randn(b, nh * hd, device=dev, dtype=torch.bfloat16)

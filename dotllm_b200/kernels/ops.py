@@ -193,8 +193,10 @@ def swiglu(gate_up):
 
 
 # --------------------------------------------------------------------- linear
-def linear(x, w, out_dtype=None):
-    """y = x W^T for W [N, K].
+def linear(x, w, out_dtype=None, resident=False):
+    """y = x W^T for W [N, K].  ``resident``: the caller vouches that nothing still pending on the
+    stream writes W (a model's weights), which lets the decode kernel start streaming W while
+    the kernel before it finishes.
 
     float32: the library's own FFMA kernel (true 32-bit, the same bits for any number of rows).
     bfloat16: cuBLAS through torch with float32 accumulation, the library product that the
@@ -218,7 +220,7 @@ def linear(x, w, out_dtype=None):
         raise KernelError(f"linear: unsupported dtype {x.dtype}")
     if M > 0:
         from . import gemm_skinny
-        y = gemm_skinny.maybe_run(x, w, out_dtype)
+        y = gemm_skinny.maybe_run(x, w, out_dtype, resident=resident)
         if y is not None:
             return y
     if out_dtype == torch.bfloat16:
@@ -226,7 +228,7 @@ def linear(x, w, out_dtype=None):
     return torch.mm(x, w.t(), out_dtype=out_dtype)
 
 
-def gated_linear(x, w_gate_up):
+def gated_linear(x, w_gate_up, resident=False):
     """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] of shape [2I, K]; returns [T, I] in x's dtype.
     For a few bfloat16 rows one kernel does the product and the gating; otherwise the product
     is followed by the gating kernel."""
@@ -236,7 +238,7 @@ def gated_linear(x, w_gate_up):
         raise KernelError(f"gated_linear: x {tuple(x.shape)} does not match W {tuple(w_gate_up.shape)}")
     if x.dtype == torch.bfloat16 and x.shape[0] > 0:
         from . import gemm_skinny
-        y = gemm_skinny.maybe_run(x, w_gate_up, x.dtype, fuse_swiglu=True)
+        y = gemm_skinny.maybe_run(x, w_gate_up, x.dtype, fuse_swiglu=True, resident=resident)
         if y is not None:
             return y
     return swiglu(linear(x, w_gate_up))

@@ -64,10 +64,10 @@ class AttentionMixer(Mixer):
     def forward(self, x, step, cache_view):
         qd, kvd = self.q_dim, self.kv_dim
         if cache_view.writes:
-            qkv = ops.linear(x, self.w_qkv)
+            qkv = ops.linear(x, self.w_qkv, resident=True)
             q, k, v = qkv[:, :qd], qkv[:, qd:qd + kvd], qkv[:, qd + kvd:]
         else:                                   # reads another execution's cache: only queries
-            q, k, v = ops.linear(x, self.w_qkv[:qd]), None, None
+            q, k, v = ops.linear(x, self.w_qkv[:qd], resident=True), None, None
         fused = self.position.fused_rotary()
         if fused is None:
             self.position.apply(q, k, step.token_pos)
@@ -81,7 +81,7 @@ class AttentionMixer(Mixer):
         a = ops.attention(q, cache_view.k, cache_view.v, step.token_seq, step.token_pos,
                           cache_view.block_table, self.n_heads, self.n_kv_heads, self.head_dim,
                           self.scale, int(self.window or 0), plan=step.attention_plan)
-        return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE)
+        return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True)
 
 
 register_mixer("attention", AttentionMixer)

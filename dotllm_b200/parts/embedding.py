@@ -59,7 +59,7 @@ class LinearHead(Part):
 
     def forward(self, x):
         """[R, H] in the run dtype -> float32 logits [R, vocab]."""
-        return ops.linear(x, self.weight, out_dtype=torch.float32)
+        return ops.linear(x, self.weight, out_dtype=torch.float32, resident=True)
 
 
 register_embedding("token_embedding", TokenEmbedding)

@@ -39,7 +39,8 @@ class GatedFeedForward(FeedForward):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
     def forward(self, x):
-        return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down, out_dtype=BRANCH_DTYPE)
+        return ops.linear(ops.gated_linear(x, self.w_gate_up, resident=True), self.w_down, out_dtype=BRANCH_DTYPE,
+                          resident=True)
 
 
 register_feed_forward("gated_mlp", GatedFeedForward)

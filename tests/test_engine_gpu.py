@@ -213,3 +213,36 @@ def test_seeded_sampling_is_reproducible_and_batch_independent(tmp):
     assert [o.generated_token_ids for o in a] == [o.generated_token_ids for o in b]
     different = model.generate(prompts, [InferenceOptions(temperature=0.9, seed=99, max_tokens=10, stop_token_ids=[])] * 3)
     assert [o.generated_token_ids for o in different] != [o.generated_token_ids for o in a]
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_dependent_launch_changes_no_bit(tmp, which):
+    """Kernels that may begin before the kernel ahead of them has finished give the same logits,
+    bit for bit, as the same kernels launched strictly one after another - eagerly and from
+    captured graphs."""
+    from dotllm_b200 import StepEntry
+    from dotllm_b200.kernels import library
+    model, cfg, _, _ = load_pair(tmp, which, torch.bfloat16)
+    prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], seed=300 + n) for n in (70, 9, 100)]
+    follow = [tiny_models.random_tokens(12, cfg["vocab_size"], seed=400 + i) for i in range(3)]
+
+    def run(dependent, graphs):
+        library.set_dependent_launch(dependent)
+        try:
+            cache = model.new_cache(max_tokens=1024)
+            seqs = [cache.open_sequence() for _ in prompts]
+            outs = [model.step(cache, [StepEntry(s, p, [len(p) - 1]) for s, p in zip(seqs, prompts)])]
+            for t in range(12):
+                outs.append(model.step(cache, [StepEntry(s, [f[t]]) for s, f in zip(seqs, follow)], graphs=graphs))
+            for s in seqs:
+                cache.close_sequence(s)
+            return torch.cat(outs).clone()
+        finally:
+            library.set_dependent_launch(True)
+
+    for graphs in (False, True):
+        base = run(False, graphs)
+        got = run(True, graphs)
+        assert torch.equal(got, base), f"graphs={graphs}: max diff {(got - base).abs().max()}"
+        again = run(True, graphs)
+        assert torch.equal(got, again), f"graphs={graphs}: two runs differ by {(got - again).abs().max()}"

@@ -394,9 +394,14 @@ def _decode_plan(lengths):
 
 @pytest.mark.parametrize("nh,nkv,hd", [(6, 6, 32), (8, 2, 64), (32, 8, 128), (16, 1, 128), (12, 4, 96), (3, 1, 64)])
 @pytest.mark.parametrize("window", [0, 100])
-def test_attention_decode_split_keys(nh, nkv, hd, window):
-    """One token per sequence, lengths from 1 to several runs of keys, pages scattered, NaN in every
-    place that no live key holds."""
+@pytest.mark.parametrize("blocks", [0, 7, 1])
+def test_attention_decode_split_keys(nh, nkv, hd, window, blocks, monkeypatch):
+    """One token per sequence, lengths from 1 to many pages of keys, pages scattered, NaN in every
+    place that no live key holds.  The step's pages are cut into equal shares for every
+    multiprocessor, for 7 blocks (shares that hold whole sequences between two cut ones) and for
+    one block (nothing cut)."""
+    from dotllm_b200.kernels import attention_fast
+    monkeypatch.setattr(attention_fast, "DECODE_BLOCKS", blocks)
     lengths = [1, 31, 32, 33, 64, 65, 255, 256, 257, 700, 1500]
     k_pool, v_pool, table, dense = make_paged(len(lengths), lengths, nkv, hd, torch.bfloat16, seed=22)
     g = torch.Generator().manual_seed(23)
@@ -471,11 +476,12 @@ def test_attention_prefill_packed_unequal(nh, nkv, hd, window):
     close(fast, ref, 2 ** -9 * v_max + 1e-3, 2 ** -8)
 
 
-def test_attention_decode_long_runs(monkeypatch):
-    """Few sequences and long caches: every warp of the decode kernel takes several pages of a run
-    and a block takes several runs."""
+@pytest.mark.parametrize("blocks", [0, 3])
+def test_attention_decode_long_runs(monkeypatch, blocks):
+    """Few sequences and long caches: a (sequence, head) is spread over tens of blocks, or, with
+    three blocks, every warp takes hundreds of pages and the ring of stages wraps many times."""
     from dotllm_b200.kernels import attention_fast
-    monkeypatch.setattr(attention_fast, "RUNS_PER_BLOCK", 1)
+    monkeypatch.setattr(attention_fast, "DECODE_BLOCKS", blocks)
     nh, nkv, hd = 32, 8, 128
     lengths = [8192, 5001, 64]
     k_pool, v_pool, table, dense = make_paged(len(lengths), lengths, nkv, hd, torch.bfloat16, seed=25)
