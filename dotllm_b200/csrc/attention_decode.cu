@@ -35,7 +35,9 @@
 // One ring stage per consumer warp: warp w owns stage w and sees every phase of its barriers in
 // order.  (A warp that shared stages with others could fall two phases behind a barrier and
 // mistake an old completion for the one it waits for: mbarrier waits tell phases apart by parity only.)
+#ifndef AD_MAX_STAGES
 #define AD_MAX_STAGES 6                        // consumer warps = stages, as many as fit in shared memory
+#endif
 #define AD_THREADS (32 * (AD_MAX_STAGES + 1))  // the last warp is the producer
 #define AD_WAIT_CYCLES (1ll << 31)
 

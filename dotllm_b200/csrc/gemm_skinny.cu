@@ -27,8 +27,12 @@
 #include <mutex>
 #include <unordered_map>
 
+#ifndef GS_CONSUMERS
 #define GS_CONSUMERS 6
+#endif
+#ifndef GS_SLOTS
 #define GS_SLOTS 4                         // ring stages per consumer warp
+#endif
 #define GS_BK 256                          // k per chunk
 #define GS_STAGE_ELEMS (16 * GS_BK)         // a stage is the dense box the copy engine writes: [16 rows][256 k]
 #define GS_THREADS (32 * (GS_CONSUMERS + 1))

@@ -48,6 +48,32 @@ def _time(fn, iters, flush):
     return times[len(times) // 2], times[0]
 
 
+def _time_graph(fn, iters):
+    """Median time of one replay of ``fn`` captured as a CUDA graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
 SCATTER_PAGES = True       # pages of a sequence in random order (False: in the order they were taken)
 
 
@@ -111,6 +137,13 @@ def main(argv=None):
         ms, best = _time(fn, args.iters, flush)
         result.update(batch=b, context=ctx, bytes=nbytes, ms=ms, best_ms=best, gbs=nbytes / ms / 1e6,
                       frac_of_hbm=nbytes / ms / 1e6 / hbm)
+        # As a decode step issues it: launches back to back from a captured graph (no host in the
+        # timed region), each on its own cache (together larger than the L2).
+        copies = max(2, (300 << 20) // nbytes + 1)
+        caches = [(k_pool, v_pool, table)] + [_paged(b, ctx, nkv, hd, dev) for _ in range(copies - 1)]
+        chained = _time_graph(lambda: [ops.attention(q, kp, vp, seqs, pos, tb, nh, nkv, hd, 1 / math.sqrt(hd), 0, plan=plan)
+                                       for kp, vp, tb in caches], args.iters) / copies
+        result.update(chained_ms=chained, chained_gbs=nbytes / chained / 1e6, chained_frac_of_hbm=nbytes / chained / 1e6 / hbm)
     elif args.kernel == "attention_prefill":
         T = args.tokens
         k_pool, v_pool, table = _paged(1, T, nkv, hd, dev)
@@ -136,6 +169,18 @@ def main(argv=None):
         lib_fn = lambda: torch.mm(x, w.t())
         lib_ms, _ = _time(lib_fn, args.iters, flush)
         result["library_mm_ms"] = lib_ms
+        # The same product as a decode step issues it: launches back to back from a captured graph,
+        # each on a different copy of W (together larger than the L2), with and without the
+        # overlap of programmatic dependent launch.
+        copies = max(2, (300 << 20) // nbytes + 1)
+        ws = [w] + [w.clone() for _ in range(copies - 1)]
+        from . import library
+        for name, dependent in (("chained_ms", True), ("chained_serial_ms", False)):
+            library.set_dependent_launch(dependent)
+            result[name] = _time_graph(lambda: [gemm_skinny.run(x, wi, out_dtype, fuse_swiglu=args.gated, resident=True)
+                                                for wi in ws], args.iters) / copies
+        library.set_dependent_launch(True)
+        result["chained_gbs"] = nbytes / result["chained_ms"] / 1e6
     elif args.kernel == "norm":
         rows, width = args.rows, args.width
         res = torch.randn(rows, width, device=dev)
