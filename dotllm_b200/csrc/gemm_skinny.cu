@@ -234,6 +234,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const __nv_bfloat16
                 if (whole) {
                     gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, out_stride, tile, M, N, g, t);
                 } else {
+#ifndef GS_EXP_NO_FIXUP
                     // a warp's first tile may be shared with the share before, its last with the share after
                     const int which = (tile == begin / cpt) ? 0 : 1;
                     float* mine = partials + ((size_t)gw * 2 + which) * (NT * 4 * 32);
@@ -269,6 +270,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const __nv_bfloat16
                         }
                         gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, out_stride, tile, M, N, g, t);
                     }
+#endif
                 }
 #pragma unroll
                 for (int j = 0; j < NT; ++j)

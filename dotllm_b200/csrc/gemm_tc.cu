@@ -1,0 +1,395 @@
+// y = x W^T for many rows of x (prefill): a tcgen05 product with the accumulators in tensor memory.
+//
+// The reference runs its prefill projections through cuBLAS and gates the feed-forward with a
+// separate kernel (src/DotLLM.Cuda/CudaGemm.cs:29-40, native/kernels/swiglu.cu:7-41).  This kernel
+// is for the products where fusing pays: with W = [gate; up] the epilogue writes silu(gate) * up, so
+// the [T, 2I] intermediate never goes to memory.  It also takes the plain product.
+//
+// Shape: persistent, one block per multiprocessor, six warps with fixed roles.
+//   warp 0   one thread issues the tensor-map copies (TMA, 128-byte swizzle) of x and W tiles into a
+//            ring of four stages (x 128 x 64, W 256 x 64 bfloat16 = 48 KB a stage);
+//   warp 1   one thread issues tcgen05.mma (M 128, N 256, K 16; four per stage) into one of two
+//            accumulators of 256 columns in tensor memory, and commits each stage back to the ring;
+//   warps 2-5  the epilogue: each warp reads its 32 lanes (rows) of the finished accumulator with
+//            tcgen05.ld, converts (or gates) and stores, while the MMA warp fills the other one.
+// A tile is 128 rows of x by 256 rows of W (gated: 128 gate rows and the 128 matching up rows, 128
+// output columns).  Tiles are taken in row-of-x-fastest order, so that the blocks running at one
+// time share a panel of W in the L2.  Parts of a tile outside the matrices are read as zeros by the
+// copy engine and never stored.
+//
+// Every wait on an mbarrier is bounded (about a second of clock cycles); on expiry the kernel
+// records a code in `status`, stops issuing work, waits (bounded) for copies in flight, frees its
+// tensor memory and returns.
+#include "common.cuh"
+#include "tma.cuh"
+#include <mutex>
+#include <unordered_map>
+
+#define GT_BM 128
+#define GT_BN 256
+#define GT_BK 64
+#define GT_STAGES 4
+#define GT_THREADS 192
+#define GT_A_BYTES (GT_BM * GT_BK * 2)
+#define GT_B_BYTES (GT_BN * GT_BK * 2)
+#define GT_STAGE_BYTES (GT_A_BYTES + GT_B_BYTES)
+#define GT_TMEM_COLS 512
+#define GT_WAIT_CYCLES (1ll << 31)
+
+__device__ __forceinline__ uint32_t gt_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gt_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gt_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void gt_mbar_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(gt_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gt_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gt_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool gt_mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(gt_smem(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the phase did not complete in time or another thread already gave up.
+__device__ __forceinline__ bool gt_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* gave_up) {
+    if (gt_mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!gt_mbar_try(bar, parity)) {
+        if (*gave_up || clock64() - t0 > GT_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+
+// Shared-memory operand descriptor of a K-major tile in the 128-byte swizzle that the copy engine
+// writes: rows of 128 bytes, groups of 8 rows 1024 bytes apart (the stride offset), version 1.
+__device__ __forceinline__ uint64_t gt_operand_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);            // start address
+    d |= (uint64_t)1 << 16;                                   // leading offset: unused with a swizzle
+    d |= (uint64_t)(1024 >> 4) << 32;                         // stride offset between 8-row groups
+    d |= (uint64_t)1 << 46;                                   // descriptor version
+    d |= (uint64_t)2 << 61;                                   // 128-byte swizzle
+    return d;
+}
+
+// D (float32, tensor memory) (+)= A (bfloat16, K-major) x B^T (bfloat16, K-major), M 128, N 256, K 16.
+__device__ __forceinline__ void gt_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The barrier gets one arrival when every tcgen05.mma issued so far by this thread has finished.
+__device__ __forceinline__ void gt_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gt_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void gt_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void gt_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive float32 columns of this thread's lane of tensor memory.
+__device__ __forceinline__ void gt_tmem_load32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ uint32_t gt_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Store 32 consecutive outputs of one row, columns col0 .. col0+31, those below n_cols only.
+template <typename TOut>
+__device__ __forceinline__ void gt_store32(TOut* row_ptr, int col0, int n_cols, const float (&v)[32], bool vec_ok);
+template <>
+__device__ __forceinline__ void gt_store32<__nv_bfloat16>(__nv_bfloat16* row_ptr, int col0, int n_cols, const float (&v)[32],
+                                                          bool vec_ok) {
+    if (vec_ok && col0 + 32 <= n_cols) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 p;
+            p.x = gt_pack(v[8 * i], v[8 * i + 1]);
+            p.y = gt_pack(v[8 * i + 2], v[8 * i + 3]);
+            p.z = gt_pack(v[8 * i + 4], v[8 * i + 5]);
+            p.w = gt_pack(v[8 * i + 6], v[8 * i + 7]);
+            *reinterpret_cast<uint4*>(row_ptr + col0 + 8 * i) = p;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (col0 + i < n_cols) row_ptr[col0 + i] = __float2bfloat16_rn(v[i]);
+    }
+}
+template <>
+__device__ __forceinline__ void gt_store32<float>(float* row_ptr, int col0, int n_cols, const float (&v)[32], bool vec_ok) {
+    if (vec_ok && col0 + 32 <= n_cols) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(row_ptr + col0 + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (col0 + i < n_cols) row_ptr[col0 + i] = v[i];
+    }
+}
+
+// GATED: W is [2N, K], gate rows then up rows; a tile's accumulator holds 128 gate columns then the
+// 128 matching up columns, and the output tile is 128 columns wide.
+template <typename TOut, bool GATED>
+__global__ void __launch_bounds__(GT_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, TOut* __restrict__ out,
+               int out_stride, int M, int N, int K, int vec_ok, int* __restrict__ status) {
+    extern __shared__ unsigned char gt_smem_raw[];
+    // the swizzled tiles must start on 1024-byte boundaries
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)gt_smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[GT_STAGES], empty_bar[GT_STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_holder;
+    __shared__ volatile int gave_up;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int OUT_BN = GATED ? GT_BN / 2 : GT_BN;
+    const int tiles_m = (M + GT_BM - 1) / GT_BM;
+    const int tiles_n = (N + OUT_BN - 1) / OUT_BN;
+    const int n_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + GT_BK - 1) / GT_BK;
+
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int s = 0; s < GT_STAGES; ++s) {
+            gt_mbar_init(&full_bar[s], 1);
+            gt_mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            gt_mbar_init(&acc_full[b], 1);
+            gt_mbar_init(&acc_empty[b], 4);                   // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                                          // the MMA warp owns the tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gt_smem(&tmem_base_holder)),
+                     "r"((uint32_t)GT_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    gt_fence_before();
+    __syncthreads();
+    gt_fence_after();
+    const uint32_t tmem_base = tmem_base_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ copies
+        if (lane == 0) {
+            int it = 0;
+            bool stop = false;
+            for (int tile = blockIdx.x; tile < n_tiles && !stop; tile += gridDim.x) {
+                const int tm = tile % tiles_m, tn = tile / tiles_m;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % GT_STAGES;
+                    if (it >= GT_STAGES && !gt_mbar_wait(&empty_bar[s], ((it / GT_STAGES) - 1) & 1, &gave_up)) {
+                        if (!gave_up) atomicExch(status, 21);
+                        gave_up = 1;
+                        stop = true;
+                        break;
+                    }
+                    unsigned char* a = tiles + (size_t)s * GT_STAGE_BYTES;
+                    unsigned char* b = a + GT_A_BYTES;
+                    gt_mbar_expect(&full_bar[s], GT_STAGE_BYTES);
+                    dl_tma_load_2d(a, &tmap_x, kb * GT_BK, tm * GT_BM, &full_bar[s]);
+                    if (GATED) {
+                        dl_tma_load_2d(b, &tmap_w, kb * GT_BK, tn * OUT_BN, &full_bar[s]);
+                        dl_tma_load_2d(b + GT_B_BYTES / 2, &tmap_w, kb * GT_BK, N + tn * OUT_BN, &full_bar[s]);
+                    } else {
+                        dl_tma_load_2d(b, &tmap_w, kb * GT_BK, tn * GT_BN, &full_bar[s]);
+                    }
+                }
+            }
+            if (stop) {
+                // copies already issued must land before the block's shared memory is released
+                for (int i = max(0, it - GT_STAGES); i < it; ++i) {
+                    const long long t0 = clock64();
+                    while (!gt_mbar_try(&full_bar[i % GT_STAGES], (i / GT_STAGES) & 1) && clock64() - t0 < GT_WAIT_CYCLES) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ tensor-core issue
+        if (lane == 0) {
+            // instruction descriptor: float32 accumulate, bfloat16 A and B, both K-major, N 256, M 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(GT_BN >> 3) << 17) | ((uint32_t)(GT_BM >> 4) << 24);
+            int it = 0, local = 0;
+            bool stop = false;
+            for (int tile = blockIdx.x; tile < n_tiles && !stop; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (local >= 2 && !gt_mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, &gave_up)) {
+                    if (!gave_up) atomicExch(status, 22);
+                    gave_up = 1;
+                    break;
+                }
+                gt_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * GT_BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % GT_STAGES;
+                    if (!gt_mbar_wait(&full_bar[s], (it / GT_STAGES) & 1, &gave_up)) {
+                        if (!gave_up) atomicExch(status, 23);
+                        gave_up = 1;
+                        stop = true;
+                        break;
+                    }
+                    gt_fence_after();
+                    const uint32_t a_addr = gt_smem(tiles + (size_t)s * GT_STAGE_BYTES);
+                    const uint64_t a_desc = gt_operand_desc(a_addr), b_desc = gt_operand_desc(a_addr + GT_A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < GT_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled rows
+                        gt_mma(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                    gt_commit(&empty_bar[s]);                    // the stage is free once these MMAs have read it
+                }
+                if (!stop) gt_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue: warp w reads lanes 32 (w % 4) ..
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            const int buf = local & 1;
+            // the decision is the warp's: tcgen05.ld below needs all 32 lanes
+            const bool ready = gt_mbar_wait(&acc_full[buf], (local >> 1) & 1, &gave_up);
+            if (!__all_sync(0xffffffffu, ready)) {
+                if (lane == 0 && !gave_up) atomicExch(status, 24);
+                gave_up = 1;
+                break;
+            }
+            gt_fence_after();
+            const int row = tm * GT_BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * GT_BN);
+            TOut* row_ptr = out + (size_t)row * out_stride;
+            const int col_base = tn * OUT_BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < OUT_BN; c0 += 32) {
+                float v[32];
+                gt_tmem_load32(taddr + (uint32_t)c0, v);        // every lane of the warp takes part
+                if (GATED) {
+                    float u[32];
+                    gt_tmem_load32(taddr + (uint32_t)(GT_BN / 2 + c0), u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = v[i] * (1.0f / (1.0f + expf(-v[i]))) * u[i];
+                }
+                if (row < M && col_base + c0 < N) gt_store32<TOut>(row_ptr, col_base + c0, N, v, vec_ok != 0);
+            }
+            gt_fence_before();
+            __syncwarp();
+            if (lane == 0) gt_mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    gt_fence_before();
+    __syncthreads();                                         // nobody leaves while copies or MMAs may be in flight
+    if (warp == 1) {
+        gt_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)GT_TMEM_COLS) : "memory");
+    }
+}
+
+struct GtMapKey {
+    const void* base;
+    long long rows, cols, pitch;
+    int box_rows;
+    bool operator==(const GtMapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows;
+    }
+};
+struct GtMapKeyHash {
+    size_t operator()(const GtMapKey& k) const {
+        return std::hash<const void*>()(k.base) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 10007u) ^ ((size_t)k.pitch * 31u) ^
+               (size_t)k.box_rows;
+    }
+};
+
+// Tensor maps cost a driver call to encode; they are kept per (matrix, shape, box).
+static int gt_tensor_map(CUtensorMap* out, const void* base, long long rows, long long cols, long long pitch_bytes, int box_rows) {
+    static std::unordered_map<GtMapKey, CUtensorMap, GtMapKeyHash> maps;
+    static std::mutex maps_mutex;
+    std::lock_guard<std::mutex> lock(maps_mutex);
+    const GtMapKey key{base, rows, cols, pitch_bytes, box_rows};
+    auto it = maps.find(key);
+    if (it == maps.end()) {
+        CUtensorMap fresh;
+        if (dl_tmap_encode_2d_bf16(&fresh, base, (uint64_t)rows, (uint64_t)cols, (uint64_t)pitch_bytes, box_rows, GT_BK,
+                                   DL_TMAP_SWIZZLE_128B) != 0)
+            return DL_ERR_LAUNCH;
+        if (maps.size() > 4096) maps.clear();
+        it = maps.emplace(key, fresh).first;
+    }
+    *out = it->second;
+    return DL_OK;
+}
+
+template <typename TOut, bool GATED>
+static int gt_launch(cudaStream_t s, const void* x, int x_stride, const void* w, void* out, int out_stride, int M, int N, int K,
+                     int blocks, int* status) {
+    const size_t smem = (size_t)GT_STAGES * GT_STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TOut, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap tmap_x, tmap_w;
+    int rc = gt_tensor_map(&tmap_x, x, M, K, (long long)x_stride * 2, GT_BM);
+    if (rc != DL_OK) return rc;
+    rc = gt_tensor_map(&tmap_w, w, GATED ? 2ll * N : N, K, (long long)K * 2, GATED ? GT_BN / 2 : GT_BN);
+    if (rc != DL_OK) return rc;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return dl_fail(DL_ERR_LAUNCH, "gemm_tc: cannot query the device");
+    const int out_bn = GATED ? GT_BN / 2 : GT_BN;
+    const long long n_tiles = (long long)((M + GT_BM - 1) / GT_BM) * ((N + out_bn - 1) / out_bn);
+    if (blocks <= 0 || blocks > sms) blocks = sms;
+    if (blocks > n_tiles) blocks = (int)n_tiles;
+    const int elem = (int)sizeof(TOut);
+    const int vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)out_stride * elem) % 16 == 0) ? 1 : 0;
+    gemm_tc_kernel<TOut, GATED><<<blocks, GT_THREADS, smem, s>>>(tmap_x, tmap_w, (TOut*)out, out_stride, M, N, K, vec_ok, status);
+    DL_CHECK_LAUNCH("gemm_tc");
+    return DL_OK;
+}
+
+// x: bf16 [M, K], rows x_stride elements apart.  w: bf16, contiguous rows of K.
+// flags bit 0 (gated) clear: w is [N, K], out [M, N].  Set: w is [2N, K] (N gate rows, then N up
+// rows), out [M, N] = silu(x Wg^T) * (x Wu^T), bfloat16 only.
+// out_dtype: 0 = float32, 1 = bfloat16.  blocks: persistent blocks (<= 0: one per multiprocessor).
+// status: int32, set non-zero if a wait expired.
+extern "C" int dl_gemm_tc_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype, int out_stride, int M,
+                               int N, int K, int flags, int blocks, int* status, void* stream) {
+    DL_REQUIRE(M >= 1 && N >= 1 && K >= 8 && K % 8 == 0, "gemm_tc: M=%d N=%d K=%d (K must be a positive multiple of 8)", M, N, K);
+    DL_REQUIRE(x_stride >= K && x_stride % 8 == 0, "gemm_tc: row stride of x (%d) must be a multiple of 8 and at least K", x_stride);
+    DL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_tc: x and W must be 16-byte aligned");
+    DL_REQUIRE(out_stride >= N, "gemm_tc: out stride shorter than N");
+    DL_REQUIRE(out_dtype == DL_F32 || out_dtype == DL_BF16, "gemm_tc: out dtype %d", out_dtype);
+    DL_REQUIRE((flags & ~1) == 0, "gemm_tc: unknown flags %d", flags);
+    DL_REQUIRE(status != nullptr, "gemm_tc: needs a status word");
+    DL_REQUIRE((long long)M * out_stride < (1ll << 40), "gemm_tc: output too large");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (flags & 1) {
+        DL_REQUIRE(out_dtype == DL_BF16, "gemm_tc: the gated product writes bfloat16");
+        return gt_launch<__nv_bfloat16, true>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+    }
+    if (out_dtype == DL_F32) return gt_launch<float, false>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+    return gt_launch<__nv_bfloat16, false>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+}

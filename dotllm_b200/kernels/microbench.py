@@ -89,7 +89,7 @@ def _paged(batch, context, nkv, hd, dev):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_skinny", "norm", "rope"])
+    ap.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_skinny", "gemm_tc", "norm", "rope"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -181,6 +181,23 @@ def main(argv=None):
                                                 for wi in ws], args.iters) / copies
         library.set_dependent_launch(True)
         result["chained_gbs"] = nbytes / result["chained_ms"] / 1e6
+    elif args.kernel == "gemm_tc":
+        from . import gemm_tc
+        M, N, K = args.rows, args.n, args.k
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn((2 if args.gated else 1) * N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        out_dtype = torch.float32 if args.out_f32 else torch.bfloat16
+        fn = lambda: gemm_tc.run(x, w, out_dtype, fuse_swiglu=args.gated)
+        flops = 2 * M * w.shape[0] * K
+        ms, best = _time(fn, args.iters, flush)
+        result.update(rows=M, n=N, k=K, gated=args.gated, flops=flops, ms=ms, best_ms=best, tflops=flops / ms / 1e9,
+                      frac_of_bf16_peak=flops / ms / 1e9 / tflops)
+        if args.gated:
+            lib_fn = lambda: ops.swiglu(torch.mm(x, w.t()))
+        else:
+            lib_fn = lambda: torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else torch.mm(x, w.t(), out_dtype=out_dtype)
+        lib_ms, _ = _time(lib_fn, args.iters, flush)
+        result.update(library_ms=lib_ms, library_tflops=flops / lib_ms / 1e9)
     elif args.kernel == "norm":
         rows, width = args.rows, args.width
         res = torch.randn(rows, width, device=dev)

@@ -359,6 +359,47 @@ def test_gemm_skinny(M, N, K, out_dtype):
     assert torch.equal(gemm_skinny.run(x.to(DEV), w.to(DEV), out_dtype).cpu(), y.cpu())
 
 
+@pytest.mark.parametrize("M,N,K", [(17, 64, 64), (128, 256, 64), (129, 257, 72), (300, 1000, 320), (2048, 384, 192),
+                                   (515, 4096, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("blocks", [0, 2])
+def test_gemm_tc(M, N, K, out_dtype, blocks, monkeypatch):
+    """The tcgen05 product at sizes that are no multiple of its 128 x 256 x 64 tile, with all
+    multiprocessors and with two blocks (many tiles per block: the stage ring wraps and both
+    accumulators in tensor memory are reused)."""
+    from dotllm_b200.kernels import gemm_tc, library
+    monkeypatch.setattr(gemm_tc, "BLOCKS", blocks)
+    g = torch.Generator().manual_seed(40)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    assert gemm_tc.takes(x.to(DEV), w.to(DEV))
+    y = gemm_tc.run(x.to(DEV), w.to(DEV), out_dtype)
+    library.check_status()
+    ref = (x.double() @ w.double().T).float()
+    close(y, ref, 2e-4 * math.sqrt(K / 64), 2 ** -8 if out_dtype == torch.bfloat16 else 1e-5)
+    assert torch.equal(gemm_tc.run(x.to(DEV), w.to(DEV), out_dtype).cpu(), y.cpu())
+    # rows of a wider buffer (a row stride larger than K)
+    wide = torch.zeros(M, K + 8, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = x.to(DEV)
+    assert torch.equal(gemm_tc.run(wide[:, :K], w.to(DEV), out_dtype).cpu(), y.cpu())
+
+
+@pytest.mark.parametrize("M,I,K", [(40, 176, 64), (300, 720, 320), (2048, 1024, 256), (130, 14336, 128)])
+@pytest.mark.parametrize("blocks", [0, 3])
+def test_gemm_tc_gated(M, I, K, blocks, monkeypatch):
+    from dotllm_b200.kernels import gemm_tc, library
+    monkeypatch.setattr(gemm_tc, "BLOCKS", blocks)
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, generator=g) * 0.1).to(torch.bfloat16)
+    gu = x.double() @ w.double().T
+    ref = plain_llama.swiglu(gu[:, :I].float(), gu[:, I:].float())
+    y = gemm_tc.run(x.to(DEV), w.to(DEV), torch.bfloat16, fuse_swiglu=True)
+    library.check_status()
+    assert y.shape == (M, I)
+    close(y, ref, 2e-4, 2 ** -8)
+
+
 @pytest.mark.parametrize("M", [1, 5, 16, 40])
 @pytest.mark.parametrize("I,K", [(176, 64), (512, 192), (720, 320), (14336, 256)])
 def test_gemm_skinny_gated(M, I, K):
