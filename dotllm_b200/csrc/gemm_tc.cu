@@ -22,6 +22,7 @@
 // tensor memory and returns.
 #include "common.cuh"
 #include "tma.cuh"
+#include "tcgen05.cuh"
 #include <mutex>
 #include <unordered_map>
 
@@ -34,81 +35,6 @@
 #define GT_B_BYTES (GT_BN * GT_BK * 2)
 #define GT_STAGE_BYTES (GT_A_BYTES + GT_B_BYTES)
 #define GT_TMEM_COLS 512
-#define GT_WAIT_CYCLES (1ll << 31)
-
-__device__ __forceinline__ uint32_t gt_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void gt_mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gt_smem(bar)), "r"(count));
-}
-__device__ __forceinline__ void gt_mbar_expect(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(gt_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void gt_mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gt_smem(bar)) : "memory");
-}
-__device__ __forceinline__ bool gt_mbar_try(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(gt_smem(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the phase did not complete in time or another thread already gave up.
-__device__ __forceinline__ bool gt_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* gave_up) {
-    if (gt_mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!gt_mbar_try(bar, parity)) {
-        if (*gave_up || clock64() - t0 > GT_WAIT_CYCLES) return false;
-    }
-    return true;
-}
-
-// Shared-memory operand descriptor of a K-major tile in the 128-byte swizzle that the copy engine
-// writes: rows of 128 bytes, groups of 8 rows 1024 bytes apart (the stride offset), version 1.
-__device__ __forceinline__ uint64_t gt_operand_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);            // start address
-    d |= (uint64_t)1 << 16;                                   // leading offset: unused with a swizzle
-    d |= (uint64_t)(1024 >> 4) << 32;                         // stride offset between 8-row groups
-    d |= (uint64_t)1 << 46;                                   // descriptor version
-    d |= (uint64_t)2 << 61;                                   // 128-byte swizzle
-    return d;
-}
-
-// D (float32, tensor memory) (+)= A (bfloat16, K-major) x B^T (bfloat16, K-major), M 128, N 256, K 16.
-__device__ __forceinline__ void gt_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// The barrier gets one arrival when every tcgen05.mma issued so far by this thread has finished.
-__device__ __forceinline__ void gt_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gt_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void gt_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void gt_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// 32 consecutive float32 columns of this thread's lane of tensor memory.
-__device__ __forceinline__ void gt_tmem_load32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 __device__ __forceinline__ uint32_t gt_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -173,24 +99,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     if (threadIdx.x == 0) {
         gave_up = 0;
         for (int s = 0; s < GT_STAGES; ++s) {
-            gt_mbar_init(&full_bar[s], 1);
-            gt_mbar_init(&empty_bar[s], 1);
+            tc_mbar_init(&full_bar[s], 1);
+            tc_mbar_init(&empty_bar[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            gt_mbar_init(&acc_full[b], 1);
-            gt_mbar_init(&acc_empty[b], 4);                   // one arrival per epilogue warp
+            tc_mbar_init(&acc_full[b], 1);
+            tc_mbar_init(&acc_empty[b], 4);                   // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                                          // the MMA warp owns the tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gt_smem(&tmem_base_holder)),
-                     "r"((uint32_t)GT_TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tc_tmem_alloc(&tmem_base_holder, GT_TMEM_COLS);
     }
-    gt_fence_before();
+    tc_fence_before();
     __syncthreads();
-    gt_fence_after();
+    tc_fence_after();
     const uint32_t tmem_base = tmem_base_holder;
 
     if (warp == 0) {
@@ -202,7 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 const int tm = tile % tiles_m, tn = tile / tiles_m;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % GT_STAGES;
-                    if (it >= GT_STAGES && !gt_mbar_wait(&empty_bar[s], ((it / GT_STAGES) - 1) & 1, &gave_up)) {
+                    if (it >= GT_STAGES && !tc_mbar_wait(&empty_bar[s], ((it / GT_STAGES) - 1) & 1, &gave_up)) {
                         if (!gave_up) atomicExch(status, 21);
                         gave_up = 1;
                         stop = true;
@@ -210,7 +133,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     }
                     unsigned char* a = tiles + (size_t)s * GT_STAGE_BYTES;
                     unsigned char* b = a + GT_A_BYTES;
-                    gt_mbar_expect(&full_bar[s], GT_STAGE_BYTES);
+                    tc_mbar_expect(&full_bar[s], GT_STAGE_BYTES);
                     dl_tma_load_2d(a, &tmap_x, kb * GT_BK, tm * GT_BM, &full_bar[s]);
                     if (GATED) {
                         dl_tma_load_2d(b, &tmap_w, kb * GT_BK, tn * OUT_BN, &full_bar[s]);
@@ -224,7 +147,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 // copies already issued must land before the block's shared memory is released
                 for (int i = max(0, it - GT_STAGES); i < it; ++i) {
                     const long long t0 = clock64();
-                    while (!gt_mbar_try(&full_bar[i % GT_STAGES], (i / GT_STAGES) & 1) && clock64() - t0 < GT_WAIT_CYCLES) {}
+                    while (!tc_mbar_try(&full_bar[i % GT_STAGES], (i / GT_STAGES) & 1) && clock64() - t0 < TC_WAIT_CYCLES) {}
                 }
             }
         }
@@ -232,35 +155,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         // ------------------------------------------------------------ tensor-core issue
         if (lane == 0) {
             // instruction descriptor: float32 accumulate, bfloat16 A and B, both K-major, N 256, M 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(GT_BN >> 3) << 17) | ((uint32_t)(GT_BM >> 4) << 24);
+            const uint32_t idesc = tc_idesc_bf16(GT_BM, GT_BN);
             int it = 0, local = 0;
             bool stop = false;
             for (int tile = blockIdx.x; tile < n_tiles && !stop; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
-                if (local >= 2 && !gt_mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, &gave_up)) {
+                if (local >= 2 && !tc_mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, &gave_up)) {
                     if (!gave_up) atomicExch(status, 22);
                     gave_up = 1;
                     break;
                 }
-                gt_fence_after();
+                tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * GT_BN);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % GT_STAGES;
-                    if (!gt_mbar_wait(&full_bar[s], (it / GT_STAGES) & 1, &gave_up)) {
+                    if (!tc_mbar_wait(&full_bar[s], (it / GT_STAGES) & 1, &gave_up)) {
                         if (!gave_up) atomicExch(status, 23);
                         gave_up = 1;
                         stop = true;
                         break;
                     }
-                    gt_fence_after();
-                    const uint32_t a_addr = gt_smem(tiles + (size_t)s * GT_STAGE_BYTES);
-                    const uint64_t a_desc = gt_operand_desc(a_addr), b_desc = gt_operand_desc(a_addr + GT_A_BYTES);
+                    tc_fence_after();
+                    const uint32_t a_addr = tc_smem(tiles + (size_t)s * GT_STAGE_BYTES);
+                    const uint64_t a_desc = tc_operand_desc(a_addr), b_desc = tc_operand_desc(a_addr + GT_A_BYTES);
 #pragma unroll
                     for (int k = 0; k < GT_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled rows
-                        gt_mma(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
-                    gt_commit(&empty_bar[s]);                    // the stage is free once these MMAs have read it
+                        tc_mma(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                    tc_commit(&empty_bar[s]);                    // the stage is free once these MMAs have read it
                 }
-                if (!stop) gt_commit(&acc_full[buf]);
+                if (!stop) tc_commit(&acc_full[buf]);
             }
         }
     } else {
@@ -271,13 +194,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int buf = local & 1;
             // the decision is the warp's: tcgen05.ld below needs all 32 lanes
-            const bool ready = gt_mbar_wait(&acc_full[buf], (local >> 1) & 1, &gave_up);
+            const bool ready = tc_mbar_wait(&acc_full[buf], (local >> 1) & 1, &gave_up);
             if (!__all_sync(0xffffffffu, ready)) {
                 if (lane == 0 && !gave_up) atomicExch(status, 24);
                 gave_up = 1;
                 break;
             }
-            gt_fence_after();
+            tc_fence_after();
             const int row = tm * GT_BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * GT_BN);
             TOut* row_ptr = out + (size_t)row * out_stride;
@@ -285,25 +208,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 #pragma unroll 1
             for (int c0 = 0; c0 < OUT_BN; c0 += 32) {
                 float v[32];
-                gt_tmem_load32(taddr + (uint32_t)c0, v);        // every lane of the warp takes part
+                tc_tmem_load32(taddr + (uint32_t)c0, v);        // every lane of the warp takes part
                 if (GATED) {
                     float u[32];
-                    gt_tmem_load32(taddr + (uint32_t)(GT_BN / 2 + c0), u);
+                    tc_tmem_load32(taddr + (uint32_t)(GT_BN / 2 + c0), u);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = v[i] * (1.0f / (1.0f + expf(-v[i]))) * u[i];
                 }
                 if (row < M && col_base + c0 < N) gt_store32<TOut>(row_ptr, col_base + c0, N, v, vec_ok != 0);
             }
-            gt_fence_before();
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) gt_mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) tc_mbar_arrive(&acc_empty[buf]);
         }
     }
-    gt_fence_before();
+    tc_fence_before();
     __syncthreads();                                         // nobody leaves while copies or MMAs may be in flight
     if (warp == 1) {
-        gt_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)GT_TMEM_COLS) : "memory");
+        tc_fence_after();
+        tc_tmem_free(tmem_base, GT_TMEM_COLS);
     }
 }
 

@@ -17,9 +17,13 @@ _library.register_signatures({
                                  _P, _P, _I, _P, _P],
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                   _F, _I, _P, _P],
+    "dl_attention_prefill_tc_bf16": [_P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
+                                     _F, _I, _P, _P],
 })
 
-PREFILL_ROWS = 128       # query rows per block of the prefill kernel (AP_ROWS)
+PREFILL_ROWS = 128       # query rows per block of the prefill kernels (AP_ROWS, PT_ROWS)
+PREFILL_TC_HEAD_DIMS = (64, 128)     # head sizes of the tcgen05 prefill kernel; others take the mma.sync one
+PREFILL_TC = True        # False: always the mma.sync kernel (tests compare the two)
 
 DECODE_HEAD_DIMS = (32, 64, 96, 128)
 DECODE_BLOCKS = 0        # > 0: persistent blocks of the decode kernel (tuning and tests); 0: one per multiprocessor
@@ -61,6 +65,13 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
         dev = host.pin_memory().to(q.device, non_blocking=True)
         plan.scratch["prefill_tiles"] = (dev[:len(tile_seq)], dev[len(tile_seq):], len(tile_seq))
     tile_seq, tile_row0, n_tiles = plan.scratch["prefill_tiles"]
+    if PREFILL_TC and head_dim in PREFILL_TC_HEAD_DIMS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+        _library.call("dl_attention_prefill_tc_bf16", q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0),
+                      k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),
+                      n_tiles, plan.seq_start.data_ptr(), plan.seq_new.data_ptr(), plan.cu_new.data_ptr(),
+                      block_table.data_ptr(), block_table.shape[1], n_heads, n_kv_heads, head_dim, scale, window,
+                      _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        return True
     _library.call("dl_attention_prefill_bf16", q.data_ptr(), q_stride, out.data_ptr(), out.stride(0),
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),
                   n_tiles, plan.seq_start.data_ptr(), plan.seq_new.data_ptr(), plan.cu_new.data_ptr(),

@@ -230,8 +230,9 @@ def linear(x, w, out_dtype=None, resident=False):
 
 def gated_linear(x, w_gate_up, resident=False):
     """silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu] of shape [2I, K]; returns [T, I] in x's dtype.
-    For a few bfloat16 rows one kernel does the product and the gating; otherwise the product
-    is followed by the gating kernel."""
+    In bfloat16 one kernel does the product and the gating in float32: the weight-streaming
+    kernel for a few rows, the tcgen05 kernel for many.  In float32 the product is followed by
+    the gating kernel."""
     _need_cuda(x, w_gate_up)
     if w_gate_up.dim() != 2 or w_gate_up.shape[0] % 2 or not w_gate_up.is_contiguous() or x.dim() != 2 \
             or x.shape[1] != w_gate_up.shape[1]:
@@ -241,6 +242,9 @@ def gated_linear(x, w_gate_up, resident=False):
         y = gemm_skinny.maybe_run(x, w_gate_up, x.dtype, fuse_swiglu=True, resident=resident)
         if y is not None:
             return y
+        from . import gemm_tc
+        if gemm_tc.takes(x, w_gate_up, fuse_swiglu=True):
+            return gemm_tc.run(x, w_gate_up, x.dtype, fuse_swiglu=True)
     return swiglu(linear(x, w_gate_up))
 
 

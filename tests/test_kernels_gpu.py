@@ -491,8 +491,12 @@ def _prefill_plan(lengths, news):
 
 @pytest.mark.parametrize("nh,nkv,hd", [(6, 6, 32), (8, 2, 64), (8, 2, 128), (5, 1, 96)])
 @pytest.mark.parametrize("window", [0, 90])
-def test_attention_prefill_packed_unequal(nh, nkv, hd, window):
-    """Whole prompts, a chunk appended to earlier context, and single tokens in one packed call."""
+@pytest.mark.parametrize("tc", [True, False])
+def test_attention_prefill_packed_unequal(nh, nkv, hd, window, tc, monkeypatch):
+    """Whole prompts, a chunk appended to earlier context, and single tokens in one packed call:
+    by the tcgen05 kernel (head sizes 64 and 128) and by the mma.sync kernel (every size)."""
+    from dotllm_b200.kernels import attention_fast
+    monkeypatch.setattr(attention_fast, "PREFILL_TC", tc)
     lengths = [1, 70, 333, 64, 500, 129]
     news = [1, 70, 33, 1, 500, 65]
     k_pool, v_pool, table, dense = make_paged(len(lengths), lengths, nkv, hd, torch.bfloat16, seed=30)
@@ -515,6 +519,37 @@ def test_attention_prefill_packed_unequal(nh, nkv, hd, window):
     # rounding to nearest) for the P V product: |error| <= 2^-9 max|v|, plus the output's rounding.
     v_max = max(float(v.abs().max()) for _, v in dense)
     close(fast, ref, 2 ** -9 * v_max + 1e-3, 2 ** -8)
+    from dotllm_b200.kernels import library
+    library.check_status()
+
+
+@pytest.mark.parametrize("hd,window", [(128, 0), (64, 0), (128, 700)])
+def test_attention_prefill_tc_long_prompt(hd, window):
+    """A prompt of 40 pages appended to 3 pages of context: the stage ring of the tcgen05 kernel
+    wraps many times, both score buffers and both weight buffers are reused, and one far key per
+    head carries a large score, so that a lost page or a wrong rescale of the running output shows.
+    Compared with the generic kernel (one warp per token and head, float32 softmax)."""
+    from dotllm_b200.kernels import library
+    nh, nkv = 4, 2
+    start, new = 170, 2500
+    lengths, news = [start + new], [new]
+    k_pool, v_pool, table, dense = make_paged(1, lengths, nkv, hd, torch.bfloat16, seed=33)
+    g = torch.Generator().manual_seed(34)
+    q = torch.randn(new, nh * hd, generator=g).to(torch.bfloat16)
+    # rows from position 2000 on look for key 1234 of their KV head (unless the window hides it)
+    k_dense = dense[0][0]
+    for h in range(nh):
+        q[2000 - start:, h * hd:(h + 1) * hd] = (k_dense[1234, h // (nh // nkv)].float() * 3.0).to(torch.bfloat16)
+    token_seq = torch.zeros(new, dtype=torch.int32, device=DEV)
+    token_pos = torch.arange(start, start + new, dtype=torch.int32, device=DEV)
+    args = (q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), token_seq, token_pos, table.to(DEV), nh, nkv, hd,
+            1.0 / math.sqrt(hd), window)
+    fast = ops().attention(*args, plan=_prefill_plan(lengths, news))
+    library.check_status()
+    generic = ops().attention(*args)
+    assert bool(torch.isfinite(fast).all())
+    v_max = float(dense[0][1].abs().max())
+    close(fast, generic, 2 ** -9 * v_max + 2e-3, 2 ** -7)
 
 
 @pytest.mark.parametrize("blocks", [0, 3])
