@@ -105,6 +105,7 @@ def main():
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=LLAMA_31_8B["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points and the prefill")
+    ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill (for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -151,11 +152,7 @@ def main():
     def counting_call(name, *a):
         launches["n"] += 1
         return real_call(name, *a)
-    library.call = counting_call
-    ops._library.call = counting_call
-    from dotllm_b200.kernels import attention_fast, gemm_skinny
-    attention_fast._library.call = counting_call
-    gemm_skinny._library.call = counting_call
+    library.call = counting_call                           # every kernel module calls through library.call
 
     def decode_point(batch, measure_e2e):
         seqs = [cache.open_sequence() for _ in range(batch)]
@@ -200,15 +197,8 @@ def main():
             cache.close_sequence(s)
         return result
 
-    main_point = decode_point(args.batch, True)
-    points = {}
-    prefill = None
-    if not args.no_points:
-        for b in batches:
-            if b != args.batch:
-                points[f"decode_b{b}"] = round(decode_point(b, False)["tok_s"], 1)
-        points[f"decode_b{args.batch}"] = round(main_point["tok_s"], 1)
-        # ---- prefill of one 2,048-token prompt
+    def prefill_point():
+        """One prompt of PREFILL_TOKENS tokens through model.step: best of three after three warm-ups."""
         prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
         times = []
         for it in range(3 + 3):
@@ -227,8 +217,22 @@ def main():
         per_layer = 2 * T * (cfg.hidden_size * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.hidden_size
                              + 3 * cfg.hidden_size * cfg.intermediate_size) + 2 * T * T * cfg.q_dim
         flops = cfg.num_hidden_layers * per_layer + 2 * cfg.hidden_size * vocab
-        prefill = {"value": round(T * 1000.0 / p_ms, 1), "tokens": T, "ms": round(p_ms, 3),
-                   "frac": round(flops / (p_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "peak": pk["source"]}
+        return {"value": round(T * 1000.0 / p_ms, 1), "tokens": T, "ms": round(p_ms, 3),
+                "frac": round(flops / (p_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "peak": pk["source"]}
+
+    if args.only_prefill:
+        print(json.dumps({"prefill": prefill_point(), "layers": cfg.num_hidden_layers}))
+        return 0
+
+    main_point = decode_point(args.batch, True)
+    points = {}
+    prefill = None
+    if not args.no_points:
+        for b in batches:
+            if b != args.batch:
+                points[f"decode_b{b}"] = round(decode_point(b, False)["tok_s"], 1)
+        points[f"decode_b{args.batch}"] = round(main_point["tok_s"], 1)
+        prefill = prefill_point()
 
     step_bytes = weight_bytes + args.batch * main_point["mean_len"] * kv_bytes_per_token
     achieved = step_bytes / (main_point["ms"] * 1e-3) / 1e9

@@ -8,6 +8,11 @@
 // rotated in place and rotated K goes straight to its cache page.  V pages are transposed.
 #include "common.cuh"
 
+// The rotation, written with explicit roundings so that both kernels below (and any compiler
+// version) produce the same bits: no contraction into fused multiply-adds.
+__device__ __forceinline__ float rope_lo(float x0, float x1, float c, float s) { return __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)); }
+__device__ __forceinline__ float rope_hi(float x0, float x1, float c, float s) { return __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)); }
+
 // Grid: (token, head) with the query heads first, then the KV heads; a block's threads each take
 // one rotation pair (query heads) or one dimension (KV heads), so a decode step's handful of
 // tokens still spreads over hundreds of blocks and no thread loops over dependent loads.
@@ -33,8 +38,8 @@ rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float x0 = dl_to_f32<T>(p[i]), x1 = dl_to_f32<T>(p[i + half]);
             const float c = cs[i], s = sn[i];
-            p[i] = dl_from_f32<T>(x0 * c - x1 * s);
-            p[i + half] = dl_from_f32<T>(x0 * s + x1 * c);
+            p[i] = dl_from_f32<T>(rope_lo(x0, x1, c, s));
+            p[i + half] = dl_from_f32<T>(rope_hi(x0, x1, c, s));
         }
         return;
     }
@@ -50,15 +55,97 @@ rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float kv;
         if (d < half) {
-            kv = dl_to_f32<T>(krow[d]) * cs[d] - dl_to_f32<T>(krow[d + half]) * sn[d];
+            kv = rope_lo(dl_to_f32<T>(krow[d]), dl_to_f32<T>(krow[d + half]), cs[d], sn[d]);
         } else if (d < 2 * half) {
             const int i = d - half;
-            kv = dl_to_f32<T>(krow[i]) * sn[i] + dl_to_f32<T>(krow[d]) * cs[i];
+            kv = rope_hi(dl_to_f32<T>(krow[i]), dl_to_f32<T>(krow[d]), cs[i], sn[i]);
         } else {
             kv = dl_to_f32<T>(krow[d]);
         }
         kdst[d] = dl_from_f32<T>(kv);
         v_pool[dl_v_offset(page, nkv, h, d, hd) + in_page] = vrow[d];
+    }
+}
+
+// The same work for steps of many tokens (prefill).  Grid: (tile of 64 packed tokens, head).  A
+// block of a KV head stages the tile's V rows in shared memory and writes them transposed, token
+// fastest, so that the tokens of one page (consecutive positions of one sequence) fill whole
+// 128-byte lines of the transposed V page instead of one 2-byte element each.
+#define RT_TOKENS 64
+#define RT_THREADS 256
+template <typename T>
+__global__ void __launch_bounds__(RT_THREADS)
+rope_cache_write_tile_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                             const T* __restrict__ v, int v_stride, const float* __restrict__ cos_t,
+                             const float* __restrict__ sin_t, int rotary_dim, int table_rows,
+                             const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
+                             const int32_t* __restrict__ block_table, int bt_stride, T* __restrict__ k_pool,
+                             T* __restrict__ v_pool, int n_pages, int n_tokens, int nh, int nkv, int hd, int write_cache) {
+    extern __shared__ __align__(16) unsigned char rt_raw[];
+    T* tile = reinterpret_cast<T*>(rt_raw);                  // [64 tokens][hd + pad]: V rows of one KV head
+    __shared__ int s_pos[RT_TOKENS], s_page[RT_TOKENS];
+    dl_launch_dependents();
+    dl_grid_dependency_wait();
+    const int t0 = blockIdx.x * RT_TOKENS;
+    const int nt = min(RT_TOKENS, n_tokens - t0);
+    const int half = rotary_dim / 2;
+    const bool is_q = (int)blockIdx.y < nh;
+    const int pitch = hd + (int)(4 / sizeof(T));             // an odd number of 32-bit words: no bank conflicts on the transpose
+    if (threadIdx.x < RT_TOKENS) {
+        int pos = -1, page = -1;
+        if ((int)threadIdx.x < nt) {
+            pos = token_pos[t0 + threadIdx.x];
+            if (pos < 0 || (half > 0 && pos >= table_rows)) pos = -1;    // host-validated; never index outside
+            if (pos >= 0 && !is_q && write_cache) {
+                page = block_table[(size_t)token_seq[t0 + threadIdx.x] * bt_stride + pos / DL_PAGE];
+                if (page < 0 || page >= n_pages) page = -1;
+            }
+        }
+        s_pos[threadIdx.x] = pos;
+        s_page[threadIdx.x] = page;
+    }
+    __syncthreads();
+    if (is_q) {                                              // a query head: rotate in place
+        for (int idx = threadIdx.x; idx < nt * half; idx += RT_THREADS) {
+            const int i = idx / half, p = idx - i * half;
+            const int pos = s_pos[i];
+            if (pos < 0) continue;
+            T* row = q + (size_t)(t0 + i) * q_stride + (size_t)blockIdx.y * hd;
+            const float x0 = dl_to_f32<T>(row[p]), x1 = dl_to_f32<T>(row[p + half]);
+            const float c = cos_t[(size_t)pos * half + p], s = sin_t[(size_t)pos * half + p];
+            row[p] = dl_from_f32<T>(rope_lo(x0, x1, c, s));
+            row[p + half] = dl_from_f32<T>(rope_hi(x0, x1, c, s));
+        }
+        return;
+    }
+    if (!write_cache) return;
+    const int h = blockIdx.y - nh;                           // a KV head: rotate K on its way to the page, stage V
+    for (int idx = threadIdx.x; idx < nt * hd; idx += RT_THREADS) {
+        const int i = idx / hd, d = idx - i * hd;
+        const int page = s_page[i], pos = s_pos[i];
+        tile[i * pitch + d] = v[(size_t)(t0 + i) * v_stride + (size_t)h * hd + d];
+        if (page < 0) continue;
+        const T* krow = k + (size_t)(t0 + i) * k_stride + (size_t)h * hd;
+        const float* cs = cos_t + (size_t)pos * half;
+        const float* sn = sin_t + (size_t)pos * half;
+        float kv;
+        if (d < half) {
+            kv = rope_lo(dl_to_f32<T>(krow[d]), dl_to_f32<T>(krow[d + half]), cs[d], sn[d]);
+        } else if (d < 2 * half) {
+            const int j = d - half;
+            kv = rope_hi(dl_to_f32<T>(krow[j]), dl_to_f32<T>(krow[d]), cs[j], sn[j]);
+        } else {
+            kv = dl_to_f32<T>(krow[d]);
+        }
+        k_pool[dl_k_offset(page, nkv, h, pos % DL_PAGE, hd) + d] = dl_from_f32<T>(kv);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < RT_TOKENS * hd; idx += RT_THREADS) {    // token fastest
+        const int i = idx % RT_TOKENS, d = idx / RT_TOKENS;
+        if (i >= nt) continue;
+        const int page = s_page[i];
+        if (page < 0) continue;
+        v_pool[dl_v_offset(page, nkv, h, d, hd) + (s_pos[i] % DL_PAGE)] = tile[i * pitch + d];
     }
 }
 
@@ -79,8 +166,26 @@ extern "C" int dl_rope_cache_write(void* q, int q_stride, const void* k, int k_s
     if (n_tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     DL_REQUIRE(nh + nkv <= 65535, "rope_cache_write: too many heads");
-    dim3 grid(n_tokens, write_cache ? nh + nkv : nh);
     cudaError_t e;
+    const size_t elem = dtype == DL_F32 ? 4 : 2;
+    const size_t tile_smem = (size_t)RT_TOKENS * (hd + 4 / elem) * elem;
+    if (n_tokens >= RT_TOKENS && tile_smem <= 48 * 1024 && (dtype == DL_F32 || dtype == DL_BF16)) {
+        dim3 tgrid((n_tokens + RT_TOKENS - 1) / RT_TOKENS, write_cache ? nh + nkv : nh);
+        if (dtype == DL_F32)
+            e = dl_launch_dependent(rope_cache_write_tile_kernel<float>, tgrid, dim3(RT_THREADS), tile_smem, s, (float*)q, q_stride,
+                                    (const float*)k, k_stride, (const float*)v, v_stride, cos_t, sin_t, rotary_dim, table_rows,
+                                    token_seq, token_pos, block_table, bt_stride, (float*)k_pool, (float*)v_pool, n_pages,
+                                    n_tokens, nh, nkv, hd, write_cache);
+        else
+            e = dl_launch_dependent(rope_cache_write_tile_kernel<__nv_bfloat16>, tgrid, dim3(RT_THREADS), tile_smem, s,
+                                    (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
+                                    v_stride, cos_t, sin_t, rotary_dim, table_rows, token_seq, token_pos, block_table,
+                                    bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, n_tokens, nh, nkv, hd,
+                                    write_cache);
+        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "rope_cache_write: %s", cudaGetErrorString(e));
+        return DL_OK;
+    }
+    dim3 grid(n_tokens, write_cache ? nh + nkv : nh);
     if (dtype == DL_F32)
         e = dl_launch_dependent(rope_cache_write_kernel<float>, grid, dim3(128), 0, s, (float*)q, q_stride, (const float*)k,
                                 k_stride, (const float*)v, v_stride, cos_t, sin_t, rotary_dim, table_rows, token_seq,

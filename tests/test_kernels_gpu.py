@@ -163,9 +163,12 @@ def test_attention_far_key_stands_out():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rd", [(4, 2, 16, 16), (6, 6, 32, 32), (8, 2, 64, 32), (3, 1, 48, 0)])
-def test_rope_cache_write(dtype, nh, nkv, hd, rd):
+@pytest.mark.parametrize("news", [[70, 1, 3], [20, 1, 3]])
+def test_rope_cache_write(dtype, nh, nkv, hd, rd, news):
+    """74 tokens take the kernel that works on tiles of 64 packed tokens (the second tile mixes
+    three sequences); 24 tokens take the kernel with one block per (token, head)."""
     g = torch.Generator().manual_seed(7)
-    lengths, news = [70, 5, 130], [70, 1, 3]
+    lengths = [70, 5, 130]
     token_seq, token_pos = [], []
     for b, (n, new) in enumerate(zip(lengths, news)):
         for p in range(n - new, n):
