@@ -105,6 +105,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--decode-blocks", type=int, default=0, help="attention_decode: persistent blocks (0: one per multiprocessor)")
+    ap.add_argument("--no-tc", action="store_true", help="attention_prefill: the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--sequential-pages", action="store_true", help="pages of a sequence lie one after another")
     args = ap.parse_args(argv)
     if args.sequential_pages:
@@ -145,6 +146,9 @@ def main(argv=None):
                                        for kp, vp, tb in caches], args.iters) / copies
         result.update(chained_ms=chained, chained_gbs=nbytes / chained / 1e6, chained_frac_of_hbm=nbytes / chained / 1e6 / hbm)
     elif args.kernel == "attention_prefill":
+        if args.no_tc:
+            from . import attention_fast
+            attention_fast.PREFILL_TC = False
         T = args.tokens
         k_pool, v_pool, table = _paged(1, T, nkv, hd, dev)
         q = torch.randn(T, nh * hd, device=dev, dtype=torch.bfloat16)
