@@ -494,6 +494,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         ad_mma(o[i2], pa[h][2][0], pa[h][2][1], pa[h][3][0], pa[h][3][1], v.z, v.w);
                     }
                 }
+                // The stage may be released only after every MMA fed from it has been issued (an MMA
+                // issues when its operands have arrived from shared memory).  The MMAs are not
+                // volatile, so pin their results here: the compiler cannot sink them below this point.
+#pragma unroll
+                for (int i2 = 0; i2 < DT; ++i2) asm volatile("" : "+f"(o[i2][0]), "+f"(o[i2][1]), "+f"(o[i2][2]), "+f"(o[i2][3]));
+                // ... and the reads themselves must be done before the copy engine may overwrite the stage:
+                // without this fence a slot that was refilled at once showed rows of the new chunk to the old reads.
+                __threadfence_block();
                 __syncwarp();
                 if (lane == 0) ad_mbar_arrive(&empty_bar[s]);
             }

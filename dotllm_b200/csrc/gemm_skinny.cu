@@ -113,172 +113,216 @@ __device__ __forceinline__ void gs_epilogue(const float (&acc)[NT][4], TOut* out
     }
 }
 
+// The product of a launch: its operands and how its chunks are cut (see GsPlan below).
+struct GsWork {
+    const __nv_bfloat16* x;
+    int x_stride;
+    void* out;
+    int out_stride;
+    int M, N, K, up_offset, cpt, total_chunks, share;
+};
+
+// The rings of a block: a private ring of GS_SLOTS stages per consumer warp.
+struct GsRings {
+    __nv_bfloat16* stage_mem;                               // [consumer][slot][16][GS_BK]
+    uint64_t (*full_bar)[GS_SLOTS];
+    uint64_t (*empty_bar)[GS_SLOTS];
+    volatile int* gave_up;
+    int* status;
+};
+
+// Producer lane `lane` (< GS_CONSUMERS) feeds consumer warp `lane`: it walks that warp's share chunk
+// by chunk, waits for the ring slot to be free, and issues one tiled copy (two for gate + up) per
+// chunk.  `cnt` counts the chunks of this ring.  False: gave up.
+template <bool FUSE_SWIGLU>
+__device__ __forceinline__ bool gs_produce(const CUtensorMap* tmap, const GsWork& w, const GsRings& r, int lane, int& cnt) {
+    const int gw = blockIdx.x * GS_CONSUMERS + lane;
+    int cur = min(w.total_chunks, gw * w.share);
+    const int end = min(w.total_chunks, (gw + 1) * w.share);
+    for (; cur < end; ++cur, ++cnt) {
+        const int slot = cnt % GS_SLOTS;
+        if (cnt >= GS_SLOTS && !gs_mbar_wait(&r.empty_bar[lane][slot], ((cnt / GS_SLOTS) - 1) & 1, r.gave_up)) {
+            if (!*r.gave_up) atomicExch(r.status, 1);
+            *r.gave_up = 1;
+            return false;
+        }
+        const int tile = cur / w.cpt, kc = cur - tile * w.cpt;
+        __nv_bfloat16* dst = r.stage_mem + (size_t)(lane * GS_SLOTS + slot) * GS_STAGE_ELEMS;
+        // a box is always written whole: parts outside the matrix arrive as zeros
+        gs_mbar_expect(&r.full_bar[lane][slot], GS_STAGE_ELEMS * 2);
+        if (FUSE_SWIGLU) {
+            dl_tma_load_2d(dst, tmap, kc * GS_BK, tile * 8, &r.full_bar[lane][slot]);
+            dl_tma_load_2d(dst + 8 * GS_BK, tmap, kc * GS_BK, w.up_offset + tile * 8, &r.full_bar[lane][slot]);
+        } else {
+            dl_tma_load_2d(dst, tmap, kc * GS_BK, tile * 16, &r.full_bar[lane][slot]);
+        }
+    }
+    return true;
+}
+
+// After giving up: copies already issued must land before the block's shared memory is released.
+__device__ __forceinline__ void gs_drain(const GsRings& r, int lane, int cnt) {
+    for (int i = max(0, cnt - GS_SLOTS); i < cnt; ++i) {
+        const long long t0 = clock64();
+        while (!gs_mbar_try(&r.full_bar[lane][i % GS_SLOTS], (i / GS_SLOTS) & 1) && clock64() - t0 < GS_WAIT_CYCLES) {}
+    }
+}
+
+// Consumer warp `warp` works through its share of the product.  `cnt` counts the chunks of its ring;
+// `dead` is set when a wait expired.
+template <int NT, typename TOut, bool FUSE_SWIGLU>
+__device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, float* __restrict__ partials,
+                                           int* __restrict__ counters, int warp, int lane, int& cnt, bool& dead) {
+    const int g = lane >> 2, t = lane & 3;
+    const int gw = blockIdx.x * GS_CONSUMERS + warp;
+    const int begin = min(w.total_chunks, gw * w.share), end = min(w.total_chunks, (gw + 1) * w.share);
+    const int cpt = w.cpt, share = w.share, M = w.M, N = w.N, K = w.K;
+    const __nv_bfloat16* x = w.x;
+    TOut* out = reinterpret_cast<TOut*>(w.out);
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+    int seg_begin = begin;                               // first chunk of the current tile's segment
+    for (int cur = begin; cur < end; ++cur, ++cnt) {
+        const int slot = cnt % GS_SLOTS;
+        const int tile = cur / cpt, kc = cur - tile * cpt;
+        const int k0 = kc * GS_BK;
+        // activations of this chunk, asked for before waiting on the weights
+        uint4 xf[GS_BK / 32][NT];
+#pragma unroll
+        for (int s = 0; s < GS_BK / 32; ++s)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int tok = j * 8 + g, k = k0 + 32 * s + 8 * t;
+                xf[s][j] = make_uint4(0u, 0u, 0u, 0u);
+                if (tok < M && k < K) xf[s][j] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)tok * w.x_stride + k));
+            }
+        if (!dead && !gs_mbar_wait(&r.full_bar[warp][slot], (cnt / GS_SLOTS) & 1, r.gave_up)) {
+            if (!*r.gave_up) atomicExch(r.status, 3);
+            *r.gave_up = 1;
+            dead = true;
+        }
+        if (!dead) {
+            // this lane's byte address in shared space; the loads below are constant offsets away.
+            // Rows beyond the matrix and k beyond K arrived as zeros, so nothing needs guarding.
+            const uint32_t st = gs_smem(r.stage_mem + (size_t)(warp * GS_SLOTS + slot) * GS_STAGE_ELEMS) +
+                                (uint32_t)(g * GS_BK + 8 * t) * 2u;
+#pragma unroll
+            for (int s = 0; s < GS_BK / 32; ++s) {
+                const uint4 a_lo = gs_lds128(st + (uint32_t)(32 * s * 2));
+                const uint4 a_hi = gs_lds128(st + (uint32_t)((8 * GS_BK + 32 * s) * 2));
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    gs_mma(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, xf[s][j].x, xf[s][j].y);
+                    gs_mma(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, xf[s][j].z, xf[s][j].w);
+                }
+            }
+            // The slot may be released only after every MMA fed from it has been issued (an MMA issues
+            // when its operands have arrived from shared memory; a released slot is overwritten by the
+            // next copy at once).  The MMAs are not volatile, so pin their results here: the compiler
+            // cannot sink them below this point.
+#pragma unroll
+            for (int j = 0; j < NT; ++j) asm volatile("" : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3]));
+            // ... and the reads themselves must be done before the copy engine may overwrite the stage:
+            // without this fence a slot that was refilled at once showed rows of the new chunk to the old reads.
+            __threadfence_block();
+            __syncwarp();
+            if (lane == 0) gs_mbar_arrive(&r.empty_bar[warp][slot]);
+        }
+        if (kc == cpt - 1 || cur == end - 1) {
+            // ---- the segment [seg_begin, cur] of this tile is done
+            const bool whole = (seg_begin == tile * cpt) && (kc == cpt - 1);
+            if (whole) {
+                gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, w.out_stride, tile, M, N, g, t);
+            } else {
+#ifndef GS_EXP_NO_FIXUP
+                // a warp's first tile may be shared with the share before, its last with the share after
+                const int which = (tile == begin / cpt) ? 0 : 1;
+                float* mine = partials + ((size_t)gw * 2 + which) * (NT * 4 * 32);
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) mine[(j * 4 + e) * 32 + lane] = acc[j][e];
+                __syncwarp();
+                const int g_lo = (tile * cpt) / share, g_hi = ((tile + 1) * cpt - 1) / share;
+                int last = 0;
+                if (lane == 0) {
+                    __threadfence();
+                    const int seen = atomicAdd(&counters[tile], 1);
+                    last = (seen == g_hi - g_lo) ? 1 : 0;
+                    if (last) {
+                        counters[tile] = 0;              // ready for the next product or launch
+                        __threadfence();
+                    }
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+                    for (int gg = g_lo; gg <= g_hi; ++gg) {          // share order: fixed
+                        const int wh = (tile == (gg * share) / cpt) ? 0 : 1;
+                        const float* theirs = partials + ((size_t)gg * 2 + wh) * (NT * 4 * 32);
+#pragma unroll
+                        for (int j = 0; j < NT; ++j)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) acc[j][e] += __ldcg(theirs + (j * 4 + e) * 32 + lane);
+                    }
+                    gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, w.out_stride, tile, M, N, g, t);
+                }
+#endif
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+            seg_begin = cur + 1;
+        }
+    }
+}
+
+#define GS_INIT_RINGS()                                                                                  \
+    extern __shared__ __align__(128) unsigned char gs_smem_raw[];                                        \
+    __shared__ uint64_t full_bar[GS_CONSUMERS][GS_SLOTS], empty_bar[GS_CONSUMERS][GS_SLOTS];             \
+    __shared__ volatile int gave_up;                                                                     \
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;                                          \
+    if (threadIdx.x == 0) {                                                                              \
+        gave_up = 0;                                                                                     \
+        for (int c = 0; c < GS_CONSUMERS; ++c)                                                           \
+            for (int s = 0; s < GS_SLOTS; ++s) {                                                         \
+                gs_mbar_init(&full_bar[c][s], 1);                                                        \
+                gs_mbar_init(&empty_bar[c][s], 1);                                                       \
+            }                                                                                            \
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");                               \
+    }                                                                                                    \
+    __syncthreads();                                                                                     \
+    dl_launch_dependents();                                                                              \
+    const GsRings rings{reinterpret_cast<__nv_bfloat16*>(gs_smem_raw), full_bar, empty_bar, &gave_up, status}
+
 template <int NT, typename TOut, bool FUSE_SWIGLU>
 __global__ void __launch_bounds__(GS_THREADS, 1)
-gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const __nv_bfloat16* __restrict__ x, int x_stride,
-                   TOut* __restrict__ out, int out_stride, int M, int N, int K, int up_offset, int cpt,
-                   int total_chunks, int share, int early_weights, float* __restrict__ partials,
-                   int* __restrict__ counters, int* __restrict__ status) {
-    extern __shared__ __align__(128) unsigned char gs_smem_raw[];
-    __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(gs_smem_raw);   // [consumer][slot][16][GS_PITCH]
-    __shared__ uint64_t full_bar[GS_CONSUMERS][GS_SLOTS], empty_bar[GS_CONSUMERS][GS_SLOTS];
-    __shared__ volatile int gave_up;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-
-    if (threadIdx.x == 0) {
-        gave_up = 0;
-        for (int c = 0; c < GS_CONSUMERS; ++c)
-            for (int s = 0; s < GS_SLOTS; ++s) {
-                gs_mbar_init(&full_bar[c][s], 1);
-                gs_mbar_init(&empty_bar[c][s], 1);
-            }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    dl_launch_dependents();
-
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const GsWork work, int early_weights,
+                   float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ status) {
+    GS_INIT_RINGS();
     if (warp == GS_CONSUMERS) {
         // ------------------------------------------------------------ producer warp
         // When the caller vouches that no pending work writes the weights (early_weights), the
         // producer does not wait for the kernel before this one: while that kernel finishes, the
         // rings fill.
         if (!early_weights) dl_grid_dependency_wait();
-        // Lane c (< GS_CONSUMERS) feeds consumer c: it walks that warp's share chunk by chunk, waits for
-        // the ring slot to be free, and issues one tiled copy (two for gate + up) per chunk.
         if (lane < GS_CONSUMERS) {
-            const int gw = blockIdx.x * GS_CONSUMERS + lane;
-            int cur = min(total_chunks, gw * share);
-            const int end = min(total_chunks, (gw + 1) * share);
             int cnt = 0;
-            bool stop = false;
-            for (; cur < end && !stop; ++cur, ++cnt) {
-                const int slot = cnt % GS_SLOTS;
-                if (cnt >= GS_SLOTS && !gs_mbar_wait(&empty_bar[lane][slot], ((cnt / GS_SLOTS) - 1) & 1, &gave_up)) {
-                    if (!gave_up) atomicExch(status, 1);
-                    gave_up = 1;
-                    stop = true;
-                    break;
-                }
-                const int tile = cur / cpt, kc = cur - tile * cpt;
-                __nv_bfloat16* dst = stage_mem + (size_t)(lane * GS_SLOTS + slot) * GS_STAGE_ELEMS;
-                // a box is always written whole: parts outside the matrix arrive as zeros
-                gs_mbar_expect(&full_bar[lane][slot], GS_STAGE_ELEMS * 2);
-                if (FUSE_SWIGLU) {
-                    dl_tma_load_2d(dst, &tmap, kc * GS_BK, tile * 8, &full_bar[lane][slot]);
-                    dl_tma_load_2d(dst + 8 * GS_BK, &tmap, kc * GS_BK, up_offset + tile * 8, &full_bar[lane][slot]);
-                } else {
-                    dl_tma_load_2d(dst, &tmap, kc * GS_BK, tile * 16, &full_bar[lane][slot]);
-                }
-            }
-            if (stop) {
-                // copies already issued must land before the block's shared memory is released
-                for (int i = max(0, cnt - GS_SLOTS); i < cnt; ++i) {
-                    const long long t0 = clock64();
-                    while (!gs_mbar_try(&full_bar[lane][i % GS_SLOTS], (i / GS_SLOTS) & 1) && clock64() - t0 < GS_WAIT_CYCLES) {}
-                }
-            }
+            if (!gs_produce<FUSE_SWIGLU>(&tmap, work, rings, lane, cnt)) gs_drain(rings, lane, cnt);
         }
     } else {
         // ------------------------------------------------------------ consumer warp
-        const int g = lane >> 2, t = lane & 3;
-        const int gw = blockIdx.x * GS_CONSUMERS + warp;
-        const int begin = min(total_chunks, gw * share), end = min(total_chunks, (gw + 1) * share);
         dl_grid_dependency_wait();       // x comes from the kernel before this one; out, partials and counters may be in use by it
-        float acc[NT][4];
-#pragma unroll
-        for (int j = 0; j < NT; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-        int seg_begin = begin;                               // first chunk of the current tile's segment
+        int cnt = 0;
         bool dead = false;
-        for (int cur = begin; cur < end; ++cur) {
-            const int cnt = cur - begin, slot = cnt % GS_SLOTS;
-            const int tile = cur / cpt, kc = cur - tile * cpt;
-            const int k0 = kc * GS_BK;
-            // activations of this chunk, asked for before waiting on the weights
-            uint4 xf[GS_BK / 32][NT];
-#pragma unroll
-            for (int s = 0; s < GS_BK / 32; ++s)
-#pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    const int tok = j * 8 + g, k = k0 + 32 * s + 8 * t;
-                    xf[s][j] = make_uint4(0u, 0u, 0u, 0u);
-                    if (tok < M && k < K) xf[s][j] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)tok * x_stride + k));
-                }
-            if (!dead && !gs_mbar_wait(&full_bar[warp][slot], (cnt / GS_SLOTS) & 1, &gave_up)) {
-                if (!gave_up) atomicExch(status, 3);
-                gave_up = 1;
-                dead = true;
-            }
-            if (!dead) {
-                // this lane's byte address in shared space; the loads below are constant offsets away.
-                // Rows beyond the matrix and k beyond K arrived as zeros, so nothing needs guarding.
-                const uint32_t st = gs_smem(stage_mem + (size_t)(warp * GS_SLOTS + slot) * GS_STAGE_ELEMS) +
-                                    (uint32_t)(g * GS_BK + 8 * t) * 2u;
-#pragma unroll
-                for (int s = 0; s < GS_BK / 32; ++s) {
-                    const uint4 a_lo = gs_lds128(st + (uint32_t)(32 * s * 2));
-                    const uint4 a_hi = gs_lds128(st + (uint32_t)((8 * GS_BK + 32 * s) * 2));
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        gs_mma(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, xf[s][j].x, xf[s][j].y);
-                        gs_mma(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, xf[s][j].z, xf[s][j].w);
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) gs_mbar_arrive(&empty_bar[warp][slot]);
-            }
-            if (kc == cpt - 1 || cur == end - 1) {
-                // ---- the segment [seg_begin, cur] of this tile is done
-                const bool whole = (seg_begin == tile * cpt) && (kc == cpt - 1);
-                if (whole) {
-                    gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, out_stride, tile, M, N, g, t);
-                } else {
-#ifndef GS_EXP_NO_FIXUP
-                    // a warp's first tile may be shared with the share before, its last with the share after
-                    const int which = (tile == begin / cpt) ? 0 : 1;
-                    float* mine = partials + ((size_t)gw * 2 + which) * (NT * 4 * 32);
-#pragma unroll
-                    for (int j = 0; j < NT; ++j)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) mine[(j * 4 + e) * 32 + lane] = acc[j][e];
-                    __syncwarp();
-                    const int g_lo = (tile * cpt) / share, g_hi = ((tile + 1) * cpt - 1) / share;
-                    int last = 0;
-                    if (lane == 0) {
-                        __threadfence();
-                        const int seen = atomicAdd(&counters[tile], 1);
-                        last = (seen == g_hi - g_lo) ? 1 : 0;
-                        if (last) {
-                            counters[tile] = 0;              // ready for the next launch
-                            __threadfence();
-                        }
-                    }
-                    last = __shfl_sync(0xffffffffu, last, 0);
-                    if (last) {
-#pragma unroll
-                        for (int j = 0; j < NT; ++j)
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-                        for (int gg = g_lo; gg <= g_hi; ++gg) {          // share order: fixed
-                            const int wh = (tile == (gg * share) / cpt) ? 0 : 1;
-                            const float* theirs = partials + ((size_t)gg * 2 + wh) * (NT * 4 * 32);
-#pragma unroll
-                            for (int j = 0; j < NT; ++j)
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) acc[j][e] += __ldcg(theirs + (j * 4 + e) * 32 + lane);
-                        }
-                        gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, out_stride, tile, M, N, g, t);
-                    }
-#endif
-                }
-#pragma unroll
-                for (int j = 0; j < NT; ++j)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-                seg_begin = cur + 1;
-            }
-        }
+        gs_consume<NT, TOut, FUSE_SWIGLU>(work, rings, partials, counters, warp, lane, cnt, dead);
     }
     __syncthreads();                                         // nobody leaves while copies may still land
 }
@@ -314,6 +358,37 @@ extern "C" int dl_gemm_skinny_scratch(int M, int N, int K, int fuse_swiglu, int 
     return DL_OK;
 }
 
+// Tensor map of W: rows of K bfloat16, boxes of 16 rows (8 for gate + up) by 256 columns.  Encoding
+// costs a driver call, so maps are kept per (matrix, shape).
+struct GsMapKey {
+    const void* w;
+    int rows, k, box;
+    bool operator==(const GsMapKey& o) const { return w == o.w && rows == o.rows && k == o.k && box == o.box; }
+};
+struct GsMapKeyHash {
+    size_t operator()(const GsMapKey& k) const {
+        return std::hash<const void*>()(k.w) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.k * 10007u) ^ (size_t)k.box;
+    }
+};
+
+static int gs_weight_map(CUtensorMap* out, const void* w, int N, int K, bool gated) {
+    static std::unordered_map<GsMapKey, CUtensorMap, GsMapKeyHash> maps;
+    static std::mutex maps_mutex;
+    const int rows = gated ? 2 * N : N, box = gated ? 8 : 16;
+    std::lock_guard<std::mutex> lock(maps_mutex);
+    const GsMapKey key{w, rows, K, box};
+    auto it = maps.find(key);
+    if (it == maps.end()) {
+        CUtensorMap fresh;
+        if (dl_tmap_encode_2d_bf16(&fresh, w, (uint64_t)rows, (uint64_t)K, (uint64_t)K * 2, box, GS_BK, DL_TMAP_SWIZZLE_NONE) != 0)
+            return DL_ERR_LAUNCH;
+        if (maps.size() > 4096) maps.clear();
+        it = maps.emplace(key, fresh).first;
+    }
+    *out = it->second;
+    return DL_OK;
+}
+
 template <int NT, typename TOut, bool FUSE>
 static int gs_launch(const GsPlan& p, cudaStream_t s, const __nv_bfloat16* x, int x_stride, const __nv_bfloat16* w,
                      void* out, int out_stride, int M, int N, int K, int up_offset, int early_weights, float* partials,
@@ -325,37 +400,11 @@ static int gs_launch(const GsPlan& p, cudaStream_t s, const __nv_bfloat16* x, in
         if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny: shared memory %zu: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    // Tensor map of W: rows of K bfloat16, boxes of 16 rows (8 for gate + up) by 256 columns.  Encoding
-    // costs a driver call, so maps are kept per (matrix, shape).
-    struct Key {
-        const void* w;
-        int rows, k, box;
-        bool operator==(const Key& o) const { return w == o.w && rows == o.rows && k == o.k && box == o.box; }
-    };
-    struct KeyHash {
-        size_t operator()(const Key& k) const {
-            return std::hash<const void*>()(k.w) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.k * 10007u) ^ (size_t)k.box;
-        }
-    };
-    static std::unordered_map<Key, CUtensorMap, KeyHash> maps;
-    static std::mutex maps_mutex;
-    const int rows = FUSE ? 2 * N : N, box = FUSE ? 8 : 16;
     CUtensorMap tmap;
-    {
-        std::lock_guard<std::mutex> lock(maps_mutex);
-        const Key key{(const void*)w, rows, K, box};
-        auto it = maps.find(key);
-        if (it == maps.end()) {
-            CUtensorMap fresh;
-            if (dl_tmap_encode_2d_bf16(&fresh, w, (uint64_t)rows, (uint64_t)K, (uint64_t)K * 2, box, GS_BK, DL_TMAP_SWIZZLE_NONE) != 0)
-                return DL_ERR_LAUNCH;
-            if (maps.size() > 4096) maps.clear();
-            it = maps.emplace(key, fresh).first;
-        }
-        tmap = it->second;
-    }
-    cudaError_t le = dl_launch_dependent(gemm_skinny_kernel<NT, TOut, FUSE>, dim3(p.blocks), dim3(GS_THREADS), smem, s, tmap, x,
-                                         x_stride, (TOut*)out, out_stride, M, N, K, up_offset, p.cpt, p.total, p.share,
+    const int rc = gs_weight_map(&tmap, w, N, K, FUSE);
+    if (rc != DL_OK) return rc;
+    const GsWork work{x, x_stride, out, out_stride, M, N, K, up_offset, p.cpt, p.total, p.share};
+    cudaError_t le = dl_launch_dependent(gemm_skinny_kernel<NT, TOut, FUSE>, dim3(p.blocks), dim3(GS_THREADS), smem, s, tmap, work,
                                          early_weights, partials, counters, status);
     if (le != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny: %s", cudaGetErrorString(le));
     return DL_OK;

@@ -88,12 +88,12 @@ def swiglu(gate_up):
     return plain_llama.swiglu(g, u).to(gate_up.dtype)
 
 
-def linear(x, w, out_dtype=None):
+def linear(x, w, out_dtype=None, resident=False):
     y = x.to(torch.float32) @ w.to(torch.float32).T
     return y.to(out_dtype or x.dtype)
 
 
-def gated_linear(x, w_gate_up):
+def gated_linear(x, w_gate_up, resident=False):
     return swiglu(linear(x, w_gate_up, torch.float32)).to(x.dtype)
 
 

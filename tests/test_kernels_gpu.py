@@ -362,6 +362,20 @@ def test_gemm_skinny(M, N, K, out_dtype):
     assert torch.equal(gemm_skinny.run(x.to(DEV), w.to(DEV), out_dtype).cpu(), y.cpu())
 
 
+def test_gemm_skinny_repeats_with_full_rings():
+    """16 rows make the consumer warps the slower side, so the rings stay full and every slot is
+    refilled the moment it is released: 30 launches must give the same bits as the first (a release
+    that does not wait for the reads of the slot shows up as a few wrong output columns)."""
+    from dotllm_b200.kernels import gemm_skinny
+    g = torch.Generator().manual_seed(27)
+    x = torch.randn(16, 4096, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(4096, 4096, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    first = gemm_skinny.run(x, w, torch.float32)
+    close(first, (x.double() @ w.double().T).float(), 2e-4 * 8, 1e-5)
+    for _ in range(30):
+        assert torch.equal(gemm_skinny.run(x, w, torch.float32), first)
+
+
 @pytest.mark.parametrize("M,N,K", [(17, 64, 64), (128, 256, 64), (129, 257, 72), (300, 1000, 320), (2048, 384, 192),
                                    (515, 4096, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
