@@ -12,6 +12,7 @@ The same kernels run, on the same data, as in an eager step: graphs change launc
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache.model_cache import PAGE
@@ -30,8 +31,16 @@ class _Captured:
         self.ints = torch.zeros(n, dtype=torch.int32, device=dev)
         self.tokens = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.host = [torch.zeros(n + batch, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.host_views = [h.numpy() for h in self.host]   # the same pinned memory, for fast slice writes
         self.events = [None] * _RING
         self.turn = 0
+        # host mirror of the block tables and which copies of it are current
+        self.table_mirror = np.full((n_groups, batch, pages), -1, dtype=np.int32)
+        self.table_rows = [[None] * batch for _ in range(n_groups)]
+        self.table_version = 0                             # bumped whenever the mirror changes
+        self.host_version = [-1] * _RING                   # version each staging buffer holds
+        self.device_version = -1                           # version the device tables hold
+        self.h2d_bytes = 0                                 # bytes copied host -> device so far
         b = batch
         self.pos, self.total, self.slots = self.ints[0:b], self.ints[b:2 * b], self.ints[2 * b:3 * b]
         self.tables = {}
@@ -59,20 +68,37 @@ class _Captured:
         if self.events[i] is not None:
             self.events[i].synchronize()                   # the copy that last used this buffer is done
         b, p = self.batch, self.pages
-        rows = [[s.length for s in seqs], [s.length + 1 for s in seqs], [s.slot for s in seqs]]
-        flat = [v for r in rows for v in r]
-        for g in kv_groups:
-            for s in seqs:
+        # Block tables change only when a sequence takes or gives back a page (or the batch changes):
+        # keep a host mirror, rewrite the rows that changed, and send the tables only then.
+        for gi, g in enumerate(kv_groups):
+            for r, s in enumerate(seqs):
                 pages = s.pages[g.index]
-                flat.extend(pages)
-                flat.extend([-1] * (p - len(pages)))
+                if self.table_rows[gi][r] != pages:
+                    self.table_mirror[gi, r, :len(pages)] = pages
+                    self.table_mirror[gi, r, len(pages):] = -1
+                    self.table_rows[gi][r] = list(pages)
+                    self.table_version += 1
         host = self.host[i]
-        n = len(flat)
-        host[:n] = torch.tensor(flat, dtype=torch.int32)
-        self.ints.copy_(host[:n], non_blocking=True)
+        view = self.host_views[i]
+        small = 3 * b
+        view[:b] = [s.length for s in seqs]
+        view[b:2 * b] = [s.length + 1 for s in seqs]
+        view[2 * b:small] = [s.slot for s in seqs]
+        n = small + self.table_mirror.size
+        if self.device_version != self.table_version:
+            if self.host_version[i] != self.table_version:
+                view[small:n] = self.table_mirror.reshape(-1)
+                self.host_version[i] = self.table_version
+            self.ints.copy_(host[:n], non_blocking=True)
+            self.device_version = self.table_version
+            self.h2d_bytes += 4 * n
+        else:
+            self.ints[:small].copy_(host[:small], non_blocking=True)
+            self.h2d_bytes += 4 * small
         if tokens is not None:
-            host[n:n + b] = torch.tensor(tokens, dtype=torch.int32)
+            view[n:n + b] = tokens
             self.tokens.copy_(host[n:n + b], non_blocking=True)
+            self.h2d_bytes += 4 * b
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
