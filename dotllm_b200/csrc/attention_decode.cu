@@ -266,13 +266,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     }
     __syncthreads();
     dl_launch_dependents();
-    dl_grid_dependency_wait();       // q and the newest cache page come from the kernel before this one
 
     if (warp == AD_MAX_STAGES) {
         // ------------------------------------------------------------ producer
         // The warp reads 32 page ids at a time (one coalesced load); lane 0 issues the copies.
+        // Of what this kernel reads, the kernel launched before it writes only q and each sequence's
+        // newest cache page (lengths and block tables are staged before the step's first kernel).
+        // So the producer starts on older pages at once and waits for that kernel only before it
+        // copies a newest page: the ring fills while the kernel before is still finishing.
         int n = 0;                                           // pages issued so far, over all runs
-        bool stop = false;
+        bool stop = false, waited = false;
         const AdCut cut = ad_cut(seq_len, n_seqs, nkv, window, gridDim.x, lane);
         AdWalk walk = ad_walk_begin(cut, seq_len, n_seqs, nkv, window, blockIdx.x, lane);
         AdSeg w;
@@ -291,6 +294,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         } else if (n >= n_stages && !ad_mbar_wait(&empty_bar[s], ((n / n_stages) - 1) & 1, &gave_up)) {
                             bad = 1;
                         } else {
+                            if (!waited && w.page0 + i0 + j == (w.len - 1) / DL_PAGE) {
+                                dl_grid_dependency_wait();
+                                waited = true;
+                            }
                             __nv_bfloat16* dst = stage_mem + (size_t)s * 2 * PAGE_ELEMS;
                             ad_mbar_expect(&full_bar[s], 2 * PAGE_BYTES);
                             ad_bulk_copy(dst, k_pool + dl_k_offset(page, nkv, w.kvh, 0, HD), PAGE_BYTES, &full_bar[s]);
@@ -315,6 +322,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
         }
     } else if (warp < n_stages) {
         // ------------------------------------------------------------ consumers (warp w owns stage w)
+        dl_grid_dependency_wait();       // q comes from the kernel before this one; out and the scratch may be in use by it
         float* my_o = merge_o + (size_t)warp * group * (HD + 4);
         const float scale2 = scale * 1.4426950408889634f;    // scores in units of log2
         int n0 = 0;                                          // pages of the runs before this one
@@ -686,6 +694,9 @@ static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int
 // part_o: float32 [part_slots, group, hd]; part_ml: float32 [part_slots, group, 2]: scratch for the
 // segments of (sequence, head) pairs that the cut spreads over several blocks, two per block.
 // status: int32, set non-zero if a wait expired.
+// Launched with programmatic dependent launch: of this call's inputs, a kernel of this library
+// launched directly before it may write only q and the newest page of each sequence (the rope and
+// cache-write kernel does); lengths, block tables and older pages must be complete by then.
 extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                         const void* v_pool, int n_pages, const int32_t* seq_len,
                                         const int32_t* block_table, int bt_stride, int n_seqs, int nh, int nkv,
