@@ -95,10 +95,10 @@ def test_embedding_and_head_parts(dtype):
 
 # ---------------------------------------------------------------------------------- a toy model
 def toy_parts():
-    """Parts defined in the test: a mixer with a decaying state per sequence, and a position
-    encoding that is not a rotation."""
-    from dotllm_b200.parts import (CacheNeed, Mixer, PositionEncoding, WeightSpec, register_mixer,
-                                   register_position_encoding)
+    """Parts defined in the test: a mixer with a decaying state per sequence, a position encoding
+    that is not a rotation, and a feed-forward that routes each token to one of three experts."""
+    from dotllm_b200.parts import (CacheNeed, FeedForward, Mixer, PositionEncoding, WeightSpec,
+                                   register_feed_forward, register_mixer, register_position_encoding)
 
     class DecayMixer(Mixer):
         """s_t = a * s_{t-1} + x_t W_in ; y_t = s_t W_out.  Keeps s per sequence in the cache's
@@ -139,8 +139,38 @@ def toy_parts():
                 if x is not None:
                     x[:, ::hd] += shift[:, None].to(x.dtype)
 
+    class RoutedFeedForward(FeedForward):
+        """Top-1 routing in float32: expert e = argmax(x W_r^T); y = silu(x U_e^T) D_e^T."""
+
+        def __init__(self, params, hidden_size, runtime):
+            super().__init__(params, hidden_size, runtime)
+            self.n_experts, self.inner = int(params["n_experts"]), int(params["inner"])
+
+        def weight_specs(self):
+            specs = {"router.weight": WeightSpec((self.n_experts, self.hidden_size), "precise", ("normal", 0.5))}
+            for e in range(self.n_experts):
+                specs[f"experts.{e}.up.weight"] = WeightSpec((self.inner, self.hidden_size))
+                specs[f"experts.{e}.down.weight"] = WeightSpec((self.hidden_size, self.inner))
+            return specs
+
+        def bind(self, tensors):
+            self.router = tensors["router.weight"]
+            self.up = [tensors[f"experts.{e}.up.weight"] for e in range(self.n_experts)]
+            self.down = [tensors[f"experts.{e}.down.weight"] for e in range(self.n_experts)]
+
+        def forward(self, x):
+            choice = (x.float() @ self.router.float().T).argmax(dim=1)
+            out = torch.zeros(x.shape[0], self.hidden_size, dtype=torch.float32, device=x.device)
+            for e in range(self.n_experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.nn.functional.silu(x[rows].float() @ self.up[e].float().T)
+                    out[rows] = h @ self.down[e].float().T
+            return out
+
     register_mixer("toy_decay", DecayMixer)
     register_position_encoding("toy_shift", ShiftEncoding)
+    register_feed_forward("toy_routed", RoutedFeedForward)
 
 
 @dataclass(frozen=True)
@@ -165,8 +195,9 @@ def toy_spec(cfg):
                                   "position": {"kind": "toy_shift", "params": {"head_dim": 16, "slope": 0.01}}},
                     "l0.attn.")
     decay = PartSpec("toy_decay", {"state_width": 24, "decay": 0.9}, "l1.mix.")
+    routed = PartSpec("toy_routed", {"n_experts": 3, "inner": 40}, "l1.moe.")
     layers = (LayerSpec("pre_norm", attn, ffn("l0.ffn.", 80), norm("l0.n1."), norm("l0.n2.")),
-              LayerSpec("pre_norm", decay, ffn("l1.ffn.", 56), norm("l1.n1."), norm("l1.n2.")))
+              LayerSpec("pre_norm", decay, routed, norm("l1.n1."), norm("l1.n2.")))
     # layer 0, layer 1, layer 1 again (its own state), layer 0 again reading the first run's cache
     schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(0, cache_of=0))
     return ModelSpec("ToyForCausalLM", cfg.hidden_size, cfg.vocab_size, 512,
@@ -202,8 +233,17 @@ def toy_plain(w, tokens):
                 outs.append(s.clone())
             h = h + torch.stack(outs) @ w[p + "mix.out_proj.weight"].T
         x = plain_llama.rms_norm(h, w[p + "n2.weight"], 1e-5)
-        g, u2 = x @ w[p + "ffn.gate_proj.weight"].T, x @ w[p + "ffn.up_proj.weight"].T
-        h = h + plain_llama.swiglu(g, u2) @ w[p + "ffn.down_proj.weight"].T
+        if layer == 0:
+            g, u2 = x @ w[p + "ffn.gate_proj.weight"].T, x @ w[p + "ffn.up_proj.weight"].T
+            h = h + plain_llama.swiglu(g, u2) @ w[p + "ffn.down_proj.weight"].T
+        else:                                                        # each token goes to its best expert
+            choice = (x @ w[p + "moe.router.weight"].T).argmax(dim=1).tolist()
+            rows = []
+            for t in range(n):
+                up, down = w[p + f"moe.experts.{choice[t]}.up.weight"], w[p + f"moe.experts.{choice[t]}.down.weight"]
+                hid = x[t] @ up.T
+                rows.append((hid * torch.sigmoid(hid)) @ down.T)
+            h = h + torch.stack(rows)
     return plain_llama.rms_norm(h, w["final.weight"], 1e-5) @ w["head.weight"].T
 
 
