@@ -38,6 +38,19 @@ LLAMA_31_8B = {
     "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 131072,
     "hidden_act": "silu",
 }
+# The other two benchmark shapes of the same architecture (selected with --shape).
+LLAMA_32_1B = dict(LLAMA_31_8B, num_hidden_layers=16, hidden_size=2048, num_attention_heads=32, num_key_value_heads=8,
+                   head_dim=64, intermediate_size=8192, vocab_size=128256, tie_word_embeddings=True,
+                   rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                 "original_max_position_embeddings": 8192})
+LLAMA_2_13B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 40,
+    "head_dim": 128, "intermediate_size": 13824, "vocab_size": 32000, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 4096, "hidden_act": "silu",
+}
+SHAPES = {"8b": ("Llama-3.1-8B-shaped", LLAMA_31_8B), "1b": ("Llama-3.2-1B-shaped", LLAMA_32_1B),
+          "13b": ("Llama-2-13B-shaped", LLAMA_2_13B)}
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -103,7 +116,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--layers", type=int, default=LLAMA_31_8B["num_hidden_layers"])
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: the 8B default, or 1b / 13b")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all of them)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill (for profiling)")
     args = ap.parse_args()
@@ -125,7 +139,8 @@ def main():
     from dotllm_b200.kernels import library, ops
 
     pk = peaks()
-    cfg_dict = dict(LLAMA_31_8B, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    cfg_dict = dict(shape, num_hidden_layers=args.layers or shape["num_hidden_layers"])
     cfg = config_from_dict(cfg_dict)
     torch.cuda.set_device(0)
     t0 = time.time()
@@ -136,7 +151,14 @@ def main():
     steps, warmup, ctx = args.steps, args.warmup, args.context
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
     room = ctx + 4 * (steps + warmup) + 128
-    cache = model.new_cache(max_tokens=max(batches) * ((room + 63) // 64 * 64), max_sequences=max(batches))
+    # The cache must fit beside the weights: a batch whose sequences of `ctx` tokens would not fit
+    # runs at the longest context that does (reported with its point).
+    per_token = 2 * 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim
+    free_bytes, _ = torch.cuda.mem_get_info()
+    budget_tokens = int(0.85 * free_bytes) // per_token
+    ctx_of = {b: min(ctx, max(256, budget_tokens // b - (room - ctx)) // 64 * 64) for b in batches}
+    cache_tokens = max(b * ((ctx_of[b] + room - ctx + 63) // 64 * 64) for b in batches)
+    cache = model.new_cache(max_tokens=cache_tokens, max_sequences=max(batches))
     for g in cache.kv_groups:                              # random cache contents (see the header)
         g.k.normal_(0.0, 0.5)
         g.v.normal_(0.0, 0.5)
@@ -155,6 +177,7 @@ def main():
     library.call = counting_call                           # every kernel module calls through library.call
 
     def decode_point(batch, measure_e2e):
+        ctx = ctx_of[batch]
         seqs = [cache.open_sequence() for _ in range(batch)]
         cache.reserve([(s, ctx) for s in seqs])
         for s in seqs:
@@ -231,7 +254,8 @@ def main():
     if not args.no_points:
         for b in batches:
             if b != args.batch:
-                points[f"decode_b{b}"] = round(decode_point(b, False)["tok_s"], 1)
+                name = f"decode_b{b}" if ctx_of[b] == ctx else f"decode_b{b}_ctx{ctx_of[b]}"
+                points[name] = round(decode_point(b, False)["tok_s"], 1)
         points[f"decode_b{args.batch}"] = round(main_point["tok_s"], 1)
         prefill = prefill_point()
 
@@ -242,11 +266,11 @@ def main():
         "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(main_point["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights, random token ids, random cache contents",
-        "config": {"model": "Llama-3.1-8B-shaped", "layers": cfg.num_hidden_layers,
-                   "layers_full": LLAMA_31_8B["num_hidden_layers"], "hidden": cfg.hidden_size,
+        "config": {"model": shape_name, "layers": cfg.num_hidden_layers,
+                   "layers_full": shape["num_hidden_layers"], "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": vocab,
-                   "global_batch": args.batch, "seq_len": ctx, "parallelism": "none (1 GPU)",
+                   "global_batch": args.batch, "seq_len": ctx_of[args.batch], "parallelism": "none (1 GPU)",
                    "weights": "bf16", "cache": "bf16 pages of 64 tokens",
                    "l2": "inputs larger than L2 (all weights are read every step)",
                    "decode": "CUDA graph replay, one captured graph per batch size",
