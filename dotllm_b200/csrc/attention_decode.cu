@@ -221,16 +221,52 @@ __device__ __forceinline__ bool ad_walk_next(AdWalk& w, AdSeg& s, const int32_t*
     return true;
 }
 
+// The step's own token, when the caller has not rotated it and written it to the cache yet: the
+// kernel then rotates q as it loads it and puts the new key and value into the newest page itself
+// (in the shared-memory stage and in the cache), so that no separate kernel has to run before it.
+// k == nullptr: q is rotated and the cache is complete already.
+struct AdFresh {
+    const __nv_bfloat16* k;          // [B, nkv*hd] rows k_stride apart, unrotated
+    int k_stride;
+    const __nv_bfloat16* v;          // [B, nkv*hd] rows v_stride apart
+    int v_stride;
+    const float* cos_t;              // [table_rows, hd/2] (rotate != 0)
+    const float* sin_t;
+    int table_rows;
+    int rotate;                      // 0: no rotation (the mixer encoded positions itself)
+};
+
+// The same roundings as the rope kernels (no contraction), so that the fused and the separate way
+// give the same bits.
+__device__ __forceinline__ float ad_rot_lo(float x0, float x1, float c, float s) { return __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)); }
+__device__ __forceinline__ float ad_rot_hi(float x0, float x1, float c, float s) { return __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)); }
+
+// Rotate the 8 dims of a low-half piece (x0) and its partner in the high half (x1) in place.
+__device__ __forceinline__ void ad_rotate8(uint4& x0, uint4& x1, const float* cs, const float* sn) {
+    const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sn), s1 = *reinterpret_cast<const float4*>(sn + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    __nv_bfloat16* a = reinterpret_cast<__nv_bfloat16*>(&x0);
+    __nv_bfloat16* b = reinterpret_cast<__nv_bfloat16*>(&x1);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float f0 = __bfloat162float(a[e]), f1 = __bfloat162float(b[e]);
+        a[e] = __float2bfloat16_rn(ad_rot_lo(f0, f1, c[e], sv[e]));
+        b[e] = __float2bfloat16_rn(ad_rot_hi(f0, f1, c[e], sv[e]));
+    }
+}
+
 // WIDE: the group has more than 8 query heads, so fragment rows 8..15 carry data too.
 template <int HD, bool WIDE>
 __global__ void __launch_bounds__(AD_THREADS, 1)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
-                        int out_stride, const __nv_bfloat16* __restrict__ k_pool,
-                        const __nv_bfloat16* __restrict__ v_pool, int n_pages,
+                        int out_stride, __nv_bfloat16* __restrict__ k_pool,
+                        __nv_bfloat16* __restrict__ v_pool, int n_pages,
                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_table,
                         int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int n_stages,
                         float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int* __restrict__ status) {
+                        float* __restrict__ part_ml, const AdFresh fresh, int* __restrict__ status) {
     constexpr int DC = HD / 32;          // 32-dim slices of a head
     constexpr int DT = HD / 8;           // 8-dim output tiles
     constexpr int PAGE_ELEMS = DL_PAGE * HD;
@@ -273,7 +309,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
         // Of what this kernel reads, the kernel launched before it writes only q and each sequence's
         // newest cache page (lengths and block tables are staged before the step's first kernel).
         // So the producer starts on older pages at once and waits for that kernel only before it
-        // copies a newest page: the ring fills while the kernel before is still finishing.
+        // copies a newest page: the ring fills while the kernel before is still finishing.  (When this
+        // kernel writes the new token itself, the copy of a newest page just brings a stale slot that
+        // the consumer overwrites in the stage, and the producer never waits.)
         int n = 0;                                           // pages issued so far, over all runs
         bool stop = false, waited = false;
         const AdCut cut = ad_cut(seq_len, n_seqs, nkv, window, gridDim.x, lane);
@@ -294,7 +332,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         } else if (n >= n_stages && !ad_mbar_wait(&empty_bar[s], ((n / n_stages) - 1) & 1, &gave_up)) {
                             bad = 1;
                         } else {
-                            if (!waited && w.page0 + i0 + j == (w.len - 1) / DL_PAGE) {
+                            if (!waited && fresh.k == nullptr && w.page0 + i0 + j == (w.len - 1) / DL_PAGE) {
                                 dl_grid_dependency_wait();
                                 waited = true;
                             }
@@ -341,6 +379,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                     if (g < group) qf_lo[c] = *reinterpret_cast<const uint4*>(qb + (size_t)g * HD + c * 32 + t * 8);
                     if (WIDE && g + 8 < group) qf_hi[c] = *reinterpret_cast<const uint4*>(qb + (size_t)(g + 8) * HD + c * 32 + t * 8);
                 }
+                if (fresh.k != nullptr && fresh.rotate) {
+                    // slice c of the low half pairs with slice c + DC/2 of the high half, same lane
+                    const int pos = min(w.len - 1, fresh.table_rows - 1);        // host-validated
+                    const float* cs = fresh.cos_t + (size_t)pos * (HD / 2);
+                    const float* sn = fresh.sin_t + (size_t)pos * (HD / 2);
+#pragma unroll
+                    for (int c = 0; c < DC / 2; ++c) {
+                        ad_rotate8(qf_lo[c], qf_lo[c + DC / 2], cs + c * 32 + t * 8, sn + c * 32 + t * 8);
+                        if (WIDE) ad_rotate8(qf_hi[c], qf_hi[c + DC / 2], cs + c * 32 + t * 8, sn + c * 32 + t * 8);
+                    }
+                }
             }
             float o[DT][4];
 #pragma unroll
@@ -362,6 +411,44 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                 __nv_bfloat16* kp = stage_mem + (size_t)s * 2 * PAGE_ELEMS;
                 __nv_bfloat16* vp = kp + PAGE_ELEMS;
                 const bool ragged = (base + DL_PAGE > w.len) || (base < w.first_key);
+                if (fresh.k != nullptr && base <= w.len - 1 && w.len - 1 < base + DL_PAGE) {
+                    // The page of the step's own token: its slot is stale in the copy that arrived.  Put the
+                    // (rotated) key and the value there, in the stage and in the cache.
+                    const int in_page = (w.len - 1) - base;
+                    const int page = block_table[(size_t)w.b * bt_stride + (w.len - 1) / DL_PAGE];
+                    const __nv_bfloat16* kn = fresh.k + (size_t)w.b * fresh.k_stride + (size_t)w.kvh * HD;
+                    const __nv_bfloat16* vn = fresh.v + (size_t)w.b * fresh.v_stride + (size_t)w.kvh * HD;
+                    const int pos = min(w.len - 1, fresh.table_rows - 1);
+                    for (int i4 = lane * 4; i4 < HD / 2; i4 += 128) {            // four rotation pairs per lane
+                        __nv_bfloat16 lo[4], hi[4];
+                        *reinterpret_cast<uint2*>(lo) = *reinterpret_cast<const uint2*>(kn + i4);
+                        *reinterpret_cast<uint2*>(hi) = *reinterpret_cast<const uint2*>(kn + HD / 2 + i4);
+                        if (fresh.rotate) {
+                            const float4 c = *reinterpret_cast<const float4*>(fresh.cos_t + (size_t)pos * (HD / 2) + i4);
+                            const float4 sn = *reinterpret_cast<const float4*>(fresh.sin_t + (size_t)pos * (HD / 2) + i4);
+                            const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float f0 = __bfloat162float(lo[e]), f1 = __bfloat162float(hi[e]);
+                                lo[e] = __float2bfloat16_rn(ad_rot_lo(f0, f1, cc[e], ss[e]));
+                                hi[e] = __float2bfloat16_rn(ad_rot_hi(f0, f1, cc[e], ss[e]));
+                            }
+                        }
+                        *reinterpret_cast<uint2*>(kp + in_page * HD + i4) = *reinterpret_cast<uint2*>(lo);
+                        *reinterpret_cast<uint2*>(kp + in_page * HD + HD / 2 + i4) = *reinterpret_cast<uint2*>(hi);
+                        if (page >= 0 && page < n_pages) {
+                            __nv_bfloat16* kg = k_pool + dl_k_offset(page, nkv, w.kvh, in_page, HD);
+                            *reinterpret_cast<uint2*>(kg + i4) = *reinterpret_cast<uint2*>(lo);
+                            *reinterpret_cast<uint2*>(kg + HD / 2 + i4) = *reinterpret_cast<uint2*>(hi);
+                        }
+                    }
+                    for (int d = lane; d < HD; d += 32) {
+                        const __nv_bfloat16 val = vn[d];
+                        vp[d * DL_PAGE + in_page] = val;
+                        if (page >= 0 && page < n_pages) v_pool[dl_v_offset(page, nkv, w.kvh, d, HD) + in_page] = val;
+                    }
+                    __syncwarp();
+                }
                 if (ragged) {
                     // Keys outside [first, len) may hold anything (even NaN): make their values exact
                     // zeros in the stage once, so that the product below needs no special case.
@@ -646,10 +733,10 @@ attention_decode_combine_kernel(__nv_bfloat16* __restrict__ out, int out_stride,
 }
 
 template <int HD, bool WIDE>
-static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
-                     const void* v_pool, int n_pages, const int32_t* seq_len, const int32_t* block_table,
+static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int out_stride, void* k_pool,
+                     void* v_pool, int n_pages, const int32_t* seq_len, const int32_t* block_table,
                      int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int blocks, float* part_o,
-                     float* part_ml, int part_slots, int* status) {
+                     float* part_ml, int part_slots, const AdFresh& fresh, int* status) {
     const int group = nh / nkv;
     int dev = 0, sms = 0, max_smem = 0;
     cudaGetDevice(&dev);
@@ -676,8 +763,8 @@ static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int
         return dl_fail(DL_ERR_ARGUMENT, "attention_decode: scratch for %d segments, %d blocks need %d", part_slots, blocks, 2 * blocks);
     cudaError_t le = dl_launch_dependent(
         attention_decode_kernel<HD, WIDE>, dim3(blocks), dim3(AD_THREADS), smem, s, (const __nv_bfloat16*)q, q_stride,
-        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, n_pages, seq_len,
-        block_table, bt_stride, n_seqs, nh, nkv, scale, window, n_stages, part_o, part_ml, status);
+        (__nv_bfloat16*)out, out_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, seq_len,
+        block_table, bt_stride, n_seqs, nh, nkv, scale, window, n_stages, part_o, part_ml, fresh, status);
     if (le != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "attention_decode: %s", cudaGetErrorString(le));
     if (blocks > 1) {
         cudaError_t e = dl_launch_dependent(attention_decode_combine_kernel, dim3(nkv, n_seqs), dim3(128), 0, s,
@@ -697,11 +784,10 @@ static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int
 // Launched with programmatic dependent launch: of this call's inputs, a kernel of this library
 // launched directly before it may write only q and the newest page of each sequence (the rope and
 // cache-write kernel does); lengths, block tables and older pages must be complete by then.
-extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
-                                        const void* v_pool, int n_pages, const int32_t* seq_len,
-                                        const int32_t* block_table, int bt_stride, int n_seqs, int nh, int nkv,
-                                        int hd, float scale, int window, int blocks, float* part_o, float* part_ml,
-                                        int part_slots, int* status, void* stream) {
+static int ad_dispatch(const void* q, int q_stride, void* out, int out_stride, void* k_pool, void* v_pool, int n_pages,
+                       const int32_t* seq_len, const int32_t* block_table, int bt_stride, int n_seqs, int nh, int nkv, int hd,
+                       float scale, int window, int blocks, float* part_o, float* part_ml, int part_slots,
+                       const AdFresh& fresh, int* status, void* stream) {
     DL_REQUIRE(n_seqs >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad head counts");
     DL_REQUIRE(nh / nkv <= 16, "attention_decode: groups of more than 16 query heads are not supported (%d)", nh / nkv);
     DL_REQUIRE(scale > 0.f, "attention_decode: the score scale must be positive");
@@ -712,6 +798,14 @@ extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, 
     DL_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0,
                "attention_decode: q and the pools must be 16-byte aligned");
     DL_REQUIRE((long long)n_seqs * nkv * bt_stride < (1ll << 30) && n_seqs <= 65535, "attention_decode: too many pages");
+    if (fresh.k != nullptr) {
+        DL_REQUIRE(fresh.v != nullptr && fresh.k_stride % 4 == 0 && fresh.v_stride % 4 == 0 && ((uintptr_t)fresh.k % 8) == 0 &&
+                       ((uintptr_t)fresh.v % 8) == 0 && fresh.k_stride >= nkv * hd && fresh.v_stride >= nkv * hd,
+                   "attention_decode: the new keys and values must be 8-byte aligned rows of nkv*hd");
+        DL_REQUIRE(!fresh.rotate || ((hd == 64 || hd == 128) && fresh.cos_t && fresh.sin_t && fresh.table_rows > 0 &&
+                                     ((uintptr_t)fresh.cos_t % 16) == 0 && ((uintptr_t)fresh.sin_t % 16) == 0),
+                   "attention_decode: rotating inside the kernel takes head_dim 64 or 128 and 16-byte aligned tables");
+    }
     if (n_seqs == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const bool wide = nh / nkv > 8;
@@ -720,12 +814,49 @@ extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, 
         if (wide)                                                                                                      \
             return ad_launch<HDV, true>(s, q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table, \
                                         bt_stride, n_seqs, nh, nkv, scale, window, blocks, part_o, part_ml, part_slots, \
-                                        status);                                                                       \
+                                        fresh, status);                                                                \
         return ad_launch<HDV, false>(s, q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table,   \
                                      bt_stride, n_seqs, nh, nkv, scale, window, blocks, part_o, part_ml, part_slots,   \
-                                     status);                                                                          \
+                                     fresh, status);                                                                   \
     }
     AD_CASE(32) AD_CASE(64) AD_CASE(96) AD_CASE(128)
 #undef AD_CASE
     return dl_fail(DL_ERR_UNSUPPORTED, "attention_decode: head_dim %d (takes 32, 64, 96, 128)", hd);
+}
+
+extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                        const void* v_pool, int n_pages, const int32_t* seq_len,
+                                        const int32_t* block_table, int bt_stride, int n_seqs, int nh, int nkv,
+                                        int hd, float scale, int window, int blocks, float* part_o, float* part_ml,
+                                        int part_slots, int* status, void* stream) {
+    AdFresh none = {};
+    return ad_dispatch(q, q_stride, out, out_stride, const_cast<void*>(k_pool), const_cast<void*>(v_pool), n_pages, seq_len,
+                       block_table, bt_stride, n_seqs, nh, nkv, hd, scale, window, blocks, part_o, part_ml, part_slots, none,
+                       status, stream);
+}
+
+// The same with the step's own token handled inside the kernel: q (unrotated), k_new and v_new
+// ([B, nkv*hd] rows, unrotated) come straight from the projection; the kernel rotates q and k_new
+// with the rotary tables (rotate != 0: cos, sin float32 [table_rows, hd/2], full-width rotation of
+// head sizes 64 and 128; rotate == 0: no rotation), writes k_new and v_new into each sequence's
+// newest page (position seq_len[b] - 1), and attends.  Replaces dl_rope_cache_write followed by
+// dl_attention_decode_bf16 for a decode step, with the same bits.
+extern "C" int dl_attention_decode_fresh_bf16(const void* q, int q_stride, const void* k_new, int k_stride, const void* v_new,
+                                              int v_stride, const float* cos_t, const float* sin_t, int table_rows, int rotate,
+                                              void* out, int out_stride, void* k_pool, void* v_pool, int n_pages,
+                                              const int32_t* seq_len, const int32_t* block_table, int bt_stride, int n_seqs,
+                                              int nh, int nkv, int hd, float scale, int window, int blocks, float* part_o,
+                                              float* part_ml, int part_slots, int* status, void* stream) {
+    DL_REQUIRE(k_new != nullptr && v_new != nullptr, "attention_decode_fresh: needs the new keys and values");
+    AdFresh fresh;
+    fresh.k = (const __nv_bfloat16*)k_new;
+    fresh.k_stride = k_stride;
+    fresh.v = (const __nv_bfloat16*)v_new;
+    fresh.v_stride = v_stride;
+    fresh.cos_t = cos_t;
+    fresh.sin_t = sin_t;
+    fresh.table_rows = table_rows;
+    fresh.rotate = rotate;
+    return ad_dispatch(q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table, bt_stride, n_seqs, nh, nkv,
+                       hd, scale, window, blocks, part_o, part_ml, part_slots, fresh, status, stream);
 }

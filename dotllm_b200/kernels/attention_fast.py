@@ -15,6 +15,8 @@ _P, _I, _F = _library._P, _library._I, _library._F
 _library.register_signatures({
     "dl_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I,
                                  _P, _P, _I, _P, _P],
+    "dl_attention_decode_fresh_bf16": [_P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I,
+                                       _I, _F, _I, _I, _P, _P, _I, _P, _P],
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                   _F, _I, _P, _P],
     "dl_attention_prefill_tc_bf16": [_P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
@@ -39,18 +41,57 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
             scale, window, plan):
     B = plan.n_seqs
     group = n_heads // n_kv_heads
-    slots = 2 * max(1, _library.library().dl_sm_count())
-    key = ("decode", group, head_dim)
-    if key not in plan.scratch:
-        plan.scratch[key] = (torch.empty(slots * group * head_dim, dtype=torch.float32, device=q.device),
-                             torch.empty(slots * group * 2, dtype=torch.float32, device=q.device))
-    part_o, part_ml = plan.scratch[key]
+    part_o, part_ml, slots = _decode_scratch(plan, group, head_dim, q.device)
     _library.call("dl_attention_decode_bf16", q.data_ptr(), q_stride, out.data_ptr(), out.stride(0),
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, plan.seq_total.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim,
                   scale, window, DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots,
                   _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     return True
+
+
+def _decode_scratch(plan, group, head_dim, device):
+    slots = 2 * max(1, _library.library().dl_sm_count())
+    key = ("decode", group, head_dim)
+    if key not in plan.scratch:
+        plan.scratch[key] = (torch.empty(slots * group * head_dim, dtype=torch.float32, device=device),
+                             torch.empty(slots * group * 2, dtype=torch.float32, device=device))
+    return plan.scratch[key] + (slots,)
+
+
+FRESH_ROTATE_HEAD_DIMS = (64, 128)   # head sizes whose rotation the decode kernel does itself
+
+
+def decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_heads, n_kv_heads, head_dim,
+                 scale, window, plan):
+    """A decode step with the new token handled inside the attention kernel (rotation of q and k,
+    cache write, attention): returns the output, or None when the sizes are not the kernel's."""
+    group = n_heads // n_kv_heads
+    if not (plan.all_single and q.shape[0] == plan.n_seqs and head_dim in DECODE_HEAD_DIMS and group <= 16
+            and decode_fits(group, head_dim) and (rotary_dim == 0 or (rotary_dim == head_dim
+                                                                      and head_dim in FRESH_ROTATE_HEAD_DIMS))):
+        return None
+    rows = lambda t: t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+    qs, ks, vs = rows(q), rows(k), rows(v)
+    if q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or qs % 8 or ks % 4 or vs % 4 \
+            or q.data_ptr() % 16 or k.data_ptr() % 8 or v.data_ptr() % 8 or k.dtype != q.dtype or v.dtype != q.dtype \
+            or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+        return None
+    if rotary_dim and (cos.dtype != torch.float32 or sin.dtype != torch.float32 or not cos.is_contiguous()
+                       or not sin.is_contiguous() or cos.shape != sin.shape or cos.shape[1] != head_dim // 2
+                       or cos.data_ptr() % 16 or sin.data_ptr() % 16):
+        return None
+    B = plan.n_seqs
+    out = torch.empty((B, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    part_o, part_ml, slots = _decode_scratch(plan, group, head_dim, q.device)
+    _library.call("dl_attention_decode_fresh_bf16", q.data_ptr(), qs, k.data_ptr(), ks, v.data_ptr(), vs,
+                  cos.data_ptr() if rotary_dim else None, sin.data_ptr() if rotary_dim else None,
+                  cos.shape[0] if rotary_dim else 0, 1 if rotary_dim else 0, out.data_ptr(), out.stride(0),
+                  k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], plan.seq_total.data_ptr(),
+                  block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window,
+                  DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots,
+                  _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    return out
 
 
 def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads, head_dim,

@@ -177,6 +177,24 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
     return out
 
 
+def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
+                         n_heads, n_kv_heads, head_dim, scale, window=0, plan=None):
+    """``rope_cache_write`` followed by ``attention`` (same arguments, same result).  A bfloat16
+    decode step (one new token per sequence) with a full-width rotation of head size 64 or 128, or
+    with no rotation, runs as one kernel that rotates q, puts the new keys and values into the
+    cache and attends; everything else runs the two kernels one after the other."""
+    if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and k is not None:
+        from . import attention_fast
+        out = attention_fast.decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_heads,
+                                          n_kv_heads, head_dim, float(scale), int(window), plan)
+        if out is not None:
+            return out
+    rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
+                     n_heads, n_kv_heads, head_dim, write_cache=k is not None)
+    return attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
+                     scale, window, plan=plan)
+
+
 # ---------------------------------------------------------------- feed-forward
 def swiglu(gate_up):
     """silu(gate) * up for gate_up = [gate | up] of shape [T, 2I]; returns [T, I]."""

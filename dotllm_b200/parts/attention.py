@@ -75,12 +75,11 @@ class AttentionMixer(Mixer):
             rotary_dim = 0
         else:
             cos, sin, rotary_dim = fused
-        ops.rope_cache_write(q, k, v, cos, sin, rotary_dim, step.token_seq, step.token_pos,
-                             cache_view.block_table, cache_view.k, cache_view.v,
-                             self.n_heads, self.n_kv_heads, self.head_dim, write_cache=cache_view.writes)
-        a = ops.attention(q, cache_view.k, cache_view.v, step.token_seq, step.token_pos,
-                          cache_view.block_table, self.n_heads, self.n_kv_heads, self.head_dim,
-                          self.scale, int(self.window or 0), plan=step.attention_plan)
+        # rotation, cache write and attention: one kernel for a decode step, two otherwise
+        a = ops.rope_cache_attention(q, k, v, cos, sin, rotary_dim, step.token_seq, step.token_pos,
+                                     cache_view.block_table, cache_view.k, cache_view.v,
+                                     self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                                     int(self.window or 0), plan=step.attention_plan)
         return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True)
 
 

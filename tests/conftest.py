@@ -30,4 +30,5 @@ def cpu_kernels(monkeypatch):
     for name in ("gather_rows", "add_rmsnorm", "rope_cache_write", "attention", "swiglu", "linear", "gated_linear",
                  "sample", "repetition_penalty"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
+    # ops.rope_cache_attention composes the two patched functions above for anything but CUDA bfloat16
     return kernel_refs

@@ -479,6 +479,54 @@ def test_attention_decode_split_keys(nh, nkv, hd, window, blocks, monkeypatch):
     assert torch.equal(fast.cpu(), again.cpu())
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rotate", [(8, 2, 64, True), (32, 8, 128, True), (16, 1, 128, True), (6, 6, 32, False),
+                                              (12, 4, 96, False), (8, 2, 128, False)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("blocks", [0, 5])
+def test_attention_decode_with_the_new_token_inside(nh, nkv, hd, rotate, window, blocks, monkeypatch):
+    """A decode step as one kernel (rotation of q and k, cache write, attention) against the same
+    step as two kernels: the same output bits and the same cache contents.  The new token lands at
+    the start, in the middle and at the end of a page."""
+    from dotllm_b200.kernels import attention_fast, library
+    monkeypatch.setattr(attention_fast, "DECODE_BLOCKS", blocks)
+    lengths = [1, 64, 65, 128, 200, 700, 1500, 33]
+    B = len(lengths)
+    k_pool, v_pool, table, _ = make_paged(B, lengths, nkv, hd, torch.bfloat16, seed=60)
+    g = torch.Generator().manual_seed(61)
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, generator=g).to(torch.bfloat16)
+    cos, sin = plain_llama.rope_tables(range(2048), hd, 10000.0) if rotate else (None, None)
+    rd = hd if rotate else 0
+    seqs = torch.arange(B, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    d = lambda t: None if t is None else t.to(DEV)
+
+    def run(fused):
+        x = qkv.to(DEV).clone()
+        q, k, v = x[:, :nh * hd], x[:, nh * hd:(nh + nkv) * hd], x[:, (nh + nkv) * hd:]
+        kp, vp = k_pool.to(DEV).clone(), v_pool.to(DEV).clone()
+        args = (q, k, v, d(cos), d(sin), rd, seqs, pos, table.to(DEV), kp, vp, nh, nkv, hd, 1.0 / math.sqrt(hd), window)
+        if fused:
+            out = ops().rope_cache_attention(*args, plan=_decode_plan(lengths))
+        else:
+            ops().rope_cache_write(*args[:14])
+            out = ops().attention(q, kp, vp, seqs, pos, table.to(DEV), nh, nkv, hd, 1.0 / math.sqrt(hd), window,
+                                  plan=_decode_plan(lengths))
+        library.check_status()
+        live = torch.stack([kp[int(table[b, (n - 1) // 64]), :, (n - 1) % 64] for b, n in enumerate(lengths)])
+        live_v = torch.stack([vp[int(table[b, (n - 1) // 64]), :, :, (n - 1) % 64] for b, n in enumerate(lengths)])
+        return out, live, live_v
+
+    calls = []
+    real = library.call
+    monkeypatch.setattr(library, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
+    one, k_one, v_one = run(True)
+    assert calls == ["dl_attention_decode_fresh_bf16"], calls            # really one kernel
+    two, k_two, v_two = run(False)
+    assert bool(torch.isfinite(one).all())
+    assert torch.equal(one, two)
+    assert torch.equal(k_one, k_two) and torch.equal(v_one, v_two)
+
+
 def test_attention_decode_far_key():
     nh, nkv, hd, n = 8, 2, 128, 3000
     k_pool, v_pool, table, dense = make_paged(1, [n], nkv, hd, torch.bfloat16, seed=24)
