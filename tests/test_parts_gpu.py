@@ -1,7 +1,7 @@
 """Each part alone against the plain implementation, and a toy architecture defined here - a
 mixer with state of its own, a windowed attention layer, a layer that runs twice, a layer that
-reads another's cache - registered, built and stepped without touching the package."""
-import math
+reads another's cache, a feed-forward with routing - registered, built and stepped without
+touching the package."""
 from dataclasses import dataclass
 
 import pytest
