@@ -155,8 +155,8 @@ def main():
     # runs at the longest context that does (reported with its point).
     per_token = 2 * 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim
     free_bytes, _ = torch.cuda.mem_get_info()
-    budget_tokens = int(0.85 * free_bytes) // per_token
-    ctx_of = {b: min(ctx, max(256, budget_tokens // b - (room - ctx)) // 64 * 64) for b in batches}
+    fit_tokens = int(0.85 * free_bytes) // per_token
+    ctx_of = {b: min(ctx, max(256, fit_tokens // b - (room - ctx)) // 64 * 64) for b in batches}
     cache_tokens = max(b * ((ctx_of[b] + room - ctx + 63) // 64 * 64) for b in batches)
     cache = model.new_cache(max_tokens=cache_tokens, max_sequences=max(batches))
     for g in cache.kv_groups:                              # random cache contents (see the header)
