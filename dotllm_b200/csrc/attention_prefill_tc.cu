@@ -50,6 +50,24 @@ __device__ __forceinline__ void pt_sts128(uint32_t addr, uint32_t a, uint32_t b,
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// Built with -DPT_TIMELINE (DOTLLM_NVCC_EXTRA), block (0, 0) - the tile with the most pages - stamps
+// clock64 at ten points of every page into pt_timeline, which dl_attention_prefill_tc_timeline
+// copies out: a per-page timeline of the issuing thread and of one softmax warp
+// (`python -m dotllm_b200.kernels.microbench attention_prefill --timeline` prints it).
+#ifdef PT_TIMELINE
+#define PT_TIMELINE_PAGES 256
+__device__ long long pt_timeline[10][PT_TIMELINE_PAGES];
+#define PT_STAMP(row, j)                                                                          \
+    do {                                                                                          \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < PT_TIMELINE_PAGES) pt_timeline[row][j] = clock64(); \
+    } while (0)
+extern "C" int dl_attention_prefill_tc_timeline(long long* out) {
+    return cudaMemcpyFromSymbol(out, pt_timeline, sizeof(pt_timeline)) == cudaSuccess ? DL_OK : DL_ERR_LAUNCH;
+}
+#else
+#define PT_STAMP(row, j)
+#endif
+
 template <int HD>
 __global__ void __launch_bounds__(PT_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -171,6 +189,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             for (int j = 0; j <= n_kv && ok; ++j) {
                 if (j < n_kv) {
                     const int s = j % PT_STAGES, sb = j & 1;
+                    PT_STAMP(0, j);                             // issuing thread: top of page j
                     ok = tc_mbar_wait(&kv_full[s], (j / PT_STAGES) & 1, &gave_up) &&
                          (j < 2 || tc_mbar_wait(&s_empty[sb], ((j >> 1) - 1) & 1, &gave_up));
                     if (!ok) {
@@ -186,10 +205,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                                tc_operand_desc(k_addr + a * (DL_PAGE * 128)) + (uint64_t)(kk * 2), idesc_qk, k != 0 ? 1u : 0u);
                     }
                     tc_commit(&s_full[sb]);
+                    PT_STAMP(1, j);                             // scores of page j issued and committed
                 }
                 if (j >= 1) {
                     const int i = j - 1, s = i % PT_STAGES, pb = i & 1;
+                    PT_STAMP(2, i);                             // waiting for the weights of page i
                     ok = tc_mbar_wait(&p_ready[pb], (i >> 1) & 1, &gave_up);
+                    PT_STAMP(3, i);                             // weights of page i seen
                     if (!ok) {
                         if (!gave_up) atomicExch(status, 34);
                         break;
@@ -202,6 +224,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                                idesc_pv, (i | k) != 0 ? 1u : 0u);
                     tc_commit(&kv_empty[s]);
                     tc_commit(&pv_done[pb]);
+                    PT_STAMP(4, i);                             // product of page i issued and committed
                 }
             }
             if (!ok) gave_up = 1;
@@ -218,7 +241,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
             const int sb = j & 1;
+            if (warp == 2 && lane == 0) PT_STAMP(5, j);         // softmax warp: waiting for the scores of page j
             ok = __all_sync(0xffffffffu, tc_mbar_wait(&s_full[sb], (j >> 1) & 1, &gave_up));
+            if (warp == 2 && lane == 0) PT_STAMP(6, j);         // scores seen
             if (!ok) {
                 if (lane == 0 && !gave_up) atomicExch(status, 35);
                 break;
@@ -237,6 +262,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             tc_fence_before();
             __syncwarp();
             if (lane == 0) tc_mbar_arrive(&s_empty[sb]);        // the score buffer may take page j + 2
+            if (warp == 2 && lane == 0) PT_STAMP(7, j);         // scores read into registers
 
             const int key0 = (page_lo + j) * DL_PAGE;
             // pages wholly visible to every row of the tile need no mask
@@ -264,6 +290,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                 l *= corr;
             }
             // the P buffer is free once the product of page j - 2 has finished
+            if (warp == 2 && lane == 0) PT_STAMP(8, j);         // maximum done
             if (j >= 2) ok = tc_mbar_wait(&pv_done[sb], ((j >> 1) - 1) & 1, &gave_up);
             // rescaling O needs the product of page j - 1 finished too (it is the other buffer's barrier)
             if (ok && rescale && j >= 1) ok = tc_mbar_wait(&pv_done[sb ^ 1], ((j - 1) >> 1) & 1, &gave_up);
@@ -313,6 +340,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             tc_fence_async_smem();                           // shared-memory writes -> the tensor core's reads
             __syncwarp();
             if (lane == 0) tc_mbar_arrive(&p_ready[sb]);
+            if (warp == 2 && lane == 0) PT_STAMP(9, j);         // weights stored and announced
         }
         // ---- O / l -> out
         if (ok && n_kv > 0) {

@@ -105,6 +105,9 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--decode-blocks", type=int, default=0, help="attention_decode: persistent blocks (0: one per multiprocessor)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="attention_prefill: print the per-page timeline of the tcgen05 kernel (needs a library built "
+                         "with DOTLLM_NVCC_EXTRA=-DPT_TIMELINE)")
     ap.add_argument("--no-tc", action="store_true", help="attention_prefill: the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--sequential-pages", action="store_true", help="pages of a sequence lie one after another")
     args = ap.parse_args(argv)
@@ -158,6 +161,25 @@ def main(argv=None):
         fn = lambda: ops.attention(q, k_pool, v_pool, seqs, pos, table, nh, nkv, hd, 1 / math.sqrt(hd), 0, plan=plan)
         flops = 2 * T * T * nh * hd                        # causal: half of 4 T^2 nh hd
         ms, best = _time(fn, args.iters, flush)
+        if args.timeline:
+            import ctypes
+            from . import library
+            lib = library.library()
+            if not hasattr(lib, "dl_attention_prefill_tc_timeline"):
+                raise SystemExit("the library was not built with DOTLLM_NVCC_EXTRA=-DPT_TIMELINE")
+            pages = 256
+            buf = (ctypes.c_longlong * (10 * pages))()
+            lib.dl_attention_prefill_tc_timeline.argtypes = [ctypes.c_void_p]
+            if lib.dl_attention_prefill_tc_timeline(buf) != 0:
+                raise SystemExit("could not read the timeline")
+            at = lambda r, j: buf[r * pages + j]
+            lo, hi = 40, min(100, (T + 63) // 64 - 2)        # steady state, away from the diagonal's mask
+            mean = lambda a, b: sum(at(b, j) - at(a, j) for j in range(lo, hi)) / (hi - lo)
+            result["timeline_cycles"] = {
+                "page_period": (at(0, hi) - at(0, lo)) / (hi - lo),
+                "issue_scores": mean(0, 1), "wait_weights": mean(2, 3), "issue_product": mean(3, 4),
+                "softmax_wait_scores": mean(5, 6), "softmax_read_scores": mean(6, 7), "softmax_maximum": mean(7, 8),
+                "softmax_exponentials_and_store": mean(8, 9)}
         result.update(tokens=T, flops=flops, ms=ms, best_ms=best, tflops=flops / ms / 1e9,
                       frac_of_bf16_peak=flops / ms / 1e9 / tflops)
     elif args.kernel == "gemm_skinny":
