@@ -162,7 +162,7 @@ def test_attention_far_key_stands_out():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd,rd", [(4, 2, 16, 16), (6, 6, 32, 32), (8, 2, 64, 32), (3, 1, 48, 0)])
+@pytest.mark.parametrize("nh,nkv,hd,rd", [(4, 2, 16, 16), (6, 6, 32, 32), (8, 2, 64, 32), (3, 1, 48, 0), (8, 2, 128, 128)])
 @pytest.mark.parametrize("news", [[70, 1, 3], [20, 1, 3]])
 def test_rope_cache_write(dtype, nh, nkv, hd, rd, news):
     """74 tokens take the kernel that works on tiles of 64 packed tokens (the second tile mixes
