@@ -113,6 +113,28 @@ __device__ __forceinline__ void gs_epilogue(const float (&acc)[NT][4], TOut* out
     }
 }
 
+// Built with -DGS_TIMELINE (DOTLLM_NVCC_EXTRA), every warp stamps the global nanosecond timer at six
+// points of a launch into gs_timeline, which dl_gemm_skinny_timeline copies out
+// (`python -m dotllm_b200.kernels.microbench gemm_skinny --timeline` prints the spread over the grid).
+#ifdef GS_TIMELINE
+__device__ long long gs_timeline[6][2048];       // [event][block * (GS_CONSUMERS + 1) + warp]
+__device__ __forceinline__ long long gs_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define GS_STAMP(ev)                                                                                                     \
+    do {                                                                                                                 \
+        const int slot__ = blockIdx.x * (GS_CONSUMERS + 1) + (threadIdx.x >> 5);                                          \
+        if ((threadIdx.x & 31) == 0 && slot__ < 2048) gs_timeline[ev][slot__] = gs_now();                                 \
+    } while (0)
+extern "C" int dl_gemm_skinny_timeline(long long* out) {
+    return cudaMemcpyFromSymbol(out, gs_timeline, sizeof(gs_timeline)) == cudaSuccess ? DL_OK : DL_ERR_LAUNCH;
+}
+#else
+#define GS_STAMP(ev)
+#endif
+
 // The product of a launch: its operands and how its chunks are cut (see GsPlan below).
 struct GsWork {
     const __nv_bfloat16* x;
@@ -204,6 +226,7 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
             *r.gave_up = 1;
             dead = true;
         }
+        if (cur == begin) GS_STAMP(2);                        // the first chunk of the share has landed
         if (!dead) {
             // this lane's byte address in shared space; the loads below are constant offsets away.
             // Rows beyond the matrix and k beyond K arrived as zeros, so nothing needs guarding.
@@ -231,6 +254,7 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
             __syncwarp();
             if (lane == 0) gs_mbar_arrive(&r.empty_bar[warp][slot]);
         }
+        if (cur == end - 1) GS_STAMP(3);                      // the last chunk of the share is consumed
         if (kc == cpt - 1 || cur == end - 1) {
             // ---- the segment [seg_begin, cur] of this tile is done
             const bool whole = (seg_begin == tile * cpt) && (kc == cpt - 1);
@@ -306,7 +330,9 @@ template <int NT, typename TOut, bool FUSE_SWIGLU>
 __global__ void __launch_bounds__(GS_THREADS, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const GsWork work, int early_weights,
                    float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ status) {
+    GS_STAMP(0);                                              // block started
     GS_INIT_RINGS();
+    GS_STAMP(1);                                              // barriers ready
     if (warp == GS_CONSUMERS) {
         // ------------------------------------------------------------ producer warp
         // When the caller vouches that no pending work writes the weights (early_weights), the
@@ -323,8 +349,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const GsWork work, 
         int cnt = 0;
         bool dead = false;
         gs_consume<NT, TOut, FUSE_SWIGLU>(work, rings, partials, counters, warp, lane, cnt, dead);
+        GS_STAMP(4);                                          // share done, hand-over of cut tiles included
     }
     __syncthreads();                                         // nobody leaves while copies may still land
+    GS_STAMP(5);
 }
 
 // How the work of an (N, K) matrix is cut: tiles of 16 rows (8 gate + 8 up when gated), chunks per

@@ -195,6 +195,29 @@ def main(argv=None):
         lib_fn = lambda: torch.mm(x, w.t())
         lib_ms, _ = _time(lib_fn, args.iters, flush)
         result["library_mm_ms"] = lib_ms
+        if args.timeline:
+            import ctypes
+            from . import library
+            lib = library.library()
+            if not hasattr(lib, "dl_gemm_skinny_timeline"):
+                raise SystemExit("the library was not built with DOTLLM_NVCC_EXTRA=-DGS_TIMELINE")
+            flush.add_(1)
+            torch.cuda.synchronize()
+            fn()                                            # one cold launch
+            torch.cuda.synchronize()
+            buf = (ctypes.c_longlong * (6 * 2048))()
+            lib.dl_gemm_skinny_timeline.argtypes = [ctypes.c_void_p]
+            if lib.dl_gemm_skinny_timeline(buf) != 0:
+                raise SystemExit("could not read the timeline")
+            blocks = min(148, 2048 // 7)
+            first = min(buf[b * 7] for b in range(blocks) if buf[b * 7])
+            names = ["block_start", "barriers_ready", "first_chunk_landed", "last_chunk_consumed", "share_done", "block_end"]
+            spread = {}
+            for e, name in enumerate(names):
+                warps = [0] if e in (0, 1, 5) else range(6)
+                v = [buf[e * 2048 + b * 7 + w] - first for b in range(blocks) for w in warps if buf[e * 2048 + b * 7 + w]]
+                spread[name] = [min(v), sum(v) // len(v), max(v)]
+            result["timeline_ns_min_mean_max"] = spread
         # The same product as a decode step issues it: launches back to back from a captured graph,
         # each on a different copy of W (together larger than the L2), with and without the
         # overlap of programmatic dependent launch.
