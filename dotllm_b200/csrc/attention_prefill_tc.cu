@@ -5,20 +5,28 @@
 // scaled by 1/sqrt(hd), softmax with the running maximum subtracted, weighted sum of values, query
 // head h reading KV head h / group.
 //
-// One block per (tile of 128 query rows, query head).  The cache's layouts are the tensor core's
-// K-major operands as they lie: a K page [64 keys][hd] is B of S = Q K^T, a transposed V page
-// [hd][64 keys] is B of O += P V.  Six warps with fixed roles:
-//   warp 0     tensor-map copies (TMA, 128-byte swizzle): the Q tile once, then K and V pages through
-//              a ring of four stages;
-//   warp 1     one thread issues tcgen05.mma: S(j) = Q K_j^T into one of two 64-column score buffers
-//              in tensor memory, and O += P(j-1) V(j-1) behind it, so that the tensor core computes the
-//              next page's scores while the softmax warps work on this page's;
-//   warps 2-5  softmax, one query row per thread (tensor-memory lane = row): read the row's 64
-//              scores with tcgen05.ld, mask, running maximum and sum in float32 (base 2), write
-//              P as bfloat16 into shared memory in the operand's swizzled layout.  O stays in tensor
-//              memory for the whole tile; it is rescaled only when a row's maximum has grown by more
-//              than 2^8 since the last rescale (the weights stay below 2^8 meanwhile, which bfloat16
-//              and the float32 sums hold without loss), and divided by the row's sum at the end.
+// One block per (256 consecutive query rows of a sequence, query head): two tiles of 128 rows that
+// share the K and V pages they walk.  The cache's layouts are the tensor core's K-major operands as
+// they lie: a K page [64 keys][hd] is B of S = Q K^T, a transposed V page [hd][64 keys] is B of
+// O += P V.  Twelve warps with fixed roles:
+//   warp 0       tensor-map copies (TMA, 128-byte swizzle): the two Q tiles once, then K and V pages
+//                through a ring of stages;
+//   warps 1, 2   one thread each issues the tcgen05.mma of one tile's scores: S(j) = Q K_j^T into one
+//                of the tile's two 64-column score buffers in tensor memory, so that the tensor core
+//                computes the next page's scores while the softmax warps work on this page's;
+//   warp 3       one thread issues both tiles' O += P(j) V(j) as their weights become ready, and hands
+//                the stage back when every tile that reads the page has had its product issued;
+//   warps 4-7    softmax of tile 0, warps 8-11 of tile 1, one query row per thread (tensor-memory lane
+//                = row): read the row's 64 scores with tcgen05.ld, mask, running maximum and sum in
+//                float32 (base 2), write P as bfloat16 into shared memory in the operand's swizzled
+//                layout.  O stays in tensor memory for the whole tile; it is rescaled only when a
+//                row's maximum has grown by more than 2^8 since the last rescale (the weights stay
+//                below 2^8 meanwhile, which bfloat16 and the float32 sums hold without loss), and
+//                divided by the row's sum at the end.
+// The tensor core takes about as long for an MMA of 64 or 128 columns as for one of 256 (measured),
+// so the kernel is bound by the number of MMAs: two tiles keep that pipe fed while each tile's
+// softmax threads work through their page.  Tensor memory: 4 x 64 columns of scores, 2 x 128 of
+// outputs - all 512, which one block per SM (its shared memory) makes safe.
 // Keys that no query of the tile may see are never used: masked scores are replaced, not
 // multiplied, and the slots of the last page beyond the sequence's length (which may hold
 // anything) are zeroed in the V stage before the product.
@@ -31,10 +39,11 @@
 #include <mutex>
 #include <unordered_map>
 
-#define PT_ROWS 128
-#define PT_STAGES 4
-#define PT_THREADS 192
-#define PT_TMEM_COLS 256
+#define PT_ROWS 128                          // query rows of a tile
+#define PT_TILES 2                           // tiles of a block: it covers PT_TILES * PT_ROWS consecutive rows
+#define PT_STAGES(hd) ((hd) > 64 ? 3 : 4)    // K/V pages in flight: what 227 KB of shared memory leave room for
+#define PT_THREADS 384
+#define PT_TMEM_COLS 512
 #define PT_RESCALE_STEP 8.0f                 // log2 units a row's maximum may grow before O is rescaled
 
 __device__ __forceinline__ float pt_ex2(float x) {             // 2^x, 2 ulp; ex2(-inf) = 0
@@ -51,12 +60,12 @@ __device__ __forceinline__ void pt_sts128(uint32_t addr, uint32_t a, uint32_t b,
 }
 
 // Built with -DPT_TIMELINE (DOTLLM_NVCC_EXTRA), block (0, 0) - the tile with the most pages - stamps
-// clock64 at ten points of every page into pt_timeline, which dl_attention_prefill_tc_timeline
+// clock64 at twelve points of every page into pt_timeline, which dl_attention_prefill_tc_timeline
 // copies out: a per-page timeline of the issuing thread and of one softmax warp
 // (`python -m dotllm_b200.kernels.microbench attention_prefill --timeline` prints it).
 #ifdef PT_TIMELINE
 #define PT_TIMELINE_PAGES 256
-__device__ long long pt_timeline[10][PT_TIMELINE_PAGES];
+__device__ long long pt_timeline[12][PT_TIMELINE_PAGES];
 #define PT_STAMP(row, j)                                                                          \
     do {                                                                                          \
         if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < PT_TIMELINE_PAGES) pt_timeline[row][j] = clock64(); \
@@ -68,6 +77,14 @@ extern "C" int dl_attention_prefill_tc_timeline(long long* out) {
 #define PT_STAMP(row, j)
 #endif
 
+// Where tile `t` of a block stands: its rows, the keys they may see, and its place in the block's walk.
+struct PtTile {
+    int rows;                // live rows (0: the tile does not exist)
+    int pos0, pos_last;      // positions of its first and last live row
+    int first_key;           // first key any of its rows may see
+    int j_lo, j_hi;          // the pages of the block's walk it takes part in (j_lo > j_hi: none)
+};
+
 template <int HD>
 __global__ void __launch_bounds__(PT_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -77,44 +94,63 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                             const int32_t* __restrict__ cu_new, const int32_t* __restrict__ block_table, int bt_stride,
                             int nkv, int group, float scale, int window, int* __restrict__ status) {
     constexpr int ATOMS = HD / 64;                           // 64-dim (128-byte) slices of a head
+    constexpr int STAGES = PT_STAGES(HD);
     constexpr uint32_t Q_BYTES = PT_ROWS * HD * 2;
     constexpr uint32_t K_BYTES = DL_PAGE * HD * 2, V_BYTES = HD * DL_PAGE * 2;
     constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
     constexpr uint32_t P_BYTES = PT_ROWS * DL_PAGE * 2;
     extern __shared__ unsigned char pt_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)pt_smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_smem = base;                            // [atom][128 rows][64 dims]
-    unsigned char* kv_smem = q_smem + Q_BYTES;               // [stage][K: [atom][64 keys][64 dims] | V: [hd][64 keys]]
-    unsigned char* p_smem = kv_smem + PT_STAGES * STAGE_BYTES;   // [2][128 rows][64 keys]
-    __shared__ uint64_t q_full, kv_full[PT_STAGES], kv_empty[PT_STAGES], s_full[2], s_empty[2], p_ready[2], pv_done[2];
+    unsigned char* q_smem = base;                            // [tile][atom][128 rows][64 dims]
+    unsigned char* kv_smem = q_smem + PT_TILES * Q_BYTES;    // [stage][K: [atom][64 keys][64 dims] | V: [hd][64 keys]]
+    unsigned char* p_smem = kv_smem + STAGES * STAGE_BYTES;  // [tile][2][128 rows][64 keys]
+    __shared__ uint64_t q_full[PT_TILES], kv_full[STAGES], kv_empty[STAGES];
+    __shared__ uint64_t s_full[PT_TILES][2], s_empty[PT_TILES][2], p_ready[PT_TILES][2], pv_done[PT_TILES][2];
     __shared__ uint32_t tmem_base_holder;
     __shared__ volatile int gave_up;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = gridDim.x - 1 - blockIdx.x;             // later tiles see more keys: start them first
+    const int blk = gridDim.x - 1 - blockIdx.x;              // later rows see more keys: start them first
     const int head = blockIdx.y, kvh = head / group;
-    const int b = tile_seq[tile], row0 = tile_row0[tile];
+    const int b = tile_seq[blk], row0 = tile_row0[blk];
     const int start = seq_start[b], n_new = seq_new[b];
-    const int rows = min(PT_ROWS, n_new - row0);             // live rows of the tile
-    const int pos0 = start + row0;                           // position of the tile's first row
-    const int pos_last = pos0 + rows - 1;
     const int total = start + n_new;                         // keys the sequence holds after this step
-    const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int page_lo = first_key / DL_PAGE, page_hi = pos_last / DL_PAGE;
-    const int n_kv = page_hi - page_lo + 1;                  // pages this tile walks
+    PtTile tiles[PT_TILES];
+#pragma unroll
+    for (int t = 0; t < PT_TILES; ++t) {
+        PtTile& T = tiles[t];
+        T.rows = max(0, min(PT_ROWS, n_new - row0 - t * PT_ROWS));
+        T.pos0 = start + row0 + t * PT_ROWS;
+        T.pos_last = T.pos0 + T.rows - 1;
+        T.first_key = (window > 0 && T.pos0 - window + 1 > 0) ? T.pos0 - window + 1 : 0;
+    }
+    // The block walks the pages from the first one tile 0 sees to the last one its last live tile sees;
+    // a tile joins at its own first page and leaves after its own last (the ranges overlap or touch).
+    const int page_lo = tiles[0].first_key / DL_PAGE;
+    int page_hi = tiles[0].pos_last / DL_PAGE;
+#pragma unroll
+    for (int t = 0; t < PT_TILES; ++t) {
+        PtTile& T = tiles[t];
+        T.j_lo = T.first_key / DL_PAGE - page_lo;
+        T.j_hi = T.rows > 0 ? T.pos_last / DL_PAGE - page_lo : T.j_lo - 1;
+        if (T.rows > 0) page_hi = max(page_hi, T.pos_last / DL_PAGE);
+    }
+    const int n_kv = page_hi - page_lo + 1;                  // pages this block walks
 
     if (threadIdx.x == 0) {
         gave_up = 0;
-        tc_mbar_init(&q_full, 1);
-        for (int s = 0; s < PT_STAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             tc_mbar_init(&kv_full[s], 1);
             tc_mbar_init(&kv_empty[s], 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            tc_mbar_init(&s_full[i], 1);
-            tc_mbar_init(&s_empty[i], 4);                     // one arrival per softmax warp
-            tc_mbar_init(&p_ready[i], 4);
-            tc_mbar_init(&pv_done[i], 1);
+        for (int t = 0; t < PT_TILES; ++t) {
+            tc_mbar_init(&q_full[t], 1);
+            for (int i = 0; i < 2; ++i) {
+                tc_mbar_init(&s_full[t][i], 1);
+                tc_mbar_init(&s_empty[t][i], 4);              // one arrival per softmax warp of the tile
+                tc_mbar_init(&p_ready[t][i], 4);
+                tc_mbar_init(&pv_done[t][i], 1);
+            }
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -123,17 +159,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_holder;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;    // S0 at 0, S1 at 64, O at 128 ..
+    // scores: tile t, buffer i at column (2 t + i) * 64; outputs: tile t at column 256 + 128 t
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * PT_TILES * DL_PAGE;
 
     if (warp == 0) {
         // ------------------------------------------------------------ copies
         bool stop = false;
         int issued = 0;
         if (lane == 0) {
-            tc_mbar_expect(&q_full, Q_BYTES);
 #pragma unroll
-            for (int a = 0; a < ATOMS; ++a)
-                dl_tma_load_2d(q_smem + a * (PT_ROWS * 128), &tmap_q, head * HD + a * 64, cu_new[b] + row0, &q_full);
+            for (int t = 0; t < PT_TILES; ++t) {
+                if (tiles[t].rows <= 0) continue;
+                tc_mbar_expect(&q_full[t], Q_BYTES);
+#pragma unroll
+                for (int a = 0; a < ATOMS; ++a)
+                    dl_tma_load_2d(q_smem + t * Q_BYTES + a * (PT_ROWS * 128), &tmap_q, head * HD + a * 64,
+                                   cu_new[b] + row0 + t * PT_ROWS, &q_full[t]);
+            }
         }
         const int32_t* pages = block_table + (size_t)b * bt_stride + page_lo;
         for (int j0 = 0; j0 < n_kv && !stop; j0 += 32) {
@@ -141,12 +183,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             const int count = min(32, n_kv - j0);
             for (int jj = 0; jj < count; ++jj) {
                 const int page = __shfl_sync(0xffffffffu, mine, jj);
-                const int j = j0 + jj, s = j % PT_STAGES;
+                const int j = j0 + jj, s = j % STAGES;
                 int bad = 0;
                 if (lane == 0) {
                     if (page < 0 || page >= n_pages) {
                         bad = 2;
-                    } else if (j >= PT_STAGES && !tc_mbar_wait(&kv_empty[s], ((j / PT_STAGES) - 1) & 1, &gave_up)) {
+                    } else if (j >= STAGES && !tc_mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, &gave_up)) {
                         bad = 31;
                     } else {
                         unsigned char* k_dst = kv_smem + (size_t)s * STAGE_BYTES;
@@ -171,79 +213,98 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         }
         if (stop && lane == 0) {
             // copies already issued must land before the block's shared memory is released
-            long long t0 = clock64();
-            while (!tc_mbar_try(&q_full, 0) && clock64() - t0 < TC_WAIT_CYCLES) {}
-            for (int i = max(0, issued - PT_STAGES); i < issued; ++i) {
-                t0 = clock64();
-                while (!tc_mbar_try(&kv_full[i % PT_STAGES], (i / PT_STAGES) & 1) && clock64() - t0 < TC_WAIT_CYCLES) {}
+            for (int t = 0; t < PT_TILES; ++t) {
+                if (tiles[t].rows <= 0) continue;
+                const long long t0 = clock64();
+                while (!tc_mbar_try(&q_full[t], 0) && clock64() - t0 < TC_WAIT_CYCLES) {}
+            }
+            for (int i = max(0, issued - STAGES); i < issued; ++i) {
+                const long long t0 = clock64();
+                while (!tc_mbar_try(&kv_full[i % STAGES], (i / STAGES) & 1) && clock64() - t0 < TC_WAIT_CYCLES) {}
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ tensor-core issue
-        if (lane == 0) {
-            const uint32_t idesc_qk = tc_idesc_bf16(PT_ROWS, DL_PAGE), idesc_pv = tc_idesc_bf16(PT_ROWS, HD);
-            const uint32_t q_addr = tc_smem(q_smem), p_addr = tc_smem(p_smem);
-            bool ok = tc_mbar_wait(&q_full, 0, &gave_up);
+    } else if (warp == 1 || warp == 2) {
+        // ------------------------------------------------------------ tensor-core issue: the scores of tile `t`
+        const int t = warp - 1;
+        const PtTile T = tiles[t];
+        if (lane == 0 && T.rows > 0) {
+            const uint32_t idesc_qk = tc_idesc_bf16(PT_ROWS, DL_PAGE);
+            const uint32_t q_addr = tc_smem(q_smem + t * Q_BYTES);
+            bool ok = tc_mbar_wait(&q_full[t], 0, &gave_up);
             if (!ok && !gave_up) atomicExch(status, 32);
-            // page j's product with V is issued behind page j+1's scores
-            for (int j = 0; j <= n_kv && ok; ++j) {
-                if (j < n_kv) {
-                    const int s = j % PT_STAGES, sb = j & 1;
-                    PT_STAMP(0, j);                             // issuing thread: top of page j
-                    ok = tc_mbar_wait(&kv_full[s], (j / PT_STAGES) & 1, &gave_up) &&
-                         (j < 2 || tc_mbar_wait(&s_empty[sb], ((j >> 1) - 1) & 1, &gave_up));
-                    if (!ok) {
-                        if (!gave_up) atomicExch(status, 33);
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t k_addr = tc_smem(kv_smem + (size_t)s * STAGE_BYTES);
-#pragma unroll
-                    for (int k = 0; k < HD / 16; ++k) {
-                        const int a = k / 4, kk = k % 4;        // 64-dim slice, 16-dim step inside it (32 bytes)
-                        tc_mma(tmem_s + (uint32_t)(sb * DL_PAGE), tc_operand_desc(q_addr + a * (PT_ROWS * 128)) + (uint64_t)(kk * 2),
-                               tc_operand_desc(k_addr + a * (DL_PAGE * 128)) + (uint64_t)(kk * 2), idesc_qk, k != 0 ? 1u : 0u);
-                    }
-                    tc_commit(&s_full[sb]);
-                    PT_STAMP(1, j);                             // scores of page j issued and committed
+            for (int j = T.j_lo; j <= T.j_hi && ok; ++j) {
+                const int c = j - T.j_lo, s = j % STAGES, sb = c & 1;
+                if (t == 0) PT_STAMP(0, j);                     // issuing thread: top of page j
+                ok = tc_mbar_wait(&kv_full[s], (j / STAGES) & 1, &gave_up) &&
+                     (c < 2 || tc_mbar_wait(&s_empty[t][sb], ((c >> 1) - 1) & 1, &gave_up));
+                if (!ok) {
+                    if (!gave_up) atomicExch(status, 33);
+                    break;
                 }
-                if (j >= 1) {
-                    const int i = j - 1, s = i % PT_STAGES, pb = i & 1;
-                    PT_STAMP(2, i);                             // waiting for the weights of page i
-                    ok = tc_mbar_wait(&p_ready[pb], (i >> 1) & 1, &gave_up);
-                    PT_STAMP(3, i);                             // weights of page i seen
+                tc_fence_after();
+                const uint32_t k_addr = tc_smem(kv_smem + (size_t)s * STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const int a = k / 4, kk = k % 4;            // 64-dim slice, 16-dim step inside it (32 bytes)
+                    tc_mma(tmem_s + (uint32_t)((2 * t + sb) * DL_PAGE), tc_operand_desc(q_addr + a * (PT_ROWS * 128)) + (uint64_t)(kk * 2),
+                           tc_operand_desc(k_addr + a * (DL_PAGE * 128)) + (uint64_t)(kk * 2), idesc_qk, k != 0 ? 1u : 0u);
+                }
+                tc_commit(&s_full[t][sb]);
+                if (t == 0) PT_STAMP(1, j);                     // scores of page j issued and committed
+            }
+            if (!ok) gave_up = 1;
+        }
+    } else if (warp == 3) {
+        // ------------------------------------------------------------ tensor-core issue: the products with V
+        if (lane == 0) {
+            const uint32_t idesc_pv = tc_idesc_bf16(PT_ROWS, HD);
+            bool ok = true;
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const int s = j % STAGES;
+                const uint32_t v_addr = tc_smem(kv_smem + (size_t)s * STAGE_BYTES + K_BYTES);
+#pragma unroll
+                for (int t = 0; t < PT_TILES; ++t) {
+                    if (j < tiles[t].j_lo || j > tiles[t].j_hi) continue;
+                    const int c = j - tiles[t].j_lo, pb = c & 1;
+                    if (t == 0) PT_STAMP(2, j);                 // waiting for the weights of page j
+                    ok = tc_mbar_wait(&p_ready[t][pb], (c >> 1) & 1, &gave_up) && tc_mbar_wait(&kv_full[s], (j / STAGES) & 1, &gave_up);
+                    if (t == 0) PT_STAMP(3, j);                 // weights of page j seen
                     if (!ok) {
                         if (!gave_up) atomicExch(status, 34);
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t v_addr = tc_smem(kv_smem + (size_t)s * STAGE_BYTES + K_BYTES);
+                    const uint32_t p_addr = tc_smem(p_smem + (2 * t + pb) * P_BYTES);
 #pragma unroll
                     for (int k = 0; k < DL_PAGE / 16; ++k)
-                        tc_mma(tmem_o, tc_operand_desc(p_addr + pb * P_BYTES) + (uint64_t)(k * 2), tc_operand_desc(v_addr) + (uint64_t)(k * 2),
-                               idesc_pv, (i | k) != 0 ? 1u : 0u);
-                    tc_commit(&kv_empty[s]);
-                    tc_commit(&pv_done[pb]);
-                    PT_STAMP(4, i);                             // product of page i issued and committed
+                        tc_mma(tmem_o + (uint32_t)(t * HD), tc_operand_desc(p_addr) + (uint64_t)(k * 2), tc_operand_desc(v_addr) + (uint64_t)(k * 2),
+                               idesc_pv, (c | k) != 0 ? 1u : 0u);
+                    tc_commit(&pv_done[t][pb]);
+                    if (t == 0) PT_STAMP(4, j);                 // product of page j issued and committed
                 }
+                if (ok) tc_commit(&kv_empty[s]);                // every tile that reads this page has issued its product
             }
             if (!ok) gave_up = 1;
         }
     } else {
-        // ------------------------------------------------------------ softmax: thread -> row
-        const int quarter = warp & 3;
+        // ------------------------------------------------------------ softmax: thread -> row of tile `t`
+        const int t = (warp - 4) >> 2, quarter = warp & 3;
+        const PtTile T = tiles[t];
         const int r = quarter * 32 + lane;                   // row of the tile = lane of tensor memory
-        const int pos = pos0 + r;
-        const bool live = r < rows;
+        const int pos = T.pos0 + r;
+        const bool live = r < T.rows;
+        const bool stamps = (warp == 4 && lane == 0);
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t my_s = tmem_s + lane_base + (uint32_t)(2 * t * DL_PAGE), my_o = tmem_o + lane_base + (uint32_t)(t * HD);
         const float scale2 = scale * 1.4426950408889634f;    // scores in units of log2
         float m_ref = -INFINITY, l = 0.f;                    // reference maximum (log2 units), sum of weights
         bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            const int sb = j & 1;
-            if (warp == 2 && lane == 0) PT_STAMP(5, j);         // softmax warp: waiting for the scores of page j
-            ok = __all_sync(0xffffffffu, tc_mbar_wait(&s_full[sb], (j >> 1) & 1, &gave_up));
-            if (warp == 2 && lane == 0) PT_STAMP(6, j);         // scores seen
+        const int n_mine = T.j_hi - T.j_lo + 1;
+        for (int c = 0; c < n_mine; ++c) {
+            const int j = T.j_lo + c, sb = c & 1;
+            if (stamps) PT_STAMP(5, j);                         // softmax warp: waiting for the scores of page j
+            ok = __all_sync(0xffffffffu, tc_mbar_wait(&s_full[t][sb], (c >> 1) & 1, &gave_up));
+            if (stamps) PT_STAMP(6, j);                         // scores seen
             if (!ok) {
                 if (lane == 0 && !gave_up) atomicExch(status, 35);
                 break;
@@ -252,22 +313,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             float sc[64];
             {
                 float half[32];
-                tc_tmem_load32(tmem_s + lane_base + (uint32_t)(sb * DL_PAGE), half);
+                tc_tmem_load32(my_s + (uint32_t)(sb * DL_PAGE), half);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sc[i] = half[i];
-                tc_tmem_load32(tmem_s + lane_base + (uint32_t)(sb * DL_PAGE + 32), half);
+                tc_tmem_load32(my_s + (uint32_t)(sb * DL_PAGE + 32), half);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sc[32 + i] = half[i];
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(&s_empty[sb]);        // the score buffer may take page j + 2
-            if (warp == 2 && lane == 0) PT_STAMP(7, j);         // scores read into registers
+            if (lane == 0) tc_mbar_arrive(&s_empty[t][sb]);     // the score buffer may take the tile's page after next
+            if (stamps) PT_STAMP(7, j);                         // scores read into registers
 
             const int key0 = (page_lo + j) * DL_PAGE;
             // pages wholly visible to every row of the tile need no mask
-            const bool ragged = rows < PT_ROWS || key0 + DL_PAGE - 1 > pos0 || key0 < first_key ||
-                                (window > 0 && key0 <= pos_last - window);
+            const bool ragged = T.rows < PT_ROWS || key0 + DL_PAGE - 1 > T.pos0 || key0 < T.first_key ||
+                                (window > 0 && key0 <= T.pos_last - window);
             if (ragged) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
@@ -276,10 +337,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                     if (!seen) sc[i] = -INFINITY;
                 }
             }
-            float mx = sc[0];
+            float mx4[4] = {sc[0], sc[1], sc[2], sc[3]};     // four chains: a single one is 64 dependent steps
 #pragma unroll
-            for (int i = 1; i < 64; ++i) mx = fmaxf(mx, sc[i]);
-            mx *= scale2;                                    // scale > 0: the maximum of the scaled scores
+            for (int i = 4; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;   // scale > 0: the maximum of the scaled scores
             const bool grow = mx > m_ref + PT_RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
             const bool rescale = __any_sync(0xffffffffu, grow);   // the warp decides: tensor-memory accesses are warp-wide
             float corr = 1.f;
@@ -289,74 +350,78 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                 m_ref = m_new;
                 l *= corr;
             }
-            // the P buffer is free once the product of page j - 2 has finished
-            if (warp == 2 && lane == 0) PT_STAMP(8, j);         // maximum done
-            if (j >= 2) ok = tc_mbar_wait(&pv_done[sb], ((j >> 1) - 1) & 1, &gave_up);
-            // rescaling O needs the product of page j - 1 finished too (it is the other buffer's barrier)
-            if (ok && rescale && j >= 1) ok = tc_mbar_wait(&pv_done[sb ^ 1], ((j - 1) >> 1) & 1, &gave_up);
+            if (stamps) PT_STAMP(8, j);                         // maximum done
+            // the P buffer is free once the product of the tile's page before last has finished
+            if (c >= 2) ok = tc_mbar_wait(&pv_done[t][sb], ((c >> 1) - 1) & 1, &gave_up);
+            // rescaling O needs the product of the page before finished too (it is the other buffer's barrier)
+            if (ok && rescale && c >= 1) ok = tc_mbar_wait(&pv_done[t][sb ^ 1], ((c - 1) >> 1) & 1, &gave_up);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 if (lane == 0 && !gave_up) atomicExch(status, 36);
                 break;
             }
-            if (rescale && j >= 1) {
+            if (stamps) PT_STAMP(10, j);                        // the weights' buffer is free
+            if (rescale && c >= 1) {
                 tc_fence_after();
 #pragma unroll 1
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     float o[32];
-                    tc_tmem_load32(tmem_o + lane_base + (uint32_t)c0, o);
+                    tc_tmem_load32(my_o + (uint32_t)c0, o);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= corr;
-                    tc_tmem_store32(tmem_o + lane_base + (uint32_t)c0, o);
+                    tc_tmem_store32(my_o + (uint32_t)c0, o);
                 }
                 tc_fence_before();
             }
             // weights of this page, as the A operand of P V: row r is 128 bytes, its 16-byte chunk c at c ^ (r & 7)
             const float sub = (m_ref == -INFINITY) ? 0.f : m_ref;
-            const uint32_t p_row = tc_smem(p_smem + sb * P_BYTES) + (uint32_t)r * 128u;
-            float sum = 0.f;
+            const uint32_t p_row = tc_smem(p_smem + (2 * t + sb) * P_BYTES) + (uint32_t)r * 128u;
+            // all exponentials first, in place: the special-function unit takes them back to back, and the
+            // sums, the packing and the stores follow in its shadow
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                float p[8];
+            for (int i = 0; i < 64; ++i) sc[i] = pt_ex2(fmaf(sc[i], scale2, -sub));
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    p[i] = pt_ex2(fmaf(sc[8 * c + i], scale2, -sub));
-                    sum += p[i];
-                }
-                pt_sts128(p_row + (uint32_t)((c ^ (r & 7)) << 4), pt_pack(p[0], p[1]), pt_pack(p[2], p[3]), pt_pack(p[4], p[5]),
+            for (int i = 0; i < 64; ++i) sum4[i & 3] += sc[i];
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                const float* p = sc + 8 * ch;
+                pt_sts128(p_row + (uint32_t)((ch ^ (r & 7)) << 4), pt_pack(p[0], p[1]), pt_pack(p[2], p[3]), pt_pack(p[4], p[5]),
                           pt_pack(p[6], p[7]));
             }
-            l += sum;
             // Slots of the sequence's last page beyond its length may hold anything: make them exact
-            // zeros in the V stage (row d of V^T is 128 bytes, key k in chunk (k / 8) ^ (d & 7)).
+            // zeros in the V stage (row d of V^T is 128 bytes, key k in chunk (k / 8) ^ (d & 7)).  Both
+            // tiles may do this to the same page; they write the same zeros.
             if (key0 + DL_PAGE > total) {
-                unsigned char* v_stage = kv_smem + (size_t)(j % PT_STAGES) * STAGE_BYTES + K_BYTES;
+                unsigned char* v_stage = kv_smem + (size_t)(j % STAGES) * STAGE_BYTES + K_BYTES;
                 const int kz = total - key0;                 // first dead key of the page (> 0: the page holds live keys)
                 for (int d = r; d < HD; d += PT_ROWS)
                     for (int k = kz; k < DL_PAGE; ++k)
                         *reinterpret_cast<__nv_bfloat16*>(v_stage + d * 128 + ((((k >> 3) ^ (d & 7)) << 4) | ((k & 7) << 1))) =
                             __float2bfloat16_rn(0.f);
             }
+            if (stamps) PT_STAMP(11, j);                        // weights stored
             tc_fence_async_smem();                           // shared-memory writes -> the tensor core's reads
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(&p_ready[sb]);
-            if (warp == 2 && lane == 0) PT_STAMP(9, j);         // weights stored and announced
+            if (lane == 0) tc_mbar_arrive(&p_ready[t][sb]);
+            if (stamps) PT_STAMP(9, j);                         // weights stored and announced
         }
         // ---- O / l -> out
-        if (ok && n_kv > 0) {
-            const int last = n_kv - 1;
-            ok = __all_sync(0xffffffffu, tc_mbar_wait(&pv_done[last & 1], (last >> 1) & 1, &gave_up));
+        if (ok && n_mine > 0) {
+            const int last = n_mine - 1;
+            ok = __all_sync(0xffffffffu, tc_mbar_wait(&pv_done[t][last & 1], (last >> 1) & 1, &gave_up));
             if (!ok && lane == 0 && !gave_up) atomicExch(status, 37);
         }
         if (!ok) gave_up = 1;
-        if (ok) {
+        if (ok && n_mine > 0) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = out + (size_t)(cu_new[b] + row0 + r) * out_stride + (size_t)head * HD;
+            __nv_bfloat16* dst = out + (size_t)(cu_new[b] + row0 + t * PT_ROWS + r) * out_stride + (size_t)head * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 float o[32];
-                tc_tmem_load32(tmem_o + lane_base + (uint32_t)c0, o);
+                tc_tmem_load32(my_o + (uint32_t)c0, o);
                 if (live) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
@@ -414,7 +479,8 @@ static int pt_launch(dim3 grid, cudaStream_t s, const void* q, int q_stride, int
                      const void* k_pool, const void* v_pool, int n_pages, const int32_t* tile_seq, const int32_t* tile_row0,
                      const int32_t* seq_start, const int32_t* seq_new, const int32_t* cu_new, const int32_t* block_table,
                      int bt_stride, int nh, int nkv, float scale, int window, int* status) {
-    const size_t smem = (size_t)PT_ROWS * HD * 2 + (size_t)PT_STAGES * 2 * DL_PAGE * HD * 2 + 2 * PT_ROWS * DL_PAGE * 2 + 1024;
+    const size_t smem = (size_t)PT_TILES * PT_ROWS * HD * 2 + (size_t)PT_STAGES(HD) * 2 * DL_PAGE * HD * 2 +
+                        (size_t)PT_TILES * 2 * PT_ROWS * DL_PAGE * 2 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -23,7 +23,8 @@ _library.register_signatures({
                                      _F, _I, _P, _P],
 })
 
-PREFILL_ROWS = 128       # query rows per block of the prefill kernels (AP_ROWS, PT_ROWS)
+PREFILL_ROWS = 128       # query rows per block of the mma.sync prefill kernel (AP_ROWS)
+PREFILL_TC_ROWS = 256    # ... and of the tcgen05 one (PT_TILES * PT_ROWS)
 PREFILL_TC_HEAD_DIMS = (64, 128)     # head sizes of the tcgen05 prefill kernel; others take the mma.sync one
 PREFILL_TC = True        # False: always the mma.sync kernel (tests compare the two)
 
@@ -96,17 +97,19 @@ def decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_h
 
 def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_kv_heads, head_dim,
              scale, window, plan):
-    if "prefill_tiles" not in plan.scratch:
+    tc = PREFILL_TC and head_dim in PREFILL_TC_HEAD_DIMS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+    rows = PREFILL_TC_ROWS if tc else PREFILL_ROWS
+    if ("prefill_tiles", rows) not in plan.scratch:
         tile_seq, tile_row0 = [], []
         for b, n in enumerate(plan.news):
-            for r0 in range(0, n, PREFILL_ROWS):
+            for r0 in range(0, n, rows):
                 tile_seq.append(b)
                 tile_row0.append(r0)
         host = torch.tensor(tile_seq + tile_row0, dtype=torch.int32)
         dev = host.pin_memory().to(q.device, non_blocking=True)
-        plan.scratch["prefill_tiles"] = (dev[:len(tile_seq)], dev[len(tile_seq):], len(tile_seq))
-    tile_seq, tile_row0, n_tiles = plan.scratch["prefill_tiles"]
-    if PREFILL_TC and head_dim in PREFILL_TC_HEAD_DIMS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+        plan.scratch[("prefill_tiles", rows)] = (dev[:len(tile_seq)], dev[len(tile_seq):], len(tile_seq))
+    tile_seq, tile_row0, n_tiles = plan.scratch[("prefill_tiles", rows)]
+    if tc:
         _library.call("dl_attention_prefill_tc_bf16", q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0),
                       k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),
                       n_tiles, plan.seq_start.data_ptr(), plan.seq_new.data_ptr(), plan.cu_new.data_ptr(),

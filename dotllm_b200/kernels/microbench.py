@@ -168,7 +168,7 @@ def main(argv=None):
             if not hasattr(lib, "dl_attention_prefill_tc_timeline"):
                 raise SystemExit("the library was not built with DOTLLM_NVCC_EXTRA=-DPT_TIMELINE")
             pages = 256
-            buf = (ctypes.c_longlong * (10 * pages))()
+            buf = (ctypes.c_longlong * (12 * pages))()
             lib.dl_attention_prefill_tc_timeline.argtypes = [ctypes.c_void_p]
             if lib.dl_attention_prefill_tc_timeline(buf) != 0:
                 raise SystemExit("could not read the timeline")
@@ -179,7 +179,8 @@ def main(argv=None):
                 "page_period": (at(0, hi) - at(0, lo)) / (hi - lo),
                 "issue_scores": mean(0, 1), "wait_weights": mean(2, 3), "issue_product": mean(3, 4),
                 "softmax_wait_scores": mean(5, 6), "softmax_read_scores": mean(6, 7), "softmax_maximum": mean(7, 8),
-                "softmax_exponentials_and_store": mean(8, 9)}
+                "softmax_wait_weights_buffer": mean(8, 10), "softmax_exponentials_and_store": mean(10, 11),
+                "softmax_fence_and_announce": mean(11, 9)}
         result.update(tokens=T, flops=flops, ms=ms, best_ms=best, tflops=flops / ms / 1e9,
                       frac_of_bf16_peak=flops / ms / 1e9 / tflops)
     elif args.kernel == "gemm_skinny":

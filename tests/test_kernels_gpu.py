@@ -562,8 +562,21 @@ def test_attention_prefill_packed_unequal(nh, nkv, hd, window, tc, monkeypatch):
     by the tcgen05 kernel (head sizes 64 and 128) and by the mma.sync kernel (every size)."""
     from dotllm_b200.kernels import attention_fast
     monkeypatch.setattr(attention_fast, "PREFILL_TC", tc)
-    lengths = [1, 70, 333, 64, 500, 129]
-    news = [1, 70, 33, 1, 500, 65]
+    _check_prefill_packed(nh, nkv, hd, window, lengths=[1, 70, 333, 64, 500, 129], news=[1, 70, 33, 1, 500, 65])
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("window", [0, 40, 200])
+def test_attention_prefill_tc_tile_edges(hd, window):
+    """The tcgen05 kernel takes 256 rows a block as two tiles of 128 that share their pages: prompts
+    that end exactly at a tile's or a block's edge or one row past it, alone and behind earlier
+    context of odd length, and windows shorter and longer than a tile (with a short window the
+    second tile joins the walk pages after the first)."""
+    _check_prefill_packed(4, 2, hd, window, lengths=[128, 134, 256 + 64, 257 + 100, 385, 511 + 7],
+                          news=[128, 129, 256, 257, 385, 511])
+
+
+def _check_prefill_packed(nh, nkv, hd, window, lengths, news):
     k_pool, v_pool, table, dense = make_paged(len(lengths), lengths, nkv, hd, torch.bfloat16, seed=30)
     g = torch.Generator().manual_seed(31)
     token_seq, token_pos = [], []
