@@ -20,11 +20,22 @@
 // 0-7 are gate rows and rows 8-15 the matching up rows, and the epilogue writes silu(gate) * up
 // (native/kernels/swiglu.cu:7-41).
 //
+//
+// Two optional fusions take the add + RMSNorm between two products of a decode step into the products
+// themselves (the reference's fused_add_rmsnorm, native/kernels/fused_add_rmsnorm.cu:9-72, is a kernel
+// of its own).  A float32 product with `gain` set adds its result into the float32 residual stream it
+// is given as `out`, writes the sum times the norm's gain as bfloat16 (`scaled`) and the sum of squares
+// of every 16-column tile and row (`sumsq_out`).  The product that follows takes `scaled` as its x
+// and `sumsq_in`: a warp of its own adds the tiles' sums in tile order, and every output row is
+// multiplied by rsqrt(sum / n + eps) in the epilogue - x W^T of the normalised row, since the
+// normalisation is one factor per row.  All of it in float32 and in a fixed order.
+//
 // Every wait on an mbarrier is bounded (about a second of clock cycles); on expiry the kernel records
 // a code in `status` and returns after waiting (bounded) for copies in flight.
 #include "common.cuh"
 #include "tma.cuh"
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #ifndef GS_CONSUMERS
@@ -35,7 +46,7 @@
 #endif
 #define GS_BK 256                          // k per chunk
 #define GS_STAGE_ELEMS (16 * GS_BK)         // a stage is the dense box the copy engine writes: [16 rows][256 k]
-#define GS_THREADS (32 * (GS_CONSUMERS + 1))
+#define GS_THREADS (32 * (GS_CONSUMERS + 2))   // consumers, the producer warp, the row-statistics warp
 #define GS_WAIT_CYCLES (1ll << 31)
 #define GS_MAX_ROWS 16
 
@@ -85,29 +96,69 @@ template <> __device__ __forceinline__ void gs_store<__nv_bfloat16>(__nv_bfloat1
     *p = __float2bfloat16_rn(v);
 }
 
+// The optional fusions of a launch (all pointers null: a plain product).
+struct GsFuse {
+    const float* gain;          // set: out is the float32 residual stream, out += x W^T in place, and ...
+    __nv_bfloat16* scaled;      // ... scaled[m][n] = bf16(out[m][n] * gain[n]), rows scaled_stride apart,
+    int scaled_stride;
+    float* sumsq_out;           // ... sumsq_out[tile * 16 + m] = sum over the tile's 16 columns of out[m][n]^2
+    const float* sumsq_in;      // set: output row m is multiplied by rsqrt(sum_p sumsq_in[p * 16 + m] * inv_n + eps)
+    int n_parts;
+    float inv_n, eps;
+};
+
 // acc[j] = {(row g, tok 2t), (row g, tok 2t+1), (row g+8, tok 2t), (row g+8, tok 2t+1)} of 8-token group j
+// `row_scale`: null, or the factor of every output row (token).  `fuse.gain` (float32 plain products
+// only): add into `out` and leave the scaled copy and the tile's sums of squares for the next product.
 template <int NT, typename TOut, bool FUSE_SWIGLU>
-__device__ __forceinline__ void gs_epilogue(const float (&acc)[NT][4], TOut* out, int out_stride, int tile, int M,
-                                            int N, int g, int t) {
+__device__ __forceinline__ void gs_epilogue(const float (&acc_in)[NT][4], TOut* out, int out_stride, int tile, int M,
+                                            int N, int g, int t, const float* row_scale, const GsFuse& fuse,
+                                            const float (&stream_in)[NT][4], const float (&gain_in)[2]) {
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         const int tok0 = j * 8 + 2 * t;
+        float acc[4] = {acc_in[j][0], acc_in[j][1], acc_in[j][2], acc_in[j][3]};
+        if (row_scale != nullptr) {
+            const float s0 = row_scale[tok0], s1 = row_scale[tok0 + 1];
+            acc[0] *= s0, acc[1] *= s1, acc[2] *= s0, acc[3] *= s1;
+        }
         if (FUSE_SWIGLU) {
             const int col = tile * 8 + g;
             if (col < N) {
-                const float g0 = acc[j][0], g1 = acc[j][1];
-                if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + col, g0 * (1.0f / (1.0f + expf(-g0))) * acc[j][2]);
-                if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + col, g1 * (1.0f / (1.0f + expf(-g1))) * acc[j][3]);
+                const float g0 = acc[0], g1 = acc[1];
+                if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + col, g0 * (1.0f / (1.0f + expf(-g0))) * acc[2]);
+                if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + col, g1 * (1.0f / (1.0f + expf(-g1))) * acc[3]);
+            }
+        } else if (std::is_same<TOut, float>::value && fuse.gain != nullptr) {
+            float* stream = reinterpret_cast<float*>(out);
+            float ss[2] = {0.f, 0.f};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = tile * 16 + g + (e >> 1) * 8, tok = tok0 + (e & 1);
+                if (row < N && tok < M) {
+                    const float h = stream_in[j][e] + acc[e];
+                    stream[(size_t)tok * out_stride + row] = h;
+                    fuse.scaled[(size_t)tok * fuse.scaled_stride + row] = __float2bfloat16_rn(h * gain_in[e >> 1]);
+                    ss[e & 1] = fmaf(h, h, ss[e & 1]);
+                }
+            }
+            // the tile's 16 columns of a token lie in the 8 lanes that share t: add them in a fixed order
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 4);
+                ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 8);
+                ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 16);
+                if (g == 0 && tok0 + e < M) fuse.sumsq_out[(size_t)tile * 16 + tok0 + e] = ss[e];
             }
         } else {
             const int row_lo = tile * 16 + g, row_hi = row_lo + 8;
             if (row_lo < N) {
-                if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + row_lo, acc[j][0]);
-                if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + row_lo, acc[j][1]);
+                if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + row_lo, acc[0]);
+                if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + row_lo, acc[1]);
             }
             if (row_hi < N) {
-                if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + row_hi, acc[j][2]);
-                if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + row_hi, acc[j][3]);
+                if (tok0 < M) gs_store<TOut>(out + (size_t)tok0 * out_stride + row_hi, acc[2]);
+                if (tok0 + 1 < M) gs_store<TOut>(out + (size_t)(tok0 + 1) * out_stride + row_hi, acc[3]);
             }
         }
     }
@@ -117,7 +168,7 @@ __device__ __forceinline__ void gs_epilogue(const float (&acc)[NT][4], TOut* out
 // points of a launch into gs_timeline, which dl_gemm_skinny_timeline copies out
 // (`python -m dotllm_b200.kernels.microbench gemm_skinny --timeline` prints the spread over the grid).
 #ifdef GS_TIMELINE
-__device__ long long gs_timeline[6][2048];       // [event][block * (GS_CONSUMERS + 1) + warp]
+__device__ long long gs_timeline[6][2048];       // [event][block * (GS_CONSUMERS + 2) + warp]
 __device__ __forceinline__ long long gs_now() {
     long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -125,7 +176,7 @@ __device__ __forceinline__ long long gs_now() {
 }
 #define GS_STAMP(ev)                                                                                                     \
     do {                                                                                                                 \
-        const int slot__ = blockIdx.x * (GS_CONSUMERS + 1) + (threadIdx.x >> 5);                                          \
+        const int slot__ = blockIdx.x * (GS_CONSUMERS + 2) + (threadIdx.x >> 5);                                          \
         if ((threadIdx.x & 31) == 0 && slot__ < 2048) gs_timeline[ev][slot__] = gs_now();                                 \
     } while (0)
 extern "C" int dl_gemm_skinny_timeline(long long* out) {
@@ -142,6 +193,7 @@ struct GsWork {
     void* out;
     int out_stride;
     int M, N, K, up_offset, cpt, total_chunks, share;
+    GsFuse fuse;
 };
 
 // The rings of a block: a private ring of GS_SLOTS stages per consumer warp.
@@ -151,6 +203,8 @@ struct GsRings {
     uint64_t (*empty_bar)[GS_SLOTS];
     volatile int* gave_up;
     int* status;
+    uint64_t* scale_bar;                                    // completes when row_scale is written
+    const float* row_scale;                                 // [16] factors of the output rows (sumsq_in)
 };
 
 // Producer lane `lane` (< GS_CONSUMERS) feeds consumer warp `lane`: it walks that warp's share chunk
@@ -206,11 +260,36 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
     for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+    const float* row_scale = nullptr;                    // set once the statistics warp has written the factors
+    // The stream's values and the gains of the tile at hand, asked for when the tile begins so that the
+    // epilogue does not wait for them (only this tile's finishing warp ever writes them).
+    float stream_in[NT][4], gain_in[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) stream_in[j][e] = 0.f;
+    int stream_tile = -1;
     int seg_begin = begin;                               // first chunk of the current tile's segment
     for (int cur = begin; cur < end; ++cur, ++cnt) {
         const int slot = cnt % GS_SLOTS;
         const int tile = cur / cpt, kc = cur - tile * cpt;
         const int k0 = kc * GS_BK;
+        if (std::is_same<TOut, float>::value && !FUSE_SWIGLU && w.fuse.gain != nullptr && tile != stream_tile) {
+            stream_tile = tile;
+            const float* stream = reinterpret_cast<const float*>(w.out);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = tile * 16 + g + 8 * h;
+                gain_in[h] = row < N ? __ldg(w.fuse.gain + row) : 0.f;
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int tok = j * 8 + 2 * t + e;
+                        stream_in[j][2 * h + e] = (row < N && tok < M) ? __ldcg(stream + (size_t)tok * w.out_stride + row) : 0.f;
+                    }
+            }
+        }
         // activations of this chunk, asked for before waiting on the weights
         uint4 xf[GS_BK / 32][NT];
 #pragma unroll
@@ -258,8 +337,18 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
         if (kc == cpt - 1 || cur == end - 1) {
             // ---- the segment [seg_begin, cur] of this tile is done
             const bool whole = (seg_begin == tile * cpt) && (kc == cpt - 1);
+            if (w.fuse.sumsq_in != nullptr && row_scale == nullptr && !dead) {
+                // the factors of the rows: written by the statistics warp long before the first tile ends
+                if (!gs_mbar_wait(r.scale_bar, 0, r.gave_up)) {
+                    if (!*r.gave_up) atomicExch(r.status, 5);
+                    *r.gave_up = 1;
+                    dead = true;
+                } else {
+                    row_scale = r.row_scale;
+                }
+            }
             if (whole) {
-                gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, w.out_stride, tile, M, N, g, t);
+                gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, w.out_stride, tile, M, N, g, t, row_scale, w.fuse, stream_in, gain_in);
             } else {
 #ifndef GS_EXP_NO_FIXUP
                 // a warp's first tile may be shared with the share before, its last with the share after
@@ -295,7 +384,7 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
 #pragma unroll
                             for (int e = 0; e < 4; ++e) acc[j][e] += __ldcg(theirs + (j * 4 + e) * 32 + lane);
                     }
-                    gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, w.out_stride, tile, M, N, g, t);
+                    gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, w.out_stride, tile, M, N, g, t, row_scale, w.fuse, stream_in, gain_in);
                 }
 #endif
             }
@@ -312,9 +401,12 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
     extern __shared__ __align__(128) unsigned char gs_smem_raw[];                                        \
     __shared__ uint64_t full_bar[GS_CONSUMERS][GS_SLOTS], empty_bar[GS_CONSUMERS][GS_SLOTS];             \
     __shared__ volatile int gave_up;                                                                     \
+    __shared__ uint64_t scale_bar;                                                                       \
+    __shared__ float row_scale_smem[GS_MAX_ROWS];                                                        \
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;                                          \
     if (threadIdx.x == 0) {                                                                              \
         gave_up = 0;                                                                                     \
+        gs_mbar_init(&scale_bar, 1);                                                                     \
         for (int c = 0; c < GS_CONSUMERS; ++c)                                                           \
             for (int s = 0; s < GS_SLOTS; ++s) {                                                         \
                 gs_mbar_init(&full_bar[c][s], 1);                                                        \
@@ -324,7 +416,8 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
     }                                                                                                    \
     __syncthreads();                                                                                     \
     dl_launch_dependents();                                                                              \
-    const GsRings rings{reinterpret_cast<__nv_bfloat16*>(gs_smem_raw), full_bar, empty_bar, &gave_up, status}
+    const GsRings rings{reinterpret_cast<__nv_bfloat16*>(gs_smem_raw), full_bar, empty_bar, &gave_up, status, &scale_bar,  \
+                        row_scale_smem}
 
 template <int NT, typename TOut, bool FUSE_SWIGLU>
 __global__ void __launch_bounds__(GS_THREADS, 1)
@@ -342,6 +435,48 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap, const GsWork work, 
         if (lane < GS_CONSUMERS) {
             int cnt = 0;
             if (!gs_produce<FUSE_SWIGLU>(&tmap, work, rings, lane, cnt)) gs_drain(rings, lane, cnt);
+        }
+    } else if (warp == GS_CONSUMERS + 1) {
+        // ------------------------------------------------------------ row-statistics warp
+        if (work.fuse.sumsq_in != nullptr) {
+            dl_grid_dependency_wait();   // the sums come from the kernel before this one
+            // A warp-wide float4 load covers 8 parts x 16 rows: lane -> (rows 4q .. 4q+3, part l/4 of
+            // every 8).  All loads of a batch are in flight together; a lane adds its parts in part
+            // order, then the 8 lanes of a row group are added in a fixed order: the same bits on
+            // every launch.
+            const int q = lane & 3, sub = lane >> 2;
+            const float4* in = reinterpret_cast<const float4*>(work.fuse.sumsq_in) + q;
+            float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p0 = 0; p0 < work.fuse.n_parts; p0 += 8 * 16) {
+                float4 v[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int p = p0 + 8 * i + sub;
+                    v[i] = p < work.fuse.n_parts ? __ldcg(in + (size_t)p * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc4.x += v[i].x, acc4.y += v[i].y, acc4.z += v[i].z, acc4.w += v[i].w;
+            }
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                // both partners add (lower lane's value) + (higher lane's value)
+                const float4 other = make_float4(__shfl_xor_sync(0xffffffffu, acc4.x, o), __shfl_xor_sync(0xffffffffu, acc4.y, o),
+                                                 __shfl_xor_sync(0xffffffffu, acc4.z, o), __shfl_xor_sync(0xffffffffu, acc4.w, o));
+                const bool low = (lane & o) == 0;
+                acc4.x = low ? acc4.x + other.x : other.x + acc4.x;
+                acc4.y = low ? acc4.y + other.y : other.y + acc4.y;
+                acc4.z = low ? acc4.z + other.z : other.z + acc4.z;
+                acc4.w = low ? acc4.w + other.w : other.w + acc4.w;
+            }
+            if (lane < 4) {
+                row_scale_smem[4 * lane + 0] = rsqrtf(acc4.x * work.fuse.inv_n + work.fuse.eps);
+                row_scale_smem[4 * lane + 1] = rsqrtf(acc4.y * work.fuse.inv_n + work.fuse.eps);
+                row_scale_smem[4 * lane + 2] = rsqrtf(acc4.z * work.fuse.inv_n + work.fuse.eps);
+                row_scale_smem[4 * lane + 3] = rsqrtf(acc4.w * work.fuse.inv_n + work.fuse.eps);
+            }
+            __threadfence_block();
+            __syncwarp();
+            if (lane == 0) gs_mbar_arrive(&scale_bar);
         }
     } else {
         // ------------------------------------------------------------ consumer warp
@@ -420,7 +555,7 @@ static int gs_weight_map(CUtensorMap* out, const void* w, int N, int K, bool gat
 template <int NT, typename TOut, bool FUSE>
 static int gs_launch(const GsPlan& p, cudaStream_t s, const __nv_bfloat16* x, int x_stride, const __nv_bfloat16* w,
                      void* out, int out_stride, int M, int N, int K, int up_offset, int early_weights, float* partials,
-                     int* counters, int* status) {
+                     int* counters, int* status, const GsFuse& fuse) {
     const size_t smem = (size_t)GS_CONSUMERS * GS_SLOTS * GS_STAGE_ELEMS * 2;
     static bool configured = false;
     if (!configured) {
@@ -431,7 +566,7 @@ static int gs_launch(const GsPlan& p, cudaStream_t s, const __nv_bfloat16* x, in
     CUtensorMap tmap;
     const int rc = gs_weight_map(&tmap, w, N, K, FUSE);
     if (rc != DL_OK) return rc;
-    const GsWork work{x, x_stride, out, out_stride, M, N, K, up_offset, p.cpt, p.total, p.share};
+    const GsWork work{x, x_stride, out, out_stride, M, N, K, up_offset, p.cpt, p.total, p.share, fuse};
     cudaError_t le = dl_launch_dependent(gemm_skinny_kernel<NT, TOut, FUSE>, dim3(p.blocks), dim3(GS_THREADS), smem, s, tmap, work,
                                          early_weights, partials, counters, status);
     if (le != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny: %s", cudaGetErrorString(le));
@@ -445,9 +580,9 @@ static int gs_launch(const GsPlan& p, cudaStream_t s, const __nv_bfloat16* x, in
 // writes w, so the kernel may start reading w before the kernel launched before it has finished.
 // partials / counters: scratch of the sizes dl_gemm_skinny_scratch gives; status: int32, set
 // non-zero if a wait expired.
-extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype,
-                                   int out_stride, int M, int N, int K, int flags, float* partials,
-                                   int partial_floats, int* counters, int n_counters, int* status, void* stream) {
+static int gs_run(const void* x, int x_stride, const void* w, void* out, int out_dtype, int out_stride, int M, int N, int K,
+                  int flags, float* partials, int partial_floats, int* counters, int n_counters, int* status, void* stream,
+                  const GsFuse& fuse) {
     const int fuse_swiglu = flags & 1, early = (flags >> 1) & 1;
     DL_REQUIRE((flags & ~3) == 0, "gemm_skinny: unknown flags %d", flags);
     DL_REQUIRE(M >= 1 && M <= GS_MAX_ROWS, "gemm_skinny: takes 1 to %d rows, got %d", GS_MAX_ROWS, M);
@@ -470,15 +605,47 @@ extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, v
 #define GS_CASE(NTV)                                                                                                   \
     if (nt == NTV) {                                                                                                   \
         if (fuse_swiglu) {                                                                                             \
-            if (out_dtype == DL_F32) return gs_launch<NTV, float, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, early, partials, counters, status); \
-            return gs_launch<NTV, __nv_bfloat16, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, early, partials, counters, status);                \
+            if (out_dtype == DL_F32) return gs_launch<NTV, float, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, early, partials, counters, status, fuse); \
+            return gs_launch<NTV, __nv_bfloat16, true>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, N, early, partials, counters, status, fuse);                \
         }                                                                                                              \
-        if (out_dtype == DL_F32) return gs_launch<NTV, float, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, early, partials, counters, status);    \
-        return gs_launch<NTV, __nv_bfloat16, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, early, partials, counters, status);                   \
+        if (out_dtype == DL_F32) return gs_launch<NTV, float, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, early, partials, counters, status, fuse);    \
+        return gs_launch<NTV, __nv_bfloat16, false>(p, s, xb, x_stride, wb, out, out_stride, M, N, K, 0, early, partials, counters, status, fuse);                   \
     }
     GS_CASE(1) GS_CASE(2)
 #undef GS_CASE
     return dl_fail(DL_ERR_UNSUPPORTED, "gemm_skinny: %d rows", M);
+}
+
+extern "C" int dl_gemm_skinny_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype,
+                                   int out_stride, int M, int N, int K, int flags, float* partials,
+                                   int partial_floats, int* counters, int n_counters, int* status, void* stream) {
+    return gs_run(x, x_stride, w, out, out_dtype, out_stride, M, N, K, flags, partials, partial_floats, counters, n_counters,
+                  status, stream, GsFuse{});
+}
+
+// The same with the fusions of an add + RMSNorm between two products (either, both or neither):
+// gain set (float32 [N]; out must be float32 and the product plain): out is the float32 residual
+//   stream and is added to in place; scaled bf16 [M, N] (rows scaled_stride apart) receives
+//   out * gain, sumsq_out float32 [ceil(N / 16) * 16] the sum of squares per 16-column tile and row.
+// sumsq_in set (float32 [n_parts * 16], as a product before this one left it): every output row m
+//   is multiplied by rsqrt(sum_p sumsq_in[p * 16 + m] / n + eps), n = 1 / inv_n the width of x's norm.
+extern "C" int dl_gemm_skinny_fused_bf16(const void* x, int x_stride, const void* w, void* out, int out_dtype,
+                                         int out_stride, int M, int N, int K, int flags, const float* gain, void* scaled,
+                                         int scaled_stride, float* sumsq_out, const float* sumsq_in, int n_parts, float inv_n,
+                                         float eps, float* partials, int partial_floats, int* counters, int n_counters,
+                                         int* status, void* stream) {
+    GsFuse fuse{};
+    if (gain != nullptr) {
+        DL_REQUIRE(out_dtype == DL_F32 && (flags & 1) == 0, "gemm_skinny: adding into the stream needs a plain float32 product");
+        DL_REQUIRE(scaled != nullptr && sumsq_out != nullptr && scaled_stride >= N, "gemm_skinny: the scaled copy and the sums need a place");
+        fuse.gain = gain, fuse.scaled = (__nv_bfloat16*)scaled, fuse.scaled_stride = scaled_stride, fuse.sumsq_out = sumsq_out;
+    }
+    if (sumsq_in != nullptr) {
+        DL_REQUIRE(n_parts > 0 && inv_n > 0.f && eps >= 0.f, "gemm_skinny: row factors need parts, a width and an eps");
+        fuse.sumsq_in = sumsq_in, fuse.n_parts = n_parts, fuse.inv_n = inv_n, fuse.eps = eps;
+    }
+    return gs_run(x, x_stride, w, out, out_dtype, out_stride, M, N, K, flags, partials, partial_floats, counters, n_counters,
+                  status, stream, fuse);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -12,9 +12,11 @@ import torch
 
 from . import library as _library
 
-_P, _I = _library._P, _library._I
+_P, _I, _F = _library._P, _library._I, _library._F
 _library.register_signatures({
     "dl_gemm_skinny_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P],
+    "dl_gemm_skinny_fused_bf16": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _I, _F, _F,
+                                  _P, _I, _P, _I, _P, _P],
     "dl_gemm_skinny_scratch": [_I, _I, _I, _I, _I, _P, _P],
 })
 
@@ -43,17 +45,39 @@ def takes(x, w, fuse_swiglu=False, max_rows=None):
             and w.data_ptr() % 16 == 0 and tiles <= _MAX_TILES)
 
 
-def run(x, w, out_dtype, fuse_swiglu=False, resident=False):
+def run(x, w, out_dtype, fuse_swiglu=False, resident=False, row_sums=None, into=None):
+    """``row_sums`` = (sums float32 [parts * 16], parts, width, eps): x is a stream times a norm's gain,
+    and every output row is multiplied by rsqrt(sum of the row's parts / width + eps).
+    ``into`` = (stream float32 [M, N], gain float32 [N]): the product is added into the stream in place;
+    returns (stream * gain as bfloat16 [M, N], sums of squares float32 [ceil(N / 16) * 16])."""
     M, K = x.shape
     n_out = w.shape[0] // 2 if fuse_swiglu else w.shape[0]
     counters, partials, sms = _device_state(x.device)
-    out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-    _library.call("dl_gemm_skinny_bf16", x.data_ptr(), x.stride(0) if M > 1 else max(K, x.stride(0)),
-                  w.data_ptr(), out.data_ptr(), 0 if out_dtype == torch.float32 else 1, n_out, M, n_out, K,
-                  (1 if fuse_swiglu else 0) | (2 if resident else 0), partials.data_ptr(), partials.numel(), counters.data_ptr(),
-                  counters.numel(), _library.status_word(x.device).data_ptr(),
-                  torch.cuda.current_stream().cuda_stream)
-    return out
+    x_stride = x.stride(0) if M > 1 else max(K, x.stride(0))
+    flags = (1 if fuse_swiglu else 0) | (2 if resident else 0)
+    tail = (partials.data_ptr(), partials.numel(), counters.data_ptr(), counters.numel(),
+            _library.status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    if row_sums is None and into is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+        _library.call("dl_gemm_skinny_bf16", x.data_ptr(), x_stride, w.data_ptr(), out.data_ptr(),
+                      0 if out_dtype == torch.float32 else 1, n_out, M, n_out, K, flags, *tail)
+        return out
+    sums_in, parts, width, eps = row_sums if row_sums is not None else (None, 0, 1, 0.0)
+    if into is not None:
+        stream, gain = into
+        scaled = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+        sums_out = torch.empty(((n_out + 15) // 16) * 16, dtype=torch.float32, device=x.device)
+        out, out_stride, result = stream, stream.stride(0), (scaled, sums_out)
+    else:
+        gain = scaled = sums_out = None
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+        out_stride, result = n_out, out
+    _library.call("dl_gemm_skinny_fused_bf16", x.data_ptr(), x_stride, w.data_ptr(), out.data_ptr(),
+                  0 if out.dtype == torch.float32 else 1, out_stride, M, n_out, K, flags,
+                  gain.data_ptr() if gain is not None else None, scaled.data_ptr() if scaled is not None else None, n_out,
+                  sums_out.data_ptr() if sums_out is not None else None,
+                  sums_in.data_ptr() if sums_in is not None else None, parts, 1.0 / width, float(eps), *tail)
+    return result
 
 
 def scratch_need(M, N, K, fuse_swiglu=False, sms=148):

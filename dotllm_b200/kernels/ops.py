@@ -69,12 +69,57 @@ def gather_rows(table, ids, out=None):
     return out
 
 
+# ------------------------------------------------- products not yet launched
+class PendingProduct:
+    """x W^T of a decode step that ``linear(..., lazy=True)`` has not launched yet.  Given to
+    ``add_rmsnorm`` as the delta, the product itself adds its result into the stream; anyone else
+    calls ``tensor()`` (or ``resolve``) and gets the plain float32 product."""
+
+    def __init__(self, x, w, resident):
+        self.x, self.w, self.resident = x, w, resident
+        self.shape = (x.shape[0], w.shape[0])
+
+    def tensor(self):
+        return linear(self.x, self.w, out_dtype=torch.float32, resident=self.resident)
+
+
+class ScaledRows:
+    """A normalised stream still lacking its factor per row: ``data`` = stream * gain (bfloat16) and the
+    sums of squares per 16-column part, left by the product that added into the stream.  ``linear``
+    and ``gated_linear`` take it as x and apply rsqrt(mean + eps) to their output rows - the product
+    of the normalised rows, since the factor is one number per row.  ``tensor()`` gives the
+    normalised rows themselves (valid until the stream is added to again)."""
+
+    def __init__(self, data, sums, width, eps, stream, gain):
+        self.data, self.sums, self.width, self.eps = data, sums, width, eps
+        self.stream, self.gain = stream, gain
+        self.shape, self.dtype = data.shape, data.dtype
+
+    def row_sums(self):
+        return self.sums, self.sums.numel() // 16, self.width, self.eps
+
+    def tensor(self):
+        return add_rmsnorm(self.stream, None, self.gain, self.eps, self.data.dtype)
+
+
+def resolve(value):
+    """The tensor behind a PendingProduct or ScaledRows; tensors and None pass through."""
+    return value.tensor() if isinstance(value, (PendingProduct, ScaledRows)) else value
+
+
 # ----------------------------------------------------------------------- norm
-def add_rmsnorm(residual, delta, gain, eps, out_dtype):
+def add_rmsnorm(residual, delta, gain, eps, out_dtype, lazy=False):
     """residual += delta (when delta is given), then rmsnorm(residual) * gain in ``out_dtype``.
 
-    residual: float32 [T, H] contiguous, updated in place.  delta: [T, H] float32/bfloat16 or None.
-    gain: float32 [H]."""
+    residual: float32 [T, H] contiguous, updated in place.  delta: [T, H] float32/bfloat16, a
+    PendingProduct, or None.  gain: float32 [H].  ``lazy``: the caller will hand the result straight
+    to ``linear`` / ``gated_linear``, so it may be a ScaledRows: a pending product then does the
+    addition itself and the next product the normalisation, with no kernel in between."""
+    if isinstance(delta, PendingProduct):
+        fused = _add_product_scaled(residual, delta, gain, eps, out_dtype) if lazy else None
+        if fused is not None:
+            return fused
+        delta = delta.tensor()
     _need_cuda(residual, delta, gain)
     if residual.dtype != torch.float32 or residual.dim() != 2 or not residual.is_contiguous():
         raise KernelError("rmsnorm: the residual stream must be contiguous float32 [T, H]")
@@ -88,6 +133,22 @@ def add_rmsnorm(residual, delta, gain, eps, out_dtype):
                   _code(delta.dtype) if delta is not None else 0, _ptr(gain), _ptr(out),
                   _code(out_dtype), rows, width, float(eps), _stream())
     return out
+
+
+def _add_product_scaled(residual, product, gain, eps, out_dtype):
+    from . import gemm_skinny
+    x = product.x
+    rows = x.row_sums() if isinstance(x, ScaledRows) else None
+    xt = x.data if rows is not None else x
+    if out_dtype != torch.bfloat16 or residual.dtype != torch.float32 or residual.dim() != 2 \
+            or residual.stride(1) != 1 or tuple(residual.shape) != product.shape \
+            or gain.dtype != torch.float32 or gain.shape != (residual.shape[1],) or not gain.is_contiguous() \
+            or not gemm_skinny.takes(xt, product.w):
+        return None
+    _need_cuda(residual, xt, product.w, gain)
+    scaled, sums = gemm_skinny.run(xt, product.w, torch.float32, resident=product.resident, row_sums=rows,
+                                   into=(residual, gain))
+    return ScaledRows(scaled, sums, residual.shape[1], eps, residual, gain)
 
 
 # --------------------------------------------------- position + cache write
@@ -211,14 +272,23 @@ def swiglu(gate_up):
 
 
 # --------------------------------------------------------------------- linear
-def linear(x, w, out_dtype=None, resident=False):
+def linear(x, w, out_dtype=None, resident=False, lazy=False):
     """y = x W^T for W [N, K].  ``resident``: the caller vouches that nothing still pending on the
     stream writes W (a model's weights), which lets the decode kernel start streaming W while
-    the kernel before it finishes.
+    the kernel before it finishes.  ``lazy`` (float32 results of a few bfloat16 rows): return a
+    PendingProduct, for a caller whose result goes to ``add_rmsnorm`` as the delta.  x may be a
+    ScaledRows.
 
     float32: the library's own FFMA kernel (true 32-bit, the same bits for any number of rows).
     bfloat16: cuBLAS through torch with float32 accumulation, the library product that the
     reference also uses for its projections (src/DotLLM.Cuda/CudaGemm.cs:29-40)."""
+    given, rows = x, None
+    if isinstance(x, ScaledRows):
+        from . import gemm_skinny
+        if gemm_skinny.takes(x.data, w):
+            rows, x = x.row_sums(), x.data
+        else:
+            given = x = x.tensor()
     _need_cuda(x, w)
     if w.dim() != 2 or not w.is_contiguous() or x.dim() != 2 or x.shape[1] != w.shape[1]:
         raise KernelError(f"linear: x {tuple(x.shape)} does not match W {tuple(w.shape)}")
@@ -227,6 +297,12 @@ def linear(x, w, out_dtype=None, resident=False):
     out_dtype = out_dtype or x.dtype
     M, K = x.shape
     N = w.shape[0]
+    if rows is not None or (lazy and out_dtype == torch.float32 and M > 0):
+        from . import gemm_skinny
+        if lazy and out_dtype == torch.float32 and gemm_skinny.takes(x, w):
+            return PendingProduct(given, w, resident)
+        if rows is not None:
+            return gemm_skinny.run(x, w, out_dtype, resident=resident, row_sums=rows)
     if x.dtype == torch.float32:
         if out_dtype != torch.float32:
             raise KernelError("linear: the float32 product writes float32")
@@ -251,6 +327,12 @@ def gated_linear(x, w_gate_up, resident=False):
     In bfloat16 one kernel does the product and the gating in float32: the weight-streaming
     kernel for a few rows, the tcgen05 kernel for many.  In float32 the product is followed by
     the gating kernel."""
+    if isinstance(x, ScaledRows):
+        from . import gemm_skinny
+        if w_gate_up.dim() == 2 and x.shape[1] == w_gate_up.shape[1] and gemm_skinny.takes(x.data, w_gate_up, True):
+            _need_cuda(x.data, w_gate_up)
+            return gemm_skinny.run(x.data, w_gate_up, x.dtype, fuse_swiglu=True, resident=resident, row_sums=x.row_sums())
+        x = x.tensor()
     _need_cuda(x, w_gate_up)
     if w_gate_up.dim() != 2 or w_gate_up.shape[0] % 2 or not w_gate_up.is_contiguous() or x.dim() != 2 \
             or x.shape[1] != w_gate_up.shape[1]:

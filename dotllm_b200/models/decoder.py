@@ -13,7 +13,7 @@ import torch
 from ..cache.model_cache import ModelCache
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..parts.base import Runtime, make_arrangement, make_part
+from ..parts.base import Runtime, make_arrangement, make_part, normalised_for
 
 
 class DecoderModel:
@@ -98,7 +98,5 @@ class DecoderModel:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
         if not step.want_all:
             residual = ops.gather_rows(residual, step.want_rows)
-            pending = ops.gather_rows(pending, step.want_rows) if pending is not None else None
-        n = self.final_norm.add_forward(residual, pending) if pending is not None \
-            else self.final_norm.forward(residual)
-        return self.head.forward(n)
+            pending = ops.gather_rows(ops.resolve(pending), step.want_rows) if pending is not None else None
+        return self.head.forward(normalised_for(self.head, self.final_norm, residual, pending))

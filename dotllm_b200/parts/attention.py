@@ -61,6 +61,8 @@ class AttentionMixer(Mixer):
     def cache_need(self):
         return CacheNeed("kv", n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, window=self.window)
 
+    takes_scaled_rows = True                    # x goes straight into the Q/K/V product
+
     def forward(self, x, step, cache_view):
         qd, kvd = self.q_dim, self.kv_dim
         if cache_view.writes:
@@ -80,7 +82,7 @@ class AttentionMixer(Mixer):
                                      cache_view.block_table, cache_view.k, cache_view.v,
                                      self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                                      int(self.window or 0), plan=step.attention_plan)
-        return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True)
+        return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
 
 
 register_mixer("attention", AttentionMixer)

@@ -95,6 +95,10 @@ class Part:
 
 
 class Norm(Part):
+    """``fuses_products``: ``add_forward`` also takes ``lazy=True`` and a delta that is a product not yet
+    launched (``ops.PendingProduct``), and may then return ``ops.ScaledRows`` instead of a tensor."""
+    fuses_products = False
+
     def forward(self, x):
         """Normalised copy of the float32 stream ``x`` in the run dtype."""
         raise NotImplementedError
@@ -102,6 +106,20 @@ class Norm(Part):
     def add_forward(self, residual, delta):
         """residual += delta in place (float32), then the normalised result in the run dtype."""
         raise NotImplementedError
+
+
+def normalised_for(consumer, norm, residual, pending):
+    """The stream, with the branch output ``pending`` (or None) added, normalised by ``norm`` for the
+    part ``consumer``.  A part may return its last product unlaunched (``ops.linear(..., lazy=True)``);
+    a norm that ``fuses_products`` then lets that product do the addition, and a consumer that
+    ``takes_scaled_rows`` (it hands its input straight to ``ops.linear`` / ``ops.gated_linear``) lets its
+    first product do the normalisation.  Everyone else gets and gives plain tensors."""
+    from ..kernels import ops
+    if pending is None:
+        return norm.forward(residual)
+    if norm.fuses_products:
+        return norm.add_forward(residual, pending, lazy=bool(getattr(consumer, "takes_scaled_rows", False)))
+    return norm.add_forward(residual, ops.resolve(pending))
 
 
 class PositionEncoding(Part):
@@ -126,7 +144,10 @@ class Mixer(Part):
         return None
 
     def forward(self, x, step, cache_view):
-        """x [T, H] in the run dtype -> the branch output [T, H] (run dtype or float32).
+        """x [T, H] in the run dtype -> the branch output [T, H] (run dtype or float32; it may be a
+        last product not yet launched, ``ops.linear(..., lazy=True)``).  A mixer that sets
+        ``takes_scaled_rows`` hands x straight to ``ops.linear`` / ``ops.gated_linear`` and may be given
+        ``ops.ScaledRows`` instead of a tensor.
 
         ``step`` is the engine's StepContext (token -> sequence map, positions, lengths);
         ``cache_view`` gives this execution's storage (``LayerCacheView``) or None."""
@@ -135,7 +156,8 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, x):
-        """x [T, H] in the run dtype -> the branch output [T, H]."""
+        """x [T, H] in the run dtype -> the branch output [T, H]; ``takes_scaled_rows`` and unlaunched
+        last products as for a mixer."""
         raise NotImplementedError
 
 

@@ -8,15 +8,14 @@ to be added ("pending"), and whoever normalises next adds it.
 """
 from __future__ import annotations
 
-from .base import Arrangement, register_arrangement
+from .base import Arrangement, normalised_for, register_arrangement
 
 
 class PreNormBlock(Arrangement):
     def forward(self, residual, pending, step, cache_view):
-        n = self.mixer_norm.add_forward(residual, pending) if pending is not None \
-            else self.mixer_norm.forward(residual)
+        n = normalised_for(self.mixer, self.mixer_norm, residual, pending)
         a = self.mixer.forward(n, step, cache_view)
-        n = self.feed_forward_norm.add_forward(residual, a)
+        n = normalised_for(self.feed_forward, self.feed_forward_norm, residual, a)
         return residual, self.feed_forward.forward(n)
 
 

@@ -57,6 +57,8 @@ class LinearHead(Part):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
+    takes_scaled_rows = True                    # x goes straight into the product
+
     def forward(self, x):
         """[R, H] in the run dtype -> float32 logits [R, vocab]."""
         return ops.linear(x, self.weight, out_dtype=torch.float32, resident=True)

@@ -38,9 +38,11 @@ class GatedFeedForward(FeedForward):
     def weight_bytes(self):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
+    takes_scaled_rows = True                    # x goes straight into the gate/up product
+
     def forward(self, x):
         return ops.linear(ops.gated_linear(x, self.w_gate_up, resident=True), self.w_down, out_dtype=BRANCH_DTYPE,
-                          resident=True)
+                          resident=True, lazy=True)
 
 
 register_feed_forward("gated_mlp", GatedFeedForward)

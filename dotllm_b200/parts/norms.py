@@ -29,11 +29,13 @@ class RmsNorm(Norm):
     def weight_bytes(self):
         return self.gain.numel() * self.gain.element_size()
 
+    fuses_products = True
+
     def forward(self, x):
         return ops.add_rmsnorm(x, None, self.gain, self.eps, self.runtime.dtype)
 
-    def add_forward(self, residual, delta):
-        return ops.add_rmsnorm(residual, delta, self.gain, self.eps, self.runtime.dtype)
+    def add_forward(self, residual, delta, lazy=False):
+        return ops.add_rmsnorm(residual, delta, self.gain, self.eps, self.runtime.dtype, lazy=lazy)
 
 
 register_norm("rmsnorm", RmsNorm)

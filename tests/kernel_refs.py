@@ -23,7 +23,7 @@ def gather_rows(table, ids, out=None):
     return res
 
 
-def add_rmsnorm(residual, delta, gain, eps, out_dtype):
+def add_rmsnorm(residual, delta, gain, eps, out_dtype, lazy=False):
     if delta is not None:
         residual += delta.to(torch.float32)
     return plain_llama.rms_norm(residual, gain, eps).to(out_dtype)
@@ -88,7 +88,7 @@ def swiglu(gate_up):
     return plain_llama.swiglu(g, u).to(gate_up.dtype)
 
 
-def linear(x, w, out_dtype=None, resident=False):
+def linear(x, w, out_dtype=None, resident=False, lazy=False):
     y = x.to(torch.float32) @ w.to(torch.float32).T
     return y.to(out_dtype or x.dtype)
 

@@ -376,6 +376,65 @@ def test_gemm_skinny_repeats_with_full_rings():
         assert torch.equal(gemm_skinny.run(x, w, torch.float32), first)
 
 
+@pytest.mark.parametrize("M,H,K,N2", [(8, 4096, 512, 1024), (1, 1000, 384, 272), (13, 1000, 384, 272), (16, 72, 64, 40)])
+def test_products_that_add_and_normalise(M, H, K, N2):
+    """A decode step's add + RMSNorm done by the two products around it: the first adds its result
+    into the float32 stream and leaves stream * gain with sums of squares per 16 columns, the second
+    multiplies its output rows by rsqrt(mean + eps).  The stream must come out with the bits of the
+    separate kernels; the second product is compared with the product of the normalised rows, for a
+    plain and a gated product, at widths that are no multiple of 16."""
+    o = ops()
+    from dotllm_b200.kernels import library
+    g = torch.Generator().manual_seed(60)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w1 = (torch.randn(H, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    w2 = (torch.randn(N2, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    wg = (torch.randn(2 * N2, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    gain = (1 + 0.3 * torch.randn(H, generator=g)).to(DEV)
+    stream0 = (torch.randn(M, H, generator=g) * 2).to(DEV)
+    stream0[0] *= 30                                       # rows of very different scale: a factor taken from the wrong row shows
+    eps = 1e-5
+    # the separate kernels
+    plain_stream = stream0.clone()
+    normed = o.add_rmsnorm(plain_stream, o.linear(a, w1, out_dtype=torch.float32), gain, eps, torch.bfloat16)
+    # the two products
+    stream = stream0.clone()
+    pending = o.linear(a, w1, out_dtype=torch.float32, lazy=True)
+    assert isinstance(pending, o.PendingProduct)
+    rows = o.add_rmsnorm(stream, pending, gain, eps, torch.bfloat16, lazy=True)
+    assert isinstance(rows, o.ScaledRows)
+    assert torch.equal(stream, plain_stream)
+    y = o.linear(rows, w2, out_dtype=torch.float32)
+    yg = o.gated_linear(rows, wg)
+    zero = torch.zeros(H, H, dtype=torch.bfloat16, device=DEV)
+    chained = o.add_rmsnorm(stream, o.linear(rows, zero, out_dtype=torch.float32, lazy=True), gain, eps, torch.bfloat16,
+                            lazy=True)                    # scaled rows in, stream out: both fusions in one launch
+    assert isinstance(chained, o.ScaledRows) and torch.equal(stream, plain_stream)     # a zero matrix adds nothing
+    assert torch.equal(chained.data, rows.data) and torch.equal(chained.sums[:M], rows.sums[:M])
+    library.check_status()
+    # what the rows stand for
+    h = plain_stream.double().cpu()
+    n = h * torch.rsqrt((h * h).mean(dim=1, keepdim=True) + eps) * gain.double().cpu()
+    close(rows.tensor(), n.float(), 0.0, 2 ** -8)
+    assert torch.equal(rows.tensor(), normed)
+    # Either way each of a row's H numbers is rounded to bfloat16 once (relative 2^-9) before the sum of
+    # products, so a result is within 2^-9 sum |n_k w_k| of the exact one (plus float32 summation).
+    w2d, wgd = w2.double().cpu(), wg.double().cpu()
+    ref, slack = n @ w2d.T, 2 ** -9 * (n.abs() @ w2d.abs().T) * 1.05 + 1e-5
+    assert bool(((y.double().cpu() - ref).abs() <= slack).all())
+    gu, gu_slack = n @ wgd.T, 2 ** -9 * (n.abs() @ wgd.abs().T) * 1.05 + 1e-5
+    gate, up, e_gate, e_up = gu[:, :N2], gu[:, N2:], gu_slack[:, :N2], gu_slack[:, N2:]
+    want = gate * torch.sigmoid(gate) * up
+    # |d silu| <= 1.1; the output is rounded to bfloat16 once more
+    slack = 1.1 * e_gate * (up.abs() + e_up) + (gate * torch.sigmoid(gate)).abs() * e_up + 2 ** -8 * want.abs() + 1e-5
+    assert bool(((yg.double().cpu() - want).abs() <= slack).all())
+    # the same bits whatever else is in the batch: row 0 alone
+    if M > 1:
+        s1 = stream0[:1].clone()
+        r1 = o.add_rmsnorm(s1, o.linear(a[:1], w1, out_dtype=torch.float32, lazy=True), gain, eps, torch.bfloat16, lazy=True)
+        assert torch.equal(s1, stream[:1]) and torch.equal(o.linear(r1, w2, out_dtype=torch.float32), y[:1])
+
+
 @pytest.mark.parametrize("M,N,K", [(17, 64, 64), (128, 256, 64), (129, 257, 72), (300, 1000, 320), (2048, 384, 192),
                                    (515, 4096, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])

@@ -9,6 +9,7 @@ import torch
 
 import plain_llama
 import tiny_models
+from dotllm_b200.kernels import ops
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda", 0)
@@ -71,8 +72,52 @@ def test_feed_forward_part(dtype):
     for rows in (3, 40):                                 # few rows: fused kernel; many: product + gating
         x = torch.randn(rows, 64, generator=torch.Generator().manual_seed(rows)).to(dtype)
         want = plain_llama.feed_forward_part(x.float(), weights, "p.")
-        got = ffn.forward(x.to(DEV)).float().cpu()
+        got = ops.resolve(ffn.forward(x.to(DEV))).float().cpu()     # few bfloat16 rows: the last product comes unlaunched
         assert torch.allclose(got, want, atol=1e-6 if dtype == torch.float32 else 2e-3)
+
+
+def test_unlaunched_products_and_parts_that_do_not_fuse():
+    """A part may return its last product unlaunched so that the next norm's addition and the next
+    part's normalisation happen inside products.  A consumer that does not declare
+    ``takes_scaled_rows``, and a norm that does not declare ``fuses_products``, must get plain tensors
+    with the values of the separate kernels."""
+    from dotllm_b200.config import PartSpec
+    from dotllm_b200.parts import make_part
+    from dotllm_b200.parts.base import Norm, normalised_for
+    rt = runtime(torch.bfloat16)
+    ffn = make_part("feed_forward", PartSpec("gated_mlp", {"intermediate_size": 176, "activation": "silu"}), 64, rt)
+    bind_random(ffn, 3, torch.bfloat16)
+    norm = make_part("norm", PartSpec("rmsnorm", {"eps": 1e-5, "gain_init": ("one_plus_uniform", 0.1)}), 64, rt)
+    bind_random(norm, 4, torch.bfloat16)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(3, 64, generator=g).to(torch.bfloat16).to(DEV)
+    stream0 = torch.randn(3, 64, generator=g).to(DEV)
+
+    class PlainConsumer:
+        pass
+
+    class PlainNorm(Norm):
+        def add_forward(self, residual, delta):
+            assert isinstance(delta, torch.Tensor)
+            residual += delta
+            return residual.to(torch.bfloat16)
+
+    pending = ffn.forward(x)
+    assert isinstance(pending, ops.PendingProduct)
+    want_stream = stream0.clone()
+    want = norm.add_forward(want_stream, pending.tensor())
+    # a consumer that fuses gets scaled rows standing for the same values
+    s1 = stream0.clone()
+    rows = normalised_for(ffn, norm, s1, ffn.forward(x))
+    assert isinstance(rows, ops.ScaledRows) and torch.equal(s1, want_stream) and torch.equal(rows.tensor(), want)
+    # a consumer that does not fuse gets the tensor
+    s2 = stream0.clone()
+    got = normalised_for(PlainConsumer(), norm, s2, ffn.forward(x))
+    assert isinstance(got, torch.Tensor) and torch.equal(got, want) and torch.equal(s2, want_stream)
+    # a norm that does not fuse gets a tensor to add
+    s3 = stream0.clone()
+    got = normalised_for(ffn, PlainNorm({}, 64, rt), s3, ffn.forward(x))
+    assert isinstance(got, torch.Tensor) and torch.equal(s3, want_stream)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
