@@ -99,7 +99,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int tile = blockIdx.x, h = blockIdx.y;
+    const int tile = blockIdx.y, h = blockIdx.x;             // x fastest: all heads of the caller's first (longest) tile start first
     const int b = tile_seq[tile];
     const int tile_row = tile_row0[tile];                // first of the block's rows among the sequence's new tokens
     const int n_new = seq_new[b];
@@ -372,7 +372,8 @@ extern "C" int dl_attention_prefill_bf16(const void* q, int q_stride, void* out,
                "attention_prefill: q and the pools must be 16-byte aligned");
     DL_REQUIRE(nh <= 65535, "attention_prefill: too many heads");
     if (n_tiles == 0) return DL_OK;
-    dim3 grid(n_tiles, nh);
+    DL_REQUIRE(n_tiles <= 65535, "attention_prefill: too many tiles (%d)", n_tiles);
+    dim3 grid(nh, n_tiles);
     cudaStream_t s = (cudaStream_t)stream;
 #define AP_CASE(HDV)                                                                                                  \
     if (hd == HDV)                                                                                                    \

@@ -110,8 +110,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     __shared__ volatile int gave_up;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int blk = gridDim.x - 1 - blockIdx.x;              // later rows see more keys: start them first
-    const int head = blockIdx.y, kvh = head / group;
+    // Blocks are handed out with x fastest: all heads of the first tile, then of the second.  The caller
+    // lists the tiles with the most keys first, so the long blocks start first and the short ones fill
+    // the multiprocessors' last gaps; the heads of a KV group run side by side and share its pages in L2.
+    const int blk = blockIdx.y;
+    const int head = blockIdx.x, kvh = head / group;
     const int b = tile_seq[blk], row0 = tile_row0[blk];
     const int start = seq_start[b], n_new = seq_new[b];
     const int total = start + n_new;                         // keys the sequence holds after this step
@@ -502,7 +505,8 @@ static int pt_launch(dim3 grid, cudaStream_t s, const void* q, int q_stride, int
 }
 
 // q, out: bf16 [n_tokens, nh*hd] packed new tokens of all sequences.  tile_seq / tile_row0: for every
-// 128-row tile its sequence and its first row among that sequence's new tokens.  seq_start,
+// 256-row tile its sequence and its first row among that sequence's new tokens, best with the tiles
+// that see the most keys first.  seq_start,
 // seq_new: cached length before the step and new tokens, per sequence; cu_new: packed offsets.
 // head_dim 64 or 128.  status: int32, set non-zero if a wait expired.
 extern "C" int dl_attention_prefill_tc_bf16(const void* q, int q_stride, int n_tokens, void* out, int out_stride,
@@ -518,10 +522,11 @@ extern "C" int dl_attention_prefill_tc_bf16(const void* q, int q_stride, int n_t
                    ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0,
                "attention_prefill_tc: q, out and the pools must be 16-byte aligned with rows a multiple of 16 bytes");
     DL_REQUIRE(q_stride >= nh * hd && out_stride >= nh * hd, "attention_prefill_tc: row strides shorter than the rows");
-    DL_REQUIRE(nh <= 65535 && (long long)n_pages * nkv * (hd > DL_PAGE ? hd : DL_PAGE) < (1ll << 31),
+    DL_REQUIRE((long long)n_pages * nkv * (hd > DL_PAGE ? hd : DL_PAGE) < (1ll << 31),
                "attention_prefill_tc: too many heads or pages");
     if (n_tiles == 0) return DL_OK;
-    dim3 grid(n_tiles, nh);
+    DL_REQUIRE(n_tiles <= 65535, "attention_prefill_tc: too many tiles (%d)", n_tiles);
+    dim3 grid(nh, n_tiles);
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 64)
         return pt_launch<64>(grid, s, q, q_stride, n_tokens, out, out_stride, k_pool, v_pool, n_pages, tile_seq, tile_row0,

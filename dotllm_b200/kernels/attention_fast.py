@@ -100,11 +100,11 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
     tc = PREFILL_TC and head_dim in PREFILL_TC_HEAD_DIMS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
     rows = PREFILL_TC_ROWS if tc else PREFILL_ROWS
     if ("prefill_tiles", rows) not in plan.scratch:
-        tile_seq, tile_row0 = [], []
-        for b, n in enumerate(plan.news):
-            for r0 in range(0, n, rows):
-                tile_seq.append(b)
-                tile_row0.append(r0)
+        # tiles that see the most keys first: the kernels start blocks in this order, and the short
+        # ones at the end fill the multiprocessors' last gaps
+        tiles = [(b, r0) for b, n in enumerate(plan.news) for r0 in range(0, n, rows)]
+        tiles.sort(key=lambda t: -(plan.starts[t[0]] + min(plan.news[t[0]], t[1] + rows)))
+        tile_seq, tile_row0 = [t[0] for t in tiles], [t[1] for t in tiles]
         host = torch.tensor(tile_seq + tile_row0, dtype=torch.int32)
         dev = host.pin_memory().to(q.device, non_blocking=True)
         plan.scratch[("prefill_tiles", rows)] = (dev[:len(tile_seq)], dev[len(tile_seq):], len(tile_seq))
