@@ -350,7 +350,6 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
             if (whole) {
                 gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, w.out_stride, tile, M, N, g, t, row_scale, w.fuse, stream_in, gain_in);
             } else {
-#ifndef GS_EXP_NO_FIXUP
                 // a warp's first tile may be shared with the share before, its last with the share after
                 const int which = (tile == begin / cpt) ? 0 : 1;
                 float* mine = partials + ((size_t)gw * 2 + which) * (NT * 4 * 32);
@@ -386,7 +385,6 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
                     }
                     gs_epilogue<NT, TOut, FUSE_SWIGLU>(acc, out, w.out_stride, tile, M, N, g, t, row_scale, w.fuse, stream_in, gain_in);
                 }
-#endif
             }
 #pragma unroll
             for (int j = 0; j < NT; ++j)

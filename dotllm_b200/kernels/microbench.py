@@ -210,13 +210,15 @@ def main(argv=None):
             lib.dl_gemm_skinny_timeline.argtypes = [ctypes.c_void_p]
             if lib.dl_gemm_skinny_timeline(buf) != 0:
                 raise SystemExit("could not read the timeline")
-            blocks = min(148, 2048 // 7)
-            first = min(buf[b * 7] for b in range(blocks) if buf[b * 7])
+            stride = 8                                      # warps of a block: six consumers, the producer, the statistics warp
+            blocks = min(148, 2048 // stride)
+            first = min(buf[b * stride] for b in range(blocks) if buf[b * stride])
             names = ["block_start", "barriers_ready", "first_chunk_landed", "last_chunk_consumed", "share_done", "block_end"]
             spread = {}
             for e, name in enumerate(names):
                 warps = [0] if e in (0, 1, 5) else range(6)
-                v = [buf[e * 2048 + b * 7 + w] - first for b in range(blocks) for w in warps if buf[e * 2048 + b * 7 + w]]
+                v = [buf[e * 2048 + b * stride + w] - first for b in range(blocks) for w in warps
+                     if buf[e * 2048 + b * stride + w]]
                 spread[name] = [min(v), sum(v) // len(v), max(v)]
             result["timeline_ns_min_mean_max"] = spread
         # The same product as a decode step issues it: launches back to back from a captured graph,
