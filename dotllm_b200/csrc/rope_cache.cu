@@ -72,7 +72,9 @@ rope_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
 // fastest, so that the tokens of one page (consecutive positions of one sequence) fill whole
 // 128-byte lines of the transposed V page instead of one 2-byte element each.
 #define RT_TOKENS 64
+#ifndef RT_THREADS
 #define RT_THREADS 256
+#endif
 template <typename T>
 __global__ void __launch_bounds__(RT_THREADS)
 rope_cache_write_tile_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
@@ -89,7 +91,9 @@ rope_cache_write_tile_kernel(T* __restrict__ q, int q_stride, const T* __restric
     const int t0 = blockIdx.x * RT_TOKENS;
     const int nt = min(RT_TOKENS, n_tokens - t0);
     const int half = rotary_dim / 2;
-    const bool is_q = (int)blockIdx.y < nh;
+    // KV heads first: their blocks do more (K to its page, V through the transposing tile) and should not start last
+    const int kv_first = write_cache ? nkv : 0;
+    const bool is_q = (int)blockIdx.y >= kv_first;
     const int pitch = hd + (int)(4 / sizeof(T));             // an odd number of 32-bit words: no bank conflicts on the transpose
     if (threadIdx.x < RT_TOKENS) {
         int pos = -1, page = -1;
@@ -110,7 +114,7 @@ rope_cache_write_tile_kernel(T* __restrict__ q, int q_stride, const T* __restric
             const int i = idx / half, p = idx - i * half;
             const int pos = s_pos[i];
             if (pos < 0) continue;
-            T* row = q + (size_t)(t0 + i) * q_stride + (size_t)blockIdx.y * hd;
+            T* row = q + (size_t)(t0 + i) * q_stride + (size_t)((int)blockIdx.y - kv_first) * hd;
             const float x0 = dl_to_f32<T>(row[p]), x1 = dl_to_f32<T>(row[p + half]);
             const float c = cos_t[(size_t)pos * half + p], s = sin_t[(size_t)pos * half + p];
             row[p] = dl_from_f32<T>(rope_lo(x0, x1, c, s));
@@ -119,7 +123,7 @@ rope_cache_write_tile_kernel(T* __restrict__ q, int q_stride, const T* __restric
         return;
     }
     if (!write_cache) return;
-    const int h = blockIdx.y - nh;                           // a KV head: rotate K on its way to the page, stage V
+    const int h = blockIdx.y;                                // a KV head: rotate K on its way to the page, stage V
     for (int idx = threadIdx.x; idx < nt * hd; idx += RT_THREADS) {
         const int i = idx / hd, d = idx - i * hd;
         const int page = s_page[i], pos = s_pos[i];
@@ -182,7 +186,9 @@ rope_cache_write_tile_vec_kernel(__nv_bfloat16* __restrict__ q, int q_stride, co
     const int t0 = blockIdx.x * RT_TOKENS;
     const int nt = min(RT_TOKENS, n_tokens - t0);
     const int half = hd / 2, groups = half / 8;              // groups of eight rotation pairs per head
-    const bool is_q = (int)blockIdx.y < nh;
+    // KV heads first: their blocks do more (K to its page, V through the transposing tile) and should not start last
+    const int kv_first = write_cache ? nkv : 0;
+    const bool is_q = (int)blockIdx.y >= kv_first;
     const int pitch = hd + 2;
     if (threadIdx.x < RT_TOKENS) {
         int pos = -1, page = -1;
@@ -203,7 +209,7 @@ rope_cache_write_tile_vec_kernel(__nv_bfloat16* __restrict__ q, int q_stride, co
             const int i = idx / groups, u = (idx - i * groups) * 8;
             const int pos = s_pos[i];
             if (pos < 0) continue;
-            __nv_bfloat16* row = q + (size_t)(t0 + i) * q_stride + (size_t)blockIdx.y * hd;
+            __nv_bfloat16* row = q + (size_t)(t0 + i) * q_stride + (size_t)((int)blockIdx.y - kv_first) * hd;
             uint4 x0 = *reinterpret_cast<const uint4*>(row + u), x1 = *reinterpret_cast<const uint4*>(row + half + u);
             rope_rotate8(x0, x1, cos_t + (size_t)pos * half + u, sin_t + (size_t)pos * half + u);
             *reinterpret_cast<uint4*>(row + u) = x0;
@@ -212,7 +218,7 @@ rope_cache_write_tile_vec_kernel(__nv_bfloat16* __restrict__ q, int q_stride, co
         return;
     }
     if (!write_cache) return;
-    const int h = blockIdx.y - nh;                           // a KV head: rotate K on its way to the page, stage V
+    const int h = blockIdx.y;                                // a KV head: rotate K on its way to the page, stage V
     for (int idx = threadIdx.x; idx < nt * groups; idx += RT_THREADS) {
         const int i = idx / groups, u = (idx - i * groups) * 8;
         const int page = s_page[i], pos = s_pos[i];

@@ -260,11 +260,18 @@ def main(argv=None):
         result.update(rows=rows, width=width, ms=ms, best_ms=best)
     elif args.kernel == "rope":
         rows = args.rows
-        k_pool, v_pool, table = _paged(rows, 128, nkv, hd, dev)
         qkv = torch.randn(rows, (nh + 2 * nkv) * hd, device=dev, dtype=torch.bfloat16)
-        cos = torch.rand(256, hd // 2, device=dev)
-        sin = torch.rand(256, hd // 2, device=dev)
-        seqs, pos = t32(list(range(rows))), t32([100] * rows)
+        if rows <= 64:                                      # a decode step: one token of each of `rows` sequences
+            k_pool, v_pool, table = _paged(rows, 128, nkv, hd, dev)
+            cos = torch.rand(256, hd // 2, device=dev)
+            sin = torch.rand(256, hd // 2, device=dev)
+            seqs, pos = t32(list(range(rows))), t32([100] * rows)
+        else:                                               # a prompt: `rows` tokens of one sequence
+            k_pool, v_pool, table = _paged(1, (rows + 63) // 64, nkv, hd, dev)
+            cos = torch.rand(rows, hd // 2, device=dev)
+            sin = torch.rand(rows, hd // 2, device=dev)
+            seqs, pos = t32([0] * rows), t32(list(range(rows)))
+            result["bytes"] = qkv.numel() * 2 + nh * hd * rows * 2 + 2 * nkv * hd * rows * 2
         qd, kvd = nh * hd, nkv * hd
         fn = lambda: ops.rope_cache_write(qkv[:, :qd], qkv[:, qd:qd + kvd], qkv[:, qd + kvd:], cos, sin, hd, seqs, pos,
                                           table, k_pool, v_pool, nh, nkv, hd)
