@@ -253,6 +253,17 @@ def test_argmax_ties_and_sizes():
         out = ops().sample(x.to(DEV))
         assert out.tolist()[0] == vocab // 2
         assert out.tolist()[1:] == torch.argmax(x, dim=-1).tolist()[1:]
+    # the greedy kernel cuts a row into slices for a cluster of blocks: a tie across slices, a row with
+    # nothing finite, NaN beside the maximum, and a vocabulary that the slices do not divide
+    x = torch.randn(4, 1003, generator=g)
+    x[1, 7] = x[1, 900] = 9.0
+    x[2] = float("-inf")
+    x[3, 5] = float("nan")
+    x[3, 600] = 8.0
+    assert ops().sample(x.to(DEV)).tolist() == [int(torch.argmax(x[0])), 7, 0, 600]
+    # ... and the same through the sampling kernel's own greedy branch (a temperature of 0 per row)
+    zeros = torch.zeros(4, device=DEV)
+    assert ops().sample(x.to(DEV), temperature=zeros, uniform=zeros).tolist() == [int(torch.argmax(x[0])), 7, 0, 600]
 
 
 def _sampled_ok(row, tok, r, **kw):
