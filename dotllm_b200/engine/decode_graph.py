@@ -41,6 +41,7 @@ class _Captured:
         self.host_version = [-1] * _RING                   # version each staging buffer holds
         self.device_version = -1                           # version the device tables hold
         self.h2d_bytes = 0                                 # bytes copied host -> device so far
+        self.staged_for = None                             # (sequences, lengths) whose next step is already on the device
         b = batch
         self.pos, self.total, self.slots = self.ints[0:b], self.ints[b:2 * b], self.ints[2 * b:3 * b]
         self.tables = {}
@@ -60,14 +61,24 @@ class _Captured:
         self.graph = None
         self.logits = None
 
-    def stage(self, seqs, tokens, kv_groups):
-        """Copy this step's positions, lengths, slots and block tables (and tokens, when the host
-        supplies them) to the device."""
+    def stage(self, seqs, tokens, kv_groups, metadata=True):
+        """Copy this step's positions, lengths, slots and block tables (``metadata``) and its tokens
+        (when the host supplies them) to the device."""
         i = self.turn
         self.turn = (self.turn + 1) % _RING
         if self.events[i] is not None:
             self.events[i].synchronize()                   # the copy that last used this buffer is done
         b, p = self.batch, self.pages
+        if not metadata:
+            host, view = self.host[i], self.host_views[i]
+            n = 3 * b + self.table_mirror.size
+            view[n:n + b] = tokens
+            self.tokens.copy_(host[n:n + b], non_blocking=True)
+            self.h2d_bytes += 4 * b
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[i] = ev
+            return
         # Block tables change only when a sequence takes or gives back a page (or the batch changes):
         # keep a host mirror, rewrite the rows that changed, and send the tables only then.
         for gi, g in enumerate(kv_groups):
@@ -150,22 +161,51 @@ class DecodeGraphs:
                                 f"{model.spec.max_positions}")
             if not device_tokens and not 0 <= int(e.tokens[0]) < model.spec.vocab_size:
                 raise StepError(f"entry {i}: token id {e.tokens[0]} is outside the vocabulary")
-        cache.reserve([(s, s.length + 1) for s in seqs])
-        pages = max(max((len(s.pages[g.index]) for g in cache.kv_groups), default=1) for s in seqs)
+        tokens = None if device_tokens else [int(e.tokens[0]) for e in entries]
         cap = self.captured.get(b)
-        fresh = cap is None or cap.pages < pages
-        if fresh:
-            room = min((model.spec.max_positions + PAGE - 1) // PAGE, max(pages + 16, (pages * 5) // 4))
-            cap = _Captured(model, cache, b, max(room, pages), len(cache.kv_groups))
-            self.captured[b] = cap
-        cap.stage(seqs, None if device_tokens else [int(e.tokens[0]) for e in entries], cache.kv_groups)
+        if cap is not None and self._staged(cap, seqs):
+            # the step before this one already reserved the pages and sent everything but the tokens
+            if tokens is not None:
+                cap.stage(seqs, tokens, cache.kv_groups, metadata=False)
+            fresh = False
+        else:
+            cache.reserve([(s, s.length + 1) for s in seqs])
+            pages = max(max((len(s.pages[g.index]) for g in cache.kv_groups), default=1) for s in seqs)
+            fresh = cap is None or cap.pages < pages
+            if fresh:
+                room = min((model.spec.max_positions + PAGE - 1) // PAGE, max(pages + 16, (pages * 5) // 4))
+                cap = _Captured(model, cache, b, max(room, pages), len(cache.kv_groups))
+                self.captured[b] = cap
+            cap.stage(seqs, tokens, cache.kv_groups)
+        cap.staged_for = None
         if fresh:
             cap.capture(model, cache)
             self.captures += 1
         cap.graph.replay()
         for s in seqs:
             cache.commit(s, s.length + 1)
+        self._stage_ahead(cap, seqs)
         return cap.logits
+
+    @staticmethod
+    def _staged(cap, seqs):
+        """Is the device already set up for exactly these sequences at their present lengths?"""
+        ahead = cap.staged_for
+        return (ahead is not None and len(ahead[0]) == len(seqs)
+                and all(a is s and n == s.length for a, n, s in zip(ahead[0], ahead[1], seqs)))
+
+    def _stage_ahead(self, cap, seqs):
+        """While the device works on this step, send the next step's positions, lengths, slots and
+        tables for the same sequences behind the running graph (same stream: they land after it has
+        read the current ones), so that the next call only adds its tokens.  Only when no sequence
+        needs a new page for its next token: nothing is reserved on a guess.  If the next call brings
+        other sequences, or these at other lengths, it stages everything afresh."""
+        model, cache = self.model, self.cache
+        for s in seqs:
+            if s.length + 1 > model.spec.max_positions or any(cache.pages_needed(s, s.length + 1).values()):
+                return
+        cap.stage(seqs, None, cache.kv_groups)
+        cap.staged_for = (list(seqs), [s.length for s in seqs])
 
     def token_buffer(self, batch):
         """The device token buffer of the graph for ``batch`` sequences (after its first run)."""

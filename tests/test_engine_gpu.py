@@ -246,3 +246,41 @@ def test_dependent_launch_changes_no_bit(tmp, which):
         assert torch.equal(got, base), f"graphs={graphs}: max diff {(got - base).abs().max()}"
         again = run(True, graphs)
         assert torch.equal(got, again), f"graphs={graphs}: two runs differ by {(got - again).abs().max()}"
+
+
+def test_graph_steps_staged_ahead_follow_what_the_caller_does(tmp):
+    """After a captured decode step the next step's positions, lengths and tables are sent ahead for the
+    same sequences.  The guess must be dropped when the caller does something else: crosses a page,
+    swaps a sequence for another of the same length, truncates one, or runs an eager step in between.
+    In float32 every cut gives the same bits, so graphs are compared with eager steps exactly."""
+    from dotllm_b200 import StepEntry
+    model, cfg, _, _ = load_pair(tmp, "A", torch.float32)
+    vocab = cfg["vocab_size"]
+    prompts = [tiny_models.random_tokens(n, vocab, seed=500 + n) for n in (61, 30, 61)]
+    feed = [tiny_models.random_tokens(40, vocab, seed=600 + i) for i in range(3)]
+
+    def run(graphs):
+        cache = model.new_cache(max_tokens=1024)
+        seqs = [cache.open_sequence() for _ in prompts]
+        outs = [model.step(cache, [StepEntry(s, p, [len(p) - 1]) for s, p in zip(seqs, prompts)])]
+        # a graph's logits live in a buffer that its next replay overwrites: keep copies
+        two = lambda t, a, b: model.step(cache, [StepEntry(seqs[a], [feed[a][t]]), StepEntry(seqs[b], [feed[b][t]])],
+                                         graphs=graphs).clone()
+        for t in range(6):                                  # 0 and 1 together; sequence 0 crosses a page at its 65th token
+            outs.append(two(t, 0, 1))
+        for t in range(6, 9):                               # same batch size and slot order, but 2 (as long as 0 was) for 0
+            outs.append(two(t, 2, 1))
+        outs.append(two(9, 0, 1))                           # back again
+        cache.truncate(seqs[1], seqs[1].length - 2)         # 1 goes two tokens back and on from there
+        for t in range(10, 14):
+            outs.append(two(t, 0, 1))
+        outs.append(model.step(cache, [StepEntry(seqs[0], [feed[0][14]]), StepEntry(seqs[1], [feed[1][14]])]))   # an eager step
+        for t in range(15, 18):
+            outs.append(two(t, 0, 1))
+        cache.check()
+        for s in seqs:
+            cache.close_sequence(s)
+        return torch.cat(outs).clone()
+
+    eager, graphed = run(False), run(True)
+    assert torch.equal(eager, graphed), f"max diff {(eager - graphed).abs().max()}"
