@@ -137,6 +137,7 @@ class DecodeGraphs:
         self.cache = cache
         self.captured = {}
         self.captures = 0
+        self.ahead_hits = 0                                # steps that found their positions and tables already sent
 
     def takes(self, entries):
         return all(len(e.tokens) == 1 and (e.want is None or list(e.want) == [0]) for e in entries)
@@ -167,6 +168,7 @@ class DecodeGraphs:
             # the step before this one already reserved the pages and sent everything but the tokens
             if tokens is not None:
                 cap.stage(seqs, tokens, cache.kv_groups, metadata=False)
+            self.ahead_hits += 1
             fresh = False
         else:
             cache.reserve([(s, s.length + 1) for s in seqs])

@@ -278,6 +278,11 @@ def test_graph_steps_staged_ahead_follow_what_the_caller_does(tmp):
         for t in range(15, 18):
             outs.append(two(t, 0, 1))
         cache.check()
+        if graphs:
+            # of the 17 graph steps, those straight after another one of the same two sequences at the next
+            # length find everything but their tokens on the device: not the first, not after a swap, the
+            # truncation or the eager step, and not the two steps that need a new page
+            assert model.decode_graphs(cache).ahead_hits == 11
         for s in seqs:
             cache.close_sequence(s)
         return torch.cat(outs).clone()
