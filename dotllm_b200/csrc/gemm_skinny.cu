@@ -361,15 +361,15 @@ __device__ __forceinline__ void gs_consume(const GsWork& w, const GsRings& r, fl
                 const int g_lo = (tile * cpt) / share, g_hi = ((tile + 1) * cpt - 1) / share;
                 int last = 0;
                 if (lane == 0) {
-                    __threadfence();
-                    const int seen = atomicAdd(&counters[tile], 1);
+                    // One read-modify-write that releases this warp's part (the lanes' stores are ordered
+                    // before it by the __syncwarp above) and acquires the parts of the warps counted before.
+                    int seen;
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(seen) : "l"(counters + tile) : "memory");
                     last = (seen == g_hi - g_lo) ? 1 : 0;
-                    if (last) {
-                        counters[tile] = 0;              // ready for the next product or launch
-                        __threadfence();
-                    }
+                    if (last) counters[tile] = 0;        // ready for the next product or launch
                 }
                 last = __shfl_sync(0xffffffffu, last, 0);
+                __syncwarp();                            // the other lanes' reads below come after lane 0's acquire
                 if (last) {
 #pragma unroll
                     for (int j = 0; j < NT; ++j)
