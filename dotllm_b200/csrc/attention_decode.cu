@@ -17,8 +17,9 @@
 // per stage, and runs ahead of the arithmetic by the depth of the ring, across segment boundaries,
 // at no cost in registers.  Consumer warp w takes pages w, w + C, ... of the stream; at the end of a
 // segment the warps merge their partial results in shared memory and the block writes either the
-// output (the segment was the whole pair) or the segment's partial (max, sum, weighted values).  A
-// second small kernel merges the segments of a (sequence, head) in block order.
+// output (the segment was the whole pair) or the segment's partial (max, sum, weighted values) and
+// counts itself in; the block that brings a pair's last missing segment merges the pair's segments in
+// block order and writes the output (no second kernel, and the same bits whoever arrives last).
 //
 // Arithmetic: lane (g, t) reads 16-byte pieces of K rows: dims 8t..8t+7 of a 32-dim slice are a
 // consistent permutation of k for Q and K in two MMAs; the 8 key columns of score tile j are keys
@@ -164,6 +165,7 @@ struct AdWalk {
 };
 struct AdSeg {
     int b, kvh, len, first_key, run_begin, page0, n_pages, slot;
+    int pair_begin, pair_pages;      // where the (sequence, KV head)'s pages start in the step's list, and how many they are
     bool whole;
 };
 
@@ -203,6 +205,8 @@ __device__ __forceinline__ bool ad_walk_next(AdWalk& w, AdSeg& s, const int32_t*
     s.run_begin = s.page0 * DL_PAGE;
     s.n_pages = n;
     s.whole = (w.pg == 0 && n == w.np);
+    s.pair_begin = w.r - w.pg;
+    s.pair_pages = w.np;
     s.slot = w.first ? 0 : 1;
     w.first = false;
     w.r += n;
@@ -257,6 +261,57 @@ __device__ __forceinline__ void ad_rotate8(uint4& x0, uint4& x1, const float* cs
     }
 }
 
+// Merge the segments of one (sequence, KV head) that the cut spread over the blocks i0 .. i0 + n_seg - 1,
+// in block order, and write the group's heads.  The pair's first segment sits in its block's first or
+// last slot (`slot_first`), every other segment in its block's first.  Called by the consumer threads
+// of the block that wrote the pair's last missing segment; thread -> (head of the group, four dims);
+// the loads of up to BATCH segments are issued together and bypass the L1 (other multiprocessors wrote them).
+template <int HD, int BATCH>
+__device__ __forceinline__ void ad_merge_pair(__nv_bfloat16* __restrict__ out_pair, int group, int i0, int n_seg, int slot_first,
+                                              const float* __restrict__ part_o, const float* __restrict__ part_ml, int tid,
+                                              int n_threads) {
+    constexpr int hd4 = HD / 4;
+    for (int idx = tid; idx < group * hd4; idx += n_threads) {
+        const int r = idx / hd4, d = (idx - r * hd4) * 4;
+        float m = -INFINITY, l = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp0 = 0; sp0 < n_seg; sp0 += BATCH) {
+            float2 ml[BATCH];
+            float4 o[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                if (sp0 + j < n_seg) {
+                    const int slot = (sp0 + j == 0) ? slot_first : 0;
+                    const size_t row = ((size_t)(i0 + sp0 + j) * 2 + slot) * group + r;
+                    ml[j] = __ldcg(reinterpret_cast<const float2*>(part_ml + row * 2));
+                    o[j] = __ldcg(reinterpret_cast<const float4*>(part_o + row * HD + d));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                if (sp0 + j < n_seg) {
+                    const float mn = fmaxf(m, ml[j].x);
+                    const float f_old = (m == -INFINITY) ? 0.f : ad_ex2(m - mn);
+                    const float f_new = (ml[j].x == -INFINITY) ? 0.f : ad_ex2(ml[j].x - mn);
+                    acc.x = acc.x * f_old + o[j].x * f_new;
+                    acc.y = acc.y * f_old + o[j].y * f_new;
+                    acc.z = acc.z * f_old + o[j].z * f_new;
+                    acc.w = acc.w * f_old + o[j].w * f_new;
+                    l = l * f_old + ml[j].y * f_new;
+                    m = mn;
+                }
+            }
+        }
+        const float inv = 1.f / l;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(out_pair + (size_t)r * HD + d) = packed;
+    }
+}
+
 // WIDE: the group has more than 8 query heads, so fragment rows 8..15 carry data too.
 template <int HD, bool WIDE>
 __global__ void __launch_bounds__(AD_THREADS, 1)
@@ -266,7 +321,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_table,
                         int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int n_stages,
                         float* __restrict__ part_o,
-                        float* __restrict__ part_ml, const AdFresh fresh, int* __restrict__ status) {
+                        float* __restrict__ part_ml, int* __restrict__ pair_counters, const AdFresh fresh,
+                        int* __restrict__ status) {
     constexpr int DC = HD / 32;          // 32-dim slices of a head
     constexpr int DT = HD / 8;           // 8-dim output tiles
     constexpr int PAGE_ELEMS = DL_PAGE * HD;
@@ -279,6 +335,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     __shared__ uint64_t full_bar[AD_MAX_STAGES], empty_bar[AD_MAX_STAGES];
     __shared__ float sm_m[AD_MAX_STAGES][16], sm_l[AD_MAX_STAGES][16];
     __shared__ volatile int gave_up;
+    __shared__ int last_of_pair;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -651,92 +708,36 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                 }
             }
             ad_consumer_sync(n_stages);                              // the merge buffers are free for the next run
+            if (!w.whole) {
+                // The pair's pages are spread over the blocks i0 .. i1 of the cut.  Each of them counts itself
+                // in once its segment is written (one acquire-release atomic: the consumer warps' stores
+                // are ordered before it by the barrier above); whichever arrives last merges the
+                // segments in block order - the same bits whatever the order of arrival.
+                const int i0 = w.pair_begin / cut.share, i1 = (w.pair_begin + w.pair_pages - 1) / cut.share;
+                if (tid == 0) {
+                    int seen;
+                    int* counter = pair_counters + w.b * nkv + w.kvh;
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(seen) : "l"(counter) : "memory");
+                    last_of_pair = (seen == i1 - i0) ? 1 : 0;
+                    if (seen == i1 - i0) *counter = 0;               // ready for the next launch
+                }
+                ad_consumer_sync(n_stages);
+                const bool last = last_of_pair != 0;
+                ad_consumer_sync(n_stages);                          // everyone has read the flag before it is written again
+                if (last)
+                    ad_merge_pair<HD, WIDE ? 4 : 8>(out + (size_t)w.b * out_stride + (size_t)w.kvh * group * HD, group, i0, i1 - i0 + 1,
+                                      (w.pair_begin == i0 * cut.share) ? 0 : 1, part_o, part_ml, tid, 32 * n_stages);
+            }
         }
     }
     __syncthreads();                                         // nobody leaves while copies may still land
-}
-
-// Merge the segments of every (sequence, KV head) that the cut spread over more than one block, in
-// block order.  One block per (sequence, KV head); thread -> (head of the group, four dims).  The
-// cut is recomputed from the lengths exactly as the main kernel computed it; the loads of up to
-// eight segments are issued together.
-__global__ void __launch_bounds__(128)
-attention_decode_combine_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const int32_t* __restrict__ seq_len,
-                                int n_seqs, int nh, int nkv, int hd, int window, int n_blocks,
-                                const float* __restrict__ part_o, const float* __restrict__ part_ml) {
-    dl_launch_dependents();
-    const int kvh = blockIdx.x, b = blockIdx.y;
-    const int group = nh / nkv;
-    const int hd4 = hd >> 2;
-    const int lane = threadIdx.x & 31;
-    dl_grid_dependency_wait();
-    int sum = 0, before = 0;
-    for (int b0 = 0; b0 < n_seqs; b0 += 32)
-        if (b0 + lane < n_seqs) {
-            const int np = ad_pages_of(seq_len[b0 + lane], window);
-            sum += np;
-            if (b0 + lane < b) before += np;
-        }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        before += __shfl_xor_sync(0xffffffffu, before, o);
-    }
-    const int total = sum * nkv;
-    const int share = max(1, (total + n_blocks - 1) / n_blocks);
-    const int np_b = ad_pages_of(seq_len[b], window);
-    if (np_b == 0) return;
-    const int begin = before * nkv + kvh * np_b;             // this pair's place in the list of pages
-    const int i0 = begin / share, i1 = (begin + np_b - 1) / share;
-    if (i0 == i1) return;                                    // one block had it all and wrote the output itself
-    const int slot_first = (begin == i0 * share) ? 0 : 1;    // the pair's first segment is its block's first or last
-    const int n_seg = i1 - i0 + 1;
-    for (int idx = threadIdx.x; idx < group * hd4; idx += blockDim.x) {
-        const int r = idx / hd4, d = (idx - r * hd4) * 4;
-        float m = -INFINITY, l = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int sp0 = 0; sp0 < n_seg; sp0 += 8) {
-            float2 ml[8];
-            float4 o[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (sp0 + j < n_seg) {
-                    const int slot = (sp0 + j == 0) ? slot_first : 0;
-                    const size_t row = ((size_t)(i0 + sp0 + j) * 2 + slot) * group + r;
-                    ml[j] = *reinterpret_cast<const float2*>(part_ml + row * 2);
-                    o[j] = *reinterpret_cast<const float4*>(part_o + row * hd + d);
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (sp0 + j < n_seg) {
-                    const float mn = fmaxf(m, ml[j].x);
-                    const float f_old = (m == -INFINITY) ? 0.f : ad_ex2(m - mn);
-                    const float f_new = (ml[j].x == -INFINITY) ? 0.f : ad_ex2(ml[j].x - mn);
-                    acc.x = acc.x * f_old + o[j].x * f_new;
-                    acc.y = acc.y * f_old + o[j].y * f_new;
-                    acc.z = acc.z * f_old + o[j].z * f_new;
-                    acc.w = acc.w * f_old + o[j].w * f_new;
-                    l = l * f_old + ml[j].y * f_new;
-                    m = mn;
-                }
-            }
-        }
-        const float inv = 1.f / l;
-        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-        __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
-        uint2 packed;
-        packed.x = *reinterpret_cast<uint32_t*>(&lo);
-        packed.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(out + (size_t)b * out_stride + (size_t)(kvh * group + r) * hd + d) = packed;
-    }
 }
 
 template <int HD, bool WIDE>
 static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int out_stride, void* k_pool,
                      void* v_pool, int n_pages, const int32_t* seq_len, const int32_t* block_table,
                      int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int blocks, float* part_o,
-                     float* part_ml, int part_slots, const AdFresh& fresh, int* status) {
+                     float* part_ml, int part_slots, int* pair_counters, int n_counters, const AdFresh& fresh, int* status) {
     const int group = nh / nkv;
     int dev = 0, sms = 0, max_smem = 0;
     cudaGetDevice(&dev);
@@ -761,17 +762,13 @@ static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int
     if (blocks > most_pages) blocks = (int)most_pages;
     if (part_slots < 2 * blocks)
         return dl_fail(DL_ERR_ARGUMENT, "attention_decode: scratch for %d segments, %d blocks need %d", part_slots, blocks, 2 * blocks);
+    if (pair_counters == nullptr || (long long)n_seqs * nkv > n_counters)
+        return dl_fail(DL_ERR_ARGUMENT, "attention_decode: %d counters, %d sequences x %d KV heads need one each", n_counters, n_seqs, nkv);
     cudaError_t le = dl_launch_dependent(
         attention_decode_kernel<HD, WIDE>, dim3(blocks), dim3(AD_THREADS), smem, s, (const __nv_bfloat16*)q, q_stride,
         (__nv_bfloat16*)out, out_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, seq_len,
-        block_table, bt_stride, n_seqs, nh, nkv, scale, window, n_stages, part_o, part_ml, fresh, status);
+        block_table, bt_stride, n_seqs, nh, nkv, scale, window, n_stages, part_o, part_ml, pair_counters, fresh, status);
     if (le != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "attention_decode: %s", cudaGetErrorString(le));
-    if (blocks > 1) {
-        cudaError_t e = dl_launch_dependent(attention_decode_combine_kernel, dim3(nkv, n_seqs), dim3(128), 0, s,
-                                            (__nv_bfloat16*)out, out_stride, seq_len, n_seqs, nh, nkv, HD, window, blocks,
-                                            (const float*)part_o, (const float*)part_ml);
-        if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "attention_decode_combine: %s", cudaGetErrorString(e));
-    }
     return DL_OK;
 }
 
@@ -780,14 +777,16 @@ static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int
 // blocks: persistent blocks to use (<= 0: one per multiprocessor).
 // part_o: float32 [part_slots, group, hd]; part_ml: float32 [part_slots, group, 2]: scratch for the
 // segments of (sequence, head) pairs that the cut spreads over several blocks, two per block.
+// pair_counters: int32 [n_counters >= n_seqs * nkv], zero before the first launch; every launch leaves
+// them zero (launches that share them must be on one stream).
 // status: int32, set non-zero if a wait expired.
 // Launched with programmatic dependent launch: of this call's inputs, a kernel of this library
 // launched directly before it may write only q and the newest page of each sequence (the rope and
 // cache-write kernel does); lengths, block tables and older pages must be complete by then.
 static int ad_dispatch(const void* q, int q_stride, void* out, int out_stride, void* k_pool, void* v_pool, int n_pages,
                        const int32_t* seq_len, const int32_t* block_table, int bt_stride, int n_seqs, int nh, int nkv, int hd,
-                       float scale, int window, int blocks, float* part_o, float* part_ml, int part_slots,
-                       const AdFresh& fresh, int* status, void* stream) {
+                       float scale, int window, int blocks, float* part_o, float* part_ml, int part_slots, int* pair_counters,
+                       int n_counters, const AdFresh& fresh, int* status, void* stream) {
     DL_REQUIRE(n_seqs >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad head counts");
     DL_REQUIRE(nh / nkv <= 16, "attention_decode: groups of more than 16 query heads are not supported (%d)", nh / nkv);
     DL_REQUIRE(scale > 0.f, "attention_decode: the score scale must be positive");
@@ -814,10 +813,10 @@ static int ad_dispatch(const void* q, int q_stride, void* out, int out_stride, v
         if (wide)                                                                                                      \
             return ad_launch<HDV, true>(s, q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table, \
                                         bt_stride, n_seqs, nh, nkv, scale, window, blocks, part_o, part_ml, part_slots, \
-                                        fresh, status);                                                                \
+                                        pair_counters, n_counters, fresh, status);                                     \
         return ad_launch<HDV, false>(s, q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table,   \
                                      bt_stride, n_seqs, nh, nkv, scale, window, blocks, part_o, part_ml, part_slots,   \
-                                     fresh, status);                                                                   \
+                                     pair_counters, n_counters, fresh, status);                                        \
     }
     AD_CASE(32) AD_CASE(64) AD_CASE(96) AD_CASE(128)
 #undef AD_CASE
@@ -828,11 +827,11 @@ extern "C" int dl_attention_decode_bf16(const void* q, int q_stride, void* out, 
                                         const void* v_pool, int n_pages, const int32_t* seq_len,
                                         const int32_t* block_table, int bt_stride, int n_seqs, int nh, int nkv,
                                         int hd, float scale, int window, int blocks, float* part_o, float* part_ml,
-                                        int part_slots, int* status, void* stream) {
+                                        int part_slots, int* pair_counters, int n_counters, int* status, void* stream) {
     AdFresh none = {};
     return ad_dispatch(q, q_stride, out, out_stride, const_cast<void*>(k_pool), const_cast<void*>(v_pool), n_pages, seq_len,
-                       block_table, bt_stride, n_seqs, nh, nkv, hd, scale, window, blocks, part_o, part_ml, part_slots, none,
-                       status, stream);
+                       block_table, bt_stride, n_seqs, nh, nkv, hd, scale, window, blocks, part_o, part_ml, part_slots,
+                       pair_counters, n_counters, none, status, stream);
 }
 
 // The same with the step's own token handled inside the kernel: q (unrotated), k_new and v_new
@@ -846,7 +845,8 @@ extern "C" int dl_attention_decode_fresh_bf16(const void* q, int q_stride, const
                                               void* out, int out_stride, void* k_pool, void* v_pool, int n_pages,
                                               const int32_t* seq_len, const int32_t* block_table, int bt_stride, int n_seqs,
                                               int nh, int nkv, int hd, float scale, int window, int blocks, float* part_o,
-                                              float* part_ml, int part_slots, int* status, void* stream) {
+                                              float* part_ml, int part_slots, int* pair_counters, int n_counters, int* status,
+                                              void* stream) {
     DL_REQUIRE(k_new != nullptr && v_new != nullptr, "attention_decode_fresh: needs the new keys and values");
     AdFresh fresh;
     fresh.k = (const __nv_bfloat16*)k_new;
@@ -858,5 +858,5 @@ extern "C" int dl_attention_decode_fresh_bf16(const void* q, int q_stride, const
     fresh.table_rows = table_rows;
     fresh.rotate = rotate;
     return ad_dispatch(q, q_stride, out, out_stride, k_pool, v_pool, n_pages, seq_len, block_table, bt_stride, n_seqs, nh, nkv,
-                       hd, scale, window, blocks, part_o, part_ml, part_slots, fresh, status, stream);
+                       hd, scale, window, blocks, part_o, part_ml, part_slots, pair_counters, n_counters, fresh, status, stream);
 }

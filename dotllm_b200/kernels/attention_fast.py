@@ -14,9 +14,9 @@ from . import library as _library
 _P, _I, _F = _library._P, _library._I, _library._F
 _library.register_signatures({
     "dl_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I,
-                                 _P, _P, _I, _P, _P],
+                                 _P, _P, _I, _P, _I, _P, _P],
     "dl_attention_decode_fresh_bf16": [_P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I,
-                                       _I, _F, _I, _I, _P, _P, _I, _P, _P],
+                                       _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _P],
     "dl_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                   _F, _I, _P, _P],
     "dl_attention_prefill_tc_bf16": [_P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
@@ -43,12 +43,26 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
     B = plan.n_seqs
     group = n_heads // n_kv_heads
     part_o, part_ml, slots = _decode_scratch(plan, group, head_dim, q.device)
+    counters = _pair_counters(q.device)
     _library.call("dl_attention_decode_bf16", q.data_ptr(), q_stride, out.data_ptr(), out.stride(0),
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, plan.seq_total.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim,
                   scale, window, DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots,
+                  counters.data_ptr(), counters.numel(),
                   _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     return True
+
+
+_counters = {}
+
+
+def _pair_counters(device):
+    """Per device: one arrival counter per (sequence, KV head) of a decode step.  Zero at rest: the block
+    that finishes a pair resets its counter.  Launches that share them must be on one stream."""
+    key = device.index
+    if key not in _counters:
+        _counters[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+    return _counters[key]
 
 
 def _decode_scratch(plan, group, head_dim, device):
@@ -85,12 +99,13 @@ def decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_h
     B = plan.n_seqs
     out = torch.empty((B, n_heads * head_dim), dtype=q.dtype, device=q.device)
     part_o, part_ml, slots = _decode_scratch(plan, group, head_dim, q.device)
+    counters = _pair_counters(q.device)
     _library.call("dl_attention_decode_fresh_bf16", q.data_ptr(), qs, k.data_ptr(), ks, v.data_ptr(), vs,
                   cos.data_ptr() if rotary_dim else None, sin.data_ptr() if rotary_dim else None,
                   cos.shape[0] if rotary_dim else 0, 1 if rotary_dim else 0, out.data_ptr(), out.stride(0),
                   k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], plan.seq_total.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window,
-                  DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots,
+                  DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots, counters.data_ptr(), counters.numel(),
                   _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     return out
 
