@@ -716,3 +716,19 @@ extern "C" int dl_gemm_skinny_bf16_static(const void* x, int x_stride, const voi
     return dl_gemm_skinny_bf16(x, x_stride, w, out, out_dtype, out_stride, M, N, K, fuse_swiglu ? 1 : 0, scratch->partials,
                                need_floats, scratch->counters, need_counters, &scratch->status, stream);
 }
+
+// The give-up word of the static calls on the current device: copies it to *code (0: every wait so
+// far was served) and clears it.  Waits for `stream` to drain, so that it speaks for every static
+// call queued there before it; allocates nothing.
+extern "C" int dl_gemm_skinny_static_status(int* code, void* stream) {
+    DL_REQUIRE(code != nullptr, "gemm_skinny_static_status: needs a place for the code");
+    GsStaticScratch* scratch = nullptr;
+    const int rc = gs_static_address(&scratch);
+    if (rc != DL_OK) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(code, &scratch->status, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess && *code != 0) e = cudaMemsetAsync(&scratch->status, 0, sizeof(int), s);
+    if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_skinny_static_status: %s", cudaGetErrorString(e));
+    return DL_OK;
+}

@@ -28,14 +28,26 @@ extern "C" {
 // Returns 0, or a status whose text dl_last_error() gives.  Shapes whose partial sums do not fit
 // the fixed scratch are refused with a message that says so; nothing is launched then.
 //
-// * No cudaMalloc, cudaFree or allocating library call is made, now or later.
+// * No cudaMalloc, cudaFree or allocating library call is made, now or later.  On the host the call
+//   takes two short mutexes (the per-device address table and the table of tensor maps) and, the first
+//   time it sees a matrix, encodes a tensor map for it (one driver call) and inserts it into a
+//   host-side map: a caller that must not block on host locks either should make one warm-up call per
+//   matrix first.
 // * The first call on a device looks up the scratch array's device address (one
 //   cudaGetSymbolAddress, with that device current) and remembers it; make that first call
 //   outside any stream capture.
 // * All calls on a device share the one array.  The call clears what must start at zero, but two
 //   calls that overlap on the GPU (different streams, no ordering between them) race on it.
+// * Every wait inside the kernel is bounded.  A wait that expires leaves `out` incomplete and sets a
+//   word inside the scratch array; the call itself has long returned 0 by then.  Ask for that word
+//   with dl_gemm_skinny_static_status at the next point where the results are needed.
 int dl_gemm_skinny_bf16_static(const void* x, int x_stride, const void* w, void* out, int out_dtype,
                                int out_stride, int M, int N, int K, int fuse_swiglu, void* stream);
+
+// Waits for `stream`, writes the give-up word of the static calls on the current device to *code
+// (0: all waits were served; 1, 3, 5: a producer's, a consumer's, the row factors' wait expired)
+// and clears it.  Allocates nothing.
+int dl_gemm_skinny_static_status(int* code, void* stream);
 
 #ifdef __cplusplus
 }

@@ -82,6 +82,19 @@ __device__ __forceinline__ void tc_tmem_load32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 8 consecutive float32 columns of this thread's lane of tensor memory (for epilogues written as
+// short loops: a block runs its epilogue once or twice, so straight-line code 32 columns wide is
+// paid for in instruction fetches).
+__device__ __forceinline__ void tc_tmem_load8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
 
 // Write 32 consecutive float32 columns of this thread's lane of tensor memory.
 __device__ __forceinline__ void tc_tmem_store32(uint32_t taddr, const float (&v)[32]) {

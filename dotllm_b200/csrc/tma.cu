@@ -1,6 +1,8 @@
 // Host side of the tensor-map helpers (see tma.cuh).
 #include "tma.cuh"
 #include "common.cuh"
+#include <mutex>
+#include <unordered_map>
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -46,5 +48,46 @@ int dl_tmap_encode_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, ui
                 (int)r, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)pitch_bytes, box_rows, box_cols);
         return -2;
     }
+    return 0;
+}
+
+namespace {
+struct MapKey {
+    const void* base;
+    unsigned long long rows, cols, pitch;
+    uint32_t box_rows, box_cols;
+    int swizzle;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows &&
+               box_cols == o.box_cols && swizzle == o.swizzle;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.base);
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.pitch;
+        h = h * 1000003u ^ ((size_t)k.box_rows << 20 | (size_t)k.box_cols << 4 | (size_t)k.swizzle);
+        return h;
+    }
+};
+}  // namespace
+
+int dl_tmap_cached_2d_bf16(CUtensorMap* out, const void* base, unsigned long long rows, unsigned long long cols,
+                           unsigned long long pitch_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+    static std::mutex maps_mutex;
+    std::lock_guard<std::mutex> lock(maps_mutex);
+    const MapKey key{base, rows, cols, pitch_bytes, box_rows, box_cols, swizzle};
+    auto it = maps.find(key);
+    if (it == maps.end()) {
+        CUtensorMap fresh;
+        const int rc = dl_tmap_encode_2d_bf16(&fresh, base, rows, cols, pitch_bytes, box_rows, box_cols, swizzle);
+        if (rc != 0) return rc;
+        if (maps.size() > 8192) maps.clear();
+        it = maps.emplace(key, fresh).first;
+    }
+    *out = it->second;
     return 0;
 }

@@ -22,6 +22,11 @@ enum DlTmapSwizzle { DL_TMAP_SWIZZLE_NONE = 0, DL_TMAP_SWIZZLE_128B = 1 };
 int dl_tmap_encode_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
                            uint32_t box_rows, uint32_t box_cols, int swizzle);
 
+// The same through a per-process table keyed by (base, shape, pitch, box, swizzle): encoding costs a
+// driver call, and a model's matrices and step buffers come back launch after launch.  Thread-safe.
+int dl_tmap_cached_2d_bf16(CUtensorMap* out, const void* base, unsigned long long rows, unsigned long long cols,
+                           unsigned long long pitch_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle);
+
 #ifdef __CUDACC__
 // Copy the box whose first element is (row, col) into shared memory; `bar` receives the bytes.
 __device__ __forceinline__ void dl_tma_load_2d(void* smem_dst, const CUtensorMap* map, int col, int row,
@@ -32,5 +37,14 @@ __device__ __forceinline__ void dl_tma_load_2d(void* smem_dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(col), "r"(row), "r"(mbar)
         : "memory");
+}
+// Copy `bytes` (a multiple of 16, both addresses 16-byte aligned) of contiguous global memory into
+// shared memory; `bar` receives the bytes.
+__device__ __forceinline__ void dl_bulk_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const uint32_t mbar = (uint32_t)__cvta_generic_to_shared(bar);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(mbar)
+                 : "memory");
 }
 #endif

@@ -164,7 +164,7 @@ class DecodeGraphs:
                 raise StepError(f"entry {i}: token id {e.tokens[0]} is outside the vocabulary")
         tokens = None if device_tokens else [int(e.tokens[0]) for e in entries]
         cap = self.captured.get(b)
-        if cap is not None and self._staged(cap, seqs):
+        if cap is not None and self._staged(cap, seqs, cache.kv_groups):
             # the step before this one already reserved the pages and sent everything but the tokens
             if tokens is not None:
                 cap.stage(seqs, tokens, cache.kv_groups, metadata=False)
@@ -190,11 +190,17 @@ class DecodeGraphs:
         return cap.logits
 
     @staticmethod
-    def _staged(cap, seqs):
-        """Is the device already set up for exactly these sequences at their present lengths?"""
+    def _staged(cap, seqs, kv_groups):
+        """Is the device already set up for exactly these sequences at their present lengths, on the
+        pages they hold now?  (A sequence that was truncated and has grown back to the staged length
+        may hold other pages than the tables sent ahead name.)"""
         ahead = cap.staged_for
-        return (ahead is not None and len(ahead[0]) == len(seqs)
-                and all(a is s and n == s.length for a, n, s in zip(ahead[0], ahead[1], seqs)))
+        if ahead is None or len(ahead[0]) != len(seqs):
+            return False
+        if not all(a is s and n == s.length for a, n, s in zip(ahead[0], ahead[1], seqs)):
+            return False
+        return all(cap.table_rows[gi][r] == s.pages[g.index]
+                   for gi, g in enumerate(kv_groups) for r, s in enumerate(seqs))
 
     def _stage_ahead(self, cap, seqs):
         """While the device works on this step, send the next step's positions, lengths, slots and

@@ -62,6 +62,7 @@ def _pair_counters(device):
     key = device.index
     if key not in _counters:
         _counters[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        _library.register_counters(_counters[key])
     return _counters[key]
 
 

@@ -1,8 +1,10 @@
-"""Dispatch to the weight-streaming product for steps of a few rows (decode).
+"""Dispatch to the weight-streaming products for steps of a few rows (decode).
 
-The kernel cuts its work into equal shares per warp; tiles that straddle two shares are summed
-through a scratch buffer with arrival counters.  Both are kept here per device (they are small
-and every launch leaves the counters zero).  Launches that share them must be on one stream.
+Up to 16 rows go to the mma.sync kernel of csrc/gemm_skinny.cu, 17 to 128 rows to the tcgen05 kernel
+of csrc/gemm_decode_tc.cu (``gemm_decode_tc.run``, same contract).  The first cuts its work into
+equal shares per warp; tiles that straddle two shares are summed through a scratch buffer with
+arrival counters.  Both are kept here per device (they are small and every launch leaves the
+counters zero).  Launches that share them must be on one stream.
 """
 from __future__ import annotations
 
@@ -20,7 +22,13 @@ _library.register_signatures({
     "dl_gemm_skinny_scratch": [_I, _I, _I, _I, _I, _P, _P],
 })
 
-MAX_ROWS = 16            # rows the kernel takes; beyond this the library product is used
+SKINNY_ROWS = 16         # rows the mma.sync kernel takes; more go to the tcgen05 kernel
+MAX_ROWS = 128           # rows the two kernels take between them; beyond this the products are prefill products
+# Of 17 to 128 rows the gated product goes to the tcgen05 kernel (47 us against 56 for the library product plus
+# gating at the 8B shape and 64 rows).  The plain products do too when TC_PLAIN is set; measured inside a decode
+# step the library's are about 7 us a product faster at those sizes, so they stay with the library.
+TC_PLAIN = False
+SUM_STRIDE = 16          # floats between the sums of squares of two 16-column tiles (mma.sync kernel)
 _MAX_TILES = 1 << 16
 _state = {}
 
@@ -30,13 +38,23 @@ def _device_state(device):
     if key not in _state:
         sms = _library.library().dl_sm_count()
         counters = torch.zeros(_MAX_TILES, dtype=torch.int32, device=device)
+        _library.register_counters(counters)
         partials = torch.empty(max(sms, 1) * 6 * 2 * 2 * 128, dtype=torch.float32, device=device)
         _state[key] = (counters, partials, sms)
     return _state[key]
 
 
+def sum_stride(rows):
+    """Floats between two parts of the sums of squares that a product of ``rows`` rows leaves."""
+    from . import gemm_decode_tc
+    return SUM_STRIDE if rows <= SKINNY_ROWS else gemm_decode_tc.SUM_STRIDE
+
+
 def takes(x, w, fuse_swiglu=False, max_rows=None):
     M, K = x.shape
+    if M > SKINNY_ROWS:
+        from . import gemm_decode_tc
+        return (fuse_swiglu or TC_PLAIN) and M <= (max_rows or MAX_ROWS) and gemm_decode_tc.takes(x, w, fuse_swiglu)
     n_out = w.shape[0] // 2 if fuse_swiglu else w.shape[0]
     tiles = (n_out + 7) // 8 if fuse_swiglu else (n_out + 15) // 16
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -47,10 +65,14 @@ def takes(x, w, fuse_swiglu=False, max_rows=None):
 
 def run(x, w, out_dtype, fuse_swiglu=False, resident=False, row_sums=None, into=None):
     """``row_sums`` = (sums float32 [parts * 16], parts, width, eps): x is a stream times a norm's gain,
-    and every output row is multiplied by rsqrt(sum of the row's parts / width + eps).
+    and every output row is multiplied by rsqrt(sum of the row's parts / width + eps); the sums must come
+    from a product of the same number of rows (``sum_stride``).
     ``into`` = (stream float32 [M, N], gain float32 [N]): the product is added into the stream in place;
     returns (stream * gain as bfloat16 [M, N], sums of squares float32 [ceil(N / 16) * 16])."""
     M, K = x.shape
+    if M > SKINNY_ROWS:
+        from . import gemm_decode_tc
+        return gemm_decode_tc.run(x, w, out_dtype, fuse_swiglu, resident, row_sums, into)
     n_out = w.shape[0] // 2 if fuse_swiglu else w.shape[0]
     counters, partials, sms = _device_state(x.device)
     x_stride = x.stride(0) if M > 1 else max(K, x.stride(0))

@@ -63,6 +63,10 @@ def library():
         lib.dl_sm_count.restype = ctypes.c_int
         lib.dl_set_dependent_launch.restype = ctypes.c_int
         lib.dl_set_dependent_launch.argtypes = [ctypes.c_int]
+        # Library products (cuBLAS through torch, used for bfloat16 prompts of more than 128 rows) must
+        # accumulate and reduce in float32 like the kernels here: no bfloat16 split-k reductions.
+        import torch
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         _lib = lib
         return lib
 
@@ -105,9 +109,17 @@ def call(name, *args):
 
 
 _status = {}
+_counters = []
 _STATUS_TEXT = {1: "a producer's wait for a free shared-memory stage expired",
                 2: "a block table named a page outside the pool",
                 3: "a consumer's wait for a bulk copy expired"}
+
+
+def register_counters(tensor):
+    """Arrival counters that kernels share between launches and leave zero.  A launch that gave up on
+    a bounded wait may leave some of them counted; ``check_status`` clears them with the status word
+    so that the launches after the error start from the state they expect."""
+    _counters.append(tensor)
 
 
 def status_word(device):
@@ -125,4 +137,7 @@ def check_status():
         code = int(word.item())
         if code:
             word.zero_()
+            for counters in _counters:
+                if counters.device.index == key:
+                    counters.zero_()
             raise KernelError(f"a kernel on cuda:{key} gave up: {_STATUS_TEXT.get(code, code)}")

@@ -101,6 +101,8 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--width", type=int, default=4096)
     ap.add_argument("--gated", action="store_true")
+    ap.add_argument("--skinny-rows", type=int, default=None,
+                    help="gemm_skinny: most rows that go to the mma.sync kernel (more go to the tcgen05 one)")
     ap.add_argument("--out-f32", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
@@ -185,6 +187,8 @@ def main(argv=None):
                       frac_of_bf16_peak=flops / ms / 1e9 / tflops)
     elif args.kernel == "gemm_skinny":
         M, N, K = args.rows, args.n, args.k
+        if args.skinny_rows is not None:
+            gemm_skinny.SKINNY_ROWS = args.skinny_rows
         x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         w = torch.randn((2 if args.gated else 1) * N, K, device=dev, dtype=torch.bfloat16) * 0.02
         out_dtype = torch.float32 if args.out_f32 else torch.bfloat16

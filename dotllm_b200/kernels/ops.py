@@ -85,7 +85,7 @@ class PendingProduct:
 
 class ScaledRows:
     """A normalised stream still lacking its factor per row: ``data`` = stream * gain (bfloat16) and the
-    sums of squares per 16-column part, left by the product that added into the stream.  ``linear``
+    sums of squares per part of 16 (up to 16 rows) or 128 columns, left by the product that added into the stream.  ``linear``
     and ``gated_linear`` take it as x and apply rsqrt(mean + eps) to their output rows - the product
     of the normalised rows, since the factor is one number per row.  ``tensor()`` gives the
     normalised rows themselves (valid until the stream is added to again)."""
@@ -96,7 +96,8 @@ class ScaledRows:
         self.shape, self.dtype = data.shape, data.dtype
 
     def row_sums(self):
-        return self.sums, self.sums.numel() // 16, self.width, self.eps
+        from . import gemm_skinny
+        return self.sums, self.sums.numel() // gemm_skinny.sum_stride(self.data.shape[0]), self.width, self.eps
 
     def tensor(self):
         return add_rmsnorm(self.stream, None, self.gain, self.eps, self.data.dtype)

@@ -289,3 +289,39 @@ def test_graph_steps_staged_ahead_follow_what_the_caller_does(tmp):
 
     eager, graphed = run(False), run(True)
     assert torch.equal(eager, graphed), f"max diff {(eager - graphed).abs().max()}"
+
+
+def test_graph_step_after_pages_changed_at_the_same_length(tmp):
+    """Two sequences are truncated by more than a page and grown back, by an eager step, to the very
+    length for which the graph's tables were sent ahead.  The cache hands out the most recently freed
+    page first, so the two sequences come back holding each other's old pages: a graph step that
+    trusted the tables sent ahead would write into, and read from, the other sequence's page."""
+    from dotllm_b200 import StepEntry
+    model, cfg, _, _ = load_pair(tmp, "A", torch.float32)
+    vocab = cfg["vocab_size"]
+    prompts = [tiny_models.random_tokens(70, vocab, seed=700 + i) for i in range(2)]
+    feed = [tiny_models.random_tokens(80, vocab, seed=710 + i) for i in range(2)]
+
+    def run(graphs):
+        cache = model.new_cache(max_tokens=512)
+        seqs = [cache.open_sequence() for _ in prompts]
+        outs = [model.step(cache, [StepEntry(s, p, [len(p) - 1]) for s, p in zip(seqs, prompts)])]
+        one = lambda t, g: model.step(cache, [StepEntry(s, [f[t]]) for s, f in zip(seqs, feed)], graphs=g).clone()
+        for t in range(3):
+            outs.append(one(t, graphs))                     # lengths 73; the step for 73 -> 74 is sent ahead
+        before = [list(s.pages[0]) for s in seqs]
+        for s in seqs:
+            cache.truncate(s, 3)                            # gives back the second page of each
+        regrow = [p[3:] + f[:3] for p, f in zip(prompts, feed)]
+        outs.append(model.step(cache, [StepEntry(s, r) for s, r in zip(seqs, regrow)]))     # eager, back to 73
+        assert [s.length for s in seqs] == [73, 73]
+        assert [list(s.pages[0]) for s in seqs] != before   # the point of the test: other pages, same lengths
+        for t in range(3, 6):
+            outs.append(one(t, graphs))
+        cache.check()
+        for s in seqs:
+            cache.close_sequence(s)
+        return torch.cat(outs).clone()
+
+    eager, graphed = run(False), run(True)
+    assert torch.equal(eager, graphed), f"max diff {(eager - graphed).abs().max()}"

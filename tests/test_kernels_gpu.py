@@ -387,15 +387,17 @@ def test_gemm_skinny_repeats_with_full_rings():
         assert torch.equal(gemm_skinny.run(x, w, torch.float32), first)
 
 
-@pytest.mark.parametrize("M,H,K,N2", [(8, 4096, 512, 1024), (1, 1000, 384, 272), (13, 1000, 384, 272), (16, 72, 64, 40)])
-def test_products_that_add_and_normalise(M, H, K, N2):
+@pytest.mark.parametrize("M,H,K,N2", [(8, 4096, 512, 1024), (1, 1000, 384, 272), (13, 1000, 384, 272), (16, 72, 64, 40),
+                                      (17, 1000, 384, 272), (64, 4096, 512, 1024), (100, 1000, 4096, 272), (128, 72, 64, 40)])
+def test_products_that_add_and_normalise(M, H, K, N2, monkeypatch):
     """A decode step's add + RMSNorm done by the two products around it: the first adds its result
-    into the float32 stream and leaves stream * gain with sums of squares per 16 columns, the second
+    into the float32 stream and leaves stream * gain with sums of squares per 16 columns (per 128 with more than 16 rows), the second
     multiplies its output rows by rsqrt(mean + eps).  The stream must come out with the bits of the
     separate kernels; the second product is compared with the product of the normalised rows, for a
     plain and a gated product, at widths that are no multiple of 16."""
     o = ops()
-    from dotllm_b200.kernels import library
+    from dotllm_b200.kernels import gemm_skinny, library
+    monkeypatch.setattr(gemm_skinny, "TC_PLAIN", True)     # above 16 rows the plain products are the library's unless asked
     g = torch.Generator().manual_seed(60)
     a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
     w1 = (torch.randn(H, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
@@ -421,7 +423,9 @@ def test_products_that_add_and_normalise(M, H, K, N2):
     chained = o.add_rmsnorm(stream, o.linear(rows, zero, out_dtype=torch.float32, lazy=True), gain, eps, torch.bfloat16,
                             lazy=True)                    # scaled rows in, stream out: both fusions in one launch
     assert isinstance(chained, o.ScaledRows) and torch.equal(stream, plain_stream)     # a zero matrix adds nothing
-    assert torch.equal(chained.data, rows.data) and torch.equal(chained.sums[:M], rows.sums[:M])
+    stride = rows.sums.numel() // rows.row_sums()[1]      # floats between two parts of the sums
+    assert torch.equal(chained.data, rows.data)
+    assert torch.equal(chained.sums.view(-1, stride)[:, :M], rows.sums.view(-1, stride)[:, :M])
     library.check_status()
     # what the rows stand for
     h = plain_stream.double().cpu()
@@ -439,11 +443,115 @@ def test_products_that_add_and_normalise(M, H, K, N2):
     # |d silu| <= 1.1; the output is rounded to bfloat16 once more
     slack = 1.1 * e_gate * (up.abs() + e_up) + (gate * torch.sigmoid(gate)).abs() * e_up + 2 ** -8 * want.abs() + 1e-5
     assert bool(((yg.double().cpu() - want).abs() <= slack).all())
-    # the same bits whatever else is in the batch: row 0 alone
-    if M > 1:
-        s1 = stream0[:1].clone()
-        r1 = o.add_rmsnorm(s1, o.linear(a[:1], w1, out_dtype=torch.float32, lazy=True), gain, eps, torch.bfloat16, lazy=True)
-        assert torch.equal(s1, stream[:1]) and torch.equal(o.linear(r1, w2, out_dtype=torch.float32), y[:1])
+    # the same bits whatever else is in the batch: the first row alone (the first 17 where the
+    # tcgen05 product runs, which takes 17 rows or more)
+    sub = 1 if M <= 16 else 17
+    if M > sub:
+        s1 = stream0[:sub].clone()
+        r1 = o.add_rmsnorm(s1, o.linear(a[:sub], w1, out_dtype=torch.float32, lazy=True), gain, eps, torch.bfloat16, lazy=True)
+        assert torch.equal(s1, stream[:sub]) and torch.equal(o.linear(r1, w2, out_dtype=torch.float32), y[:sub])
+
+
+def test_counters_are_cleared_with_the_status_word():
+    """A launch that gives up on a bounded wait may leave arrival counters counted.  ``check_status``
+    raises once and clears them with the status word, so the products after the error are right
+    again.  The failure is planted on the host: a status code and counters as an aborted launch
+    could have left them."""
+    from dotllm_b200.errors import KernelError
+    from dotllm_b200.kernels import gemm_decode_tc, gemm_skinny, library
+    g = torch.Generator().manual_seed(29)
+    w = (torch.randn(4096, 4096, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    x = torch.randn(64, 4096, generator=g).to(torch.bfloat16).to(DEV)
+    want8, want64 = gemm_skinny.run(x[:8], w, torch.float32), gemm_skinny.run(x, w, torch.float32)
+    library.check_status()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gemm_skinny._device_state(dev)[0][:256] = 1             # as if some tiles' first parts had arrived and nothing merged them
+    gemm_decode_tc._device_state(dev)[0][:32] = 1
+    library.status_word(dev).fill_(3)
+    with pytest.raises(KernelError):
+        library.check_status()
+    assert torch.equal(gemm_skinny.run(x[:8], w, torch.float32), want8)
+    assert torch.equal(gemm_skinny.run(x, w, torch.float32), want64)
+    library.check_status()
+
+
+@pytest.mark.parametrize("M", [17, 33, 64, 65, 128])
+@pytest.mark.parametrize("N,K", [(64, 64), (200, 176), (1000, 320), (4096, 4096), (6144, 512), (130, 14336)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_decode_tc(M, N, K, out_dtype):
+    """The tcgen05 weight-streaming product (17 to 128 rows) against a float64 product, at sizes off its
+    128 x 64 tile grid and with tiles cut between blocks (4096 x 4096: 2048 units on 148 blocks; 130 x
+    14336: two tiles of 224 chunks each)."""
+    from dotllm_b200.kernels import gemm_decode_tc, gemm_skinny, library
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    xd, wd = x.to(DEV), w.to(DEV)
+    assert gemm_decode_tc.takes(xd, wd)
+    y = gemm_skinny.run(xd, wd, out_dtype)                  # dispatches on the number of rows
+    library.check_status()
+    ref = (x.double() @ w.double().T).float()
+    close(y, ref, 2e-4 * math.sqrt(K / 64), 2 ** -8 if out_dtype == torch.bfloat16 else 1e-5)
+    # a row's result does not depend on the other rows in the call (17 rows: another padded width)
+    y17 = gemm_decode_tc.run(xd[:17].contiguous(), wd, out_dtype)
+    assert torch.equal(y17, y[:17])
+    # a second call gives the same bits (the merge order of cut tiles is fixed, the counters are left zero)
+    assert torch.equal(gemm_skinny.run(xd, wd, out_dtype), y)
+    # rows of a wider buffer, and a product that reads its weights early
+    wide = torch.zeros(M, K + 8, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = xd
+    assert torch.equal(gemm_skinny.run(wide[:, :K], wd, out_dtype, resident=True), y)
+    library.check_status()
+
+
+@pytest.mark.parametrize("M", [17, 40, 64, 100, 128])
+@pytest.mark.parametrize("I,K", [(176, 64), (512, 192), (720, 320), (14336, 256), (1000, 4096)])
+def test_gemm_decode_tc_gated(M, I, K):
+    from dotllm_b200.kernels import gemm_decode_tc, library
+    g = torch.Generator().manual_seed(23)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, generator=g) * 0.1).to(torch.bfloat16)
+    gu = x.double() @ w.double().T
+    ref = plain_llama.swiglu(gu[:, :I].float(), gu[:, I:].float())
+    y = gemm_decode_tc.run(x.to(DEV), w.to(DEV), torch.bfloat16, fuse_swiglu=True)
+    library.check_status()
+    assert y.shape == (M, I)
+    close(y, ref, 2e-4 * math.sqrt(K / 64), 2 ** -8)
+    assert torch.equal(gemm_decode_tc.run(x.to(DEV), w.to(DEV), torch.bfloat16, fuse_swiglu=True), y)
+    assert torch.equal(ops().gated_linear(x.to(DEV), w.to(DEV)), y)
+
+
+@pytest.mark.parametrize("M", [1, 8, 16])
+@pytest.mark.parametrize("N,K", [(200, 176), (4096, 4096)])
+def test_gemm_decode_tc_few_rows(M, N, K):
+    """The tcgen05 product also takes 1 to 16 rows (padded to 16 tokens), though the dispatcher gives
+    those to the mma.sync kernel."""
+    from dotllm_b200.kernels import gemm_decode_tc, library
+    g = torch.Generator().manual_seed(24)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    y = gemm_decode_tc.run(x.to(DEV), w.to(DEV), torch.float32)
+    library.check_status()
+    close(y, (x.double() @ w.double().T).float(), 2e-4 * math.sqrt(K / 64), 1e-5)
+
+
+def test_gemm_decode_tc_repeats():
+    """128 rows of 4096 x 4096 and 64 rows of the widest gated tile, thirty launches each: the same
+    bits every time (a stage released before its MMAs have read it, or an accumulator buffer handed
+    back too early, shows up as a few wrong outputs)."""
+    from dotllm_b200.kernels import gemm_decode_tc, library
+    g = torch.Generator().manual_seed(28)
+    x = torch.randn(128, 4096, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(4096, 4096, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    first = gemm_decode_tc.run(x, w, torch.float32)
+    close(first, (x.double() @ w.double().T).float(), 2e-4 * 8, 1e-5)
+    for _ in range(30):
+        assert torch.equal(gemm_decode_tc.run(x, w, torch.float32, resident=True), first)
+    wg = (torch.randn(2 * 2048, 4096, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    first = gemm_decode_tc.run(x[:64], wg, torch.bfloat16, fuse_swiglu=True)
+    for _ in range(30):
+        assert torch.equal(gemm_decode_tc.run(x[:64], wg, torch.bfloat16, fuse_swiglu=True, resident=True), first)
+    library.check_status()
 
 
 @pytest.mark.parametrize("M,N,K", [(17, 64, 64), (128, 256, 64), (129, 257, 72), (300, 1000, 320), (2048, 384, 192),
