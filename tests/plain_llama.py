@@ -6,9 +6,12 @@ file with its own few lines, and computes every part with elementary torch
 operations on the CPU in float32 (tables in float64).
 
 It rests on the formulas of kkokosa/dotLLM's scalar reference kernels; the
-reference is C#/.NET and cannot be compiled or imported here, so there is no
-numerical cross-check against its binaries.  Every function names the
-reference lines that it restates.  The reference applies no RoPE frequency
+reference's model code is C#/.NET and cannot be compiled or imported here.
+What can be compiled are its FP32 CUDA kernels for every part that is not a
+matrix product: tests/golden/reference_kernels.py runs them unmodified, their
+outputs are committed beside it, and tests/test_plain_llama.py holds the
+functions below to those outputs (norm, rotation, attention, gating, add,
+lookup).  Every function names the reference lines that it restates.  The reference applies no RoPE frequency
 rescaling (src/DotLLM.Cpu/Kernels/RoPE.md:303); the ``llama3`` rescaling below
 follows the rule published with the Llama 3.1 checkpoints' ``rope_scaling``
 block and has no reference counterpart.

@@ -130,3 +130,18 @@ def test_samplers():
     lg = torch.log(probs)
     assert [P.categorical(lg, r) for r in (0.0, 0.49, 0.51, 0.79, 0.81, 0.96)] == [0, 0, 1, 1, 2, 3]
     assert P.sample(lg, [], temperature=1.0, top_k=1, r=0.99) == 0
+
+
+def test_parts_agree_with_the_reference_kernels_outputs():
+    """kkokosa/dotLLM's own FP32 CUDA kernels (rmsnorm_f32, rope_f32 with the half-split pairing,
+    attention_f32 at a position offset, swiglu_f32, add_f32, embedding_lookup_f32_f32out), compiled
+    unmodified and run once on a B200: their outputs are committed in tests/golden/ with the script
+    that made them.  The plain implementation's functions must reproduce them."""
+    from golden import reference_kernels as rk
+    golden = rk.load_golden()
+    c = {k: golden[k] for k in rk.cases()}
+    for name, value in rk.cases().items():                   # the inputs are the seeded ones of the script
+        assert torch.equal(value, c[name]), name
+    errs = rk.compare_with_plain(c, golden, P)
+    for part, err in errs.items():
+        assert err <= rk.BOUNDS[part], f"{part}: differs from the reference kernel's output by {err:.3e}"
