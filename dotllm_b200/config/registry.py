@@ -79,7 +79,33 @@ def load_config(folder):
         data = json.loads(path.read_text())
     except json.JSONDecodeError as exc:
         raise ConfigError(f"{path}: not valid JSON ({exc})") from exc
-    return config_from_dict(data)
+    return config_from_dict(merge_generation_config(data, Path(folder) / "generation_config.json"))
+
+
+def merge_generation_config(data, path):
+    """``generation_config.json``, where a folder has one, names the tokens that end generation
+    (Llama 3 checkpoints list several there and one in config.json): its ``eos_token_id`` entries come
+    first, config.json's follow, duplicates dropped; its ``bos_token_id`` fills a missing one.  The
+    reference takes both ids from the tokenizer (src/DotLLM.Tokenizers/ITokenizer.cs:38-41)."""
+    if not path.is_file():
+        return data
+    try:
+        gen = json.loads(path.read_text())
+    except json.JSONDecodeError as exc:
+        raise ConfigError(f"{path}: not valid JSON ({exc})") from exc
+    if not isinstance(gen, dict):
+        raise ConfigError(f"{path} must hold a JSON object")
+    as_list = lambda v: [] if v is None else (list(v) if isinstance(v, (list, tuple)) else [v])
+    merged = []
+    for token in as_list(gen.get("eos_token_id")) + as_list(data.get("eos_token_id")):
+        if token not in merged:
+            merged.append(token)
+    out = dict(data)
+    if merged:
+        out["eos_token_id"] = merged
+    if out.get("bos_token_id") is None and gen.get("bos_token_id") is not None:
+        out["bos_token_id"] = gen["bos_token_id"]
+    return out
 
 
 def build_spec(config) -> ModelSpec:

@@ -7,8 +7,7 @@
     python -m dotllm_b200.kernels.microbench rope --rows 8
 
 Prints one JSON line with the time, the algorithmic bytes or FLOPs, and the fraction of the
-measured peak.  The same command under ``ncu -k regex:<kernel>`` gives the counters for the
-summaries in profiles/.
+measured peak.  The same command under ``ncu -k regex:<kernel>`` gives the kernel's counters.
 """
 from __future__ import annotations
 

@@ -83,8 +83,11 @@ class Model:
         return model
 
     @classmethod
-    def random(cls, config, seed=0, dtype="bfloat16", device="cuda", on_device=True, spec=None):
-        """Random weights drawn in memory from (config, seed); nothing is written."""
+    def random(cls, config, seed=0, dtype="bfloat16", device="cuda", on_device=False, spec=None):
+        """Random weights drawn in memory from (config, seed); nothing is written.  The numbers are those
+        that ``write_random_model(folder, config, seed)`` stores, so a model made here and one loaded
+        from such a folder are the same model.  ``on_device=True`` draws with the device's generator
+        instead: another stream of numbers, seconds instead of minutes for a model of many gigabytes."""
         model = cls._skeleton(config, dtype, device, spec)
         init_random(model.decoder, seed, on_device=on_device)
         return model

@@ -188,8 +188,10 @@ class SamplerPipeline:
 def sample_rows(logits, pipelines, generated, sequence_indices, steps):
     """One token for every row of ``logits`` (float32 [R, V] on the device).
 
-    ``pipelines[r]``, ``generated[r]`` (ids generated so far by row r's request),
-    ``sequence_indices[r]`` and ``steps[r]`` (how many tokens it has generated) belong to row r.
+    ``pipelines[r]``, ``generated[r]`` (ids generated so far by row r's request) and ``steps[r]``
+    (how many tokens it has generated) belong to row r.  A row's draw depends on its request's seed
+    and step only: ``sequence_indices`` (the request's place in the caller's list) plays no part, so
+    the same request gives the same tokens alone, in any batch, at any place in it.
     Returns an int32 device tensor [R]."""
     rows = logits.shape[0]
     device = logits.device
@@ -216,7 +218,7 @@ def sample_rows(logits, pipelines, generated, sequence_indices, steps):
     fl = torch.tensor([[p.row_temperature() for p in pipelines],
                        [p.top_p for p in pipelines],
                        [p.min_p for p in pipelines],
-                       [uniform(p.seed, s, n) for p, s, n in zip(pipelines, sequence_indices, steps)]],
+                       [uniform(p.seed, n) for p, n in zip(pipelines, steps)]],
                       dtype=torch.float32).to(device)
     top_k = torch.tensor([p.top_k for p in pipelines], dtype=torch.int32).to(device)
     return ops.sample(logits, temperature=fl[0].contiguous(), top_k=top_k, top_p=fl[1].contiguous(),

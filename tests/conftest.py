@@ -32,3 +32,14 @@ def cpu_kernels(monkeypatch):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
     # ops.rope_cache_attention composes the two patched functions above for anything but CUDA bfloat16
     return kernel_refs
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The worst logit errors the parity tests saw, next to the bounds they were held to."""
+    try:
+        import engine_checks
+    except ImportError:
+        return
+    for dtype, (rel_max, rel_rms, abs_max) in engine_checks.OBSERVED.items():
+        terminalreporter.write_line(f"observed {dtype}: max |diff| {abs_max:.3e}, max |diff| / row rms {rel_max:.3e}, "
+                                    f"row rms error / row rms {rel_rms:.3e}")

@@ -7,11 +7,16 @@ import torch
 import plain_llama
 import tiny_models
 
-# Bounds on |engine logit - plain logit|.  Logits of the tiny models are O(1).
+# Bounds on |engine logit - plain logit| for the tiny models, whose logit rows have an rms of 0.2 to 0.5.
 # float32: both sides compute in float32 and differ in summation order only.
 # bfloat16: both sides read the same bfloat16 weights; the engine rounds activations to
-# bfloat16 (8 significand bits, relative step 2^-8) between parts.
-TOL = {torch.float32: 2e-5, torch.bfloat16: 4e-2}
+# bfloat16 (8 significand bits) between parts.
+# The worst values seen over the whole suite on a B200 (printed at the end of every GPU run) are
+# 3.0e-6 and 1.2e-2; the bounds are about three times that.  REL_RMS bounds a row's rms error over the
+# row's rms (seen: 1.8e-6 and 6.5e-3).  A greedy token is accepted when it is the plain arg-max or lies
+# within TOL of it (each of the two logits may be off by half of that).
+TOL = {torch.float32: 1e-5, torch.bfloat16: 3e-2}
+REL_RMS = {torch.float32: 6e-6, torch.bfloat16: 1.5e-2}
 
 
 def load_pair(tmp_path, which, dtype, seed=0):
@@ -23,18 +28,46 @@ def load_pair(tmp_path, which, dtype, seed=0):
     return Model.load(folder, dtype=dtype), cfg, weights, folder
 
 
+# Worst errors seen by assert_close in this session, per dtype: (max |diff| / rms of the reference
+# row, relative rms error of a row, max |diff|).  Printed at the end of a GPU run (conftest.py).
+OBSERVED = {}
+
+
+def _record(got, want, dtype):
+    g, w = got.float().cpu().reshape(-1, got.shape[-1]), want.float().cpu().reshape(-1, want.shape[-1])
+    rms = w.pow(2).mean(dim=-1).sqrt().clamp_min(1e-30)
+    d = (g - w)
+    seen = OBSERVED.setdefault(dtype, [0.0, 0.0, 0.0])
+    seen[0] = max(seen[0], float((d.abs().amax(dim=-1) / rms).max()))
+    seen[1] = max(seen[1], float((d.pow(2).mean(dim=-1).sqrt() / rms).max()))
+    seen[2] = max(seen[2], float(d.abs().max()))
+
+
 def max_err(a, b):
     return float((a.float().cpu() - b.float().cpu()).abs().max())
 
 
 def assert_close(got, want, dtype, what=""):
     err = max_err(got, want)
+    _record(got, want, dtype)
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
     assert err <= TOL[dtype], f"{what}: max |diff| {err:.3e} > {TOL[dtype]:.1e}"
+    g, w = got.float().cpu().reshape(-1, got.shape[-1]), want.float().cpu().reshape(-1, want.shape[-1])
+    rel = float(((g - w).pow(2).mean(dim=-1).sqrt() / w.pow(2).mean(dim=-1).sqrt().clamp_min(1e-30)).max())
+    assert rel <= REL_RMS[dtype], f"{what}: rms error of a row is {rel:.3e} of the row's rms > {REL_RMS[dtype]:.1e}"
+
+
+def greedy_ok(row, token, dtype):
+    """Is ``token`` an acceptable greedy choice for the plain logits ``row``: the arg-max, or within
+    the bound of it (which can only be when the plain top two are closer than the bound)."""
+    return int(row.argmax()) == int(token) or float(row.max() - row[token]) <= TOL[dtype]
 
 
 def first_wrong(got, want, dtype):
     """Index of the first row beyond tolerance (to report where a cut goes wrong)."""
+    _record(got, want, dtype)
     err = (got.float().cpu() - want.float().cpu()).abs().amax(dim=-1)
-    bad = (err > TOL[dtype]).nonzero()
+    g, w = got.float().cpu().reshape(-1, got.shape[-1]), want.float().cpu().reshape(-1, want.shape[-1])
+    rel = (g - w).pow(2).mean(dim=-1).sqrt() / w.pow(2).mean(dim=-1).sqrt().clamp_min(1e-30)
+    bad = ((err.reshape(-1) > TOL[dtype]) | (rel > REL_RMS[dtype])).nonzero()
     return None if bad.numel() == 0 else int(bad[0])

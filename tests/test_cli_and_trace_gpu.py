@@ -10,7 +10,7 @@ import torch
 
 import plain_llama
 import tiny_models
-from engine_checks import TOL
+from engine_checks import TOL, greedy_ok
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -31,7 +31,7 @@ def read(out_dir, step, vocab):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "D"])
 def test_trace_run_whole_tail_and_batches(tmp_path, which, dtype):
     tdtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     folder = tiny_models.make_folder(tmp_path, which, seed=4, dtype=tdtype)
@@ -124,7 +124,7 @@ def test_run_command_json(tmp_path):
         ref = plain_llama.forward(cfg, weights, prompt + r["generated_token_ids"])
         for i, tok in enumerate(r["generated_token_ids"]):
             row = ref[len(prompt) - 1 + i]
-            assert float(row.max() - row[tok]) <= 2 * TOL[torch.bfloat16]
+            assert greedy_ok(row, tok, torch.bfloat16), (i, tok, int(row.argmax()))
     sampled = subprocess.run([sys.executable, "-m", "dotllm_b200", "run", str(folder), "-p", "1,2,3", "-n", "8",
                               "-t", "0.8", "--top-k", "20", "--top-p", "0.9", "--min-p", "0.02",
                               "--repeat-penalty", "1.1", "--repeat-last-n", "4", "-s", "7", "--json"],

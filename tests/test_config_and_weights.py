@@ -195,3 +195,44 @@ def test_random_weights_are_reproducible_and_as_declared(tmp_path):
 def test_check_names_and_shapes_passes_when_all_is_well():
     from dotllm_b200.parts.base import WeightSpec
     check_names_and_shapes({"w": (2, 3), "extra": (1,)}, {"w": WeightSpec((2, 3))}, optional={"extra"})
+
+
+def test_generation_config_names_the_stop_tokens(tmp_path):
+    folder = tiny_models.make_folder(tmp_path, "A")                     # config.json: eos 2, bos 1
+    assert load_config(folder).eos_token_id == (2,)
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": [9, 2, 11], "bos_token_id": 5}))
+    cfg = load_config(folder)
+    assert cfg.eos_token_id == (9, 2, 11) and cfg.bos_token_id == 1     # its ids first, duplicates dropped; bos was given
+    assert build_spec(cfg).stop_token_ids == (9, 2, 11)
+    b = tiny_models.make_folder(tmp_path, "C")                          # no ids in config.json
+    (b / "generation_config.json").write_text(json.dumps({"eos_token_id": 7, "bos_token_id": 3}))
+    cfg = load_config(b)
+    assert cfg.eos_token_id == (7,) and cfg.bos_token_id == 3
+    (b / "generation_config.json").write_text("[1, 2")
+    with pytest.raises(ConfigError, match="generation_config.json"):
+        load_config(b)
+
+
+def test_a_checkpoint_in_two_shards_loads_like_one_file(tmp_path):
+    folder = tiny_models.make_folder(tmp_path, "B")
+    whole = load_into(DecoderModel(build_spec(load_config(folder)), CPU), folder)
+    with SafetensorsFile(folder / "model.safetensors") as f:
+        tensors = {n: f.tensor(n).clone() for n in f.names()}
+    names = sorted(tensors)
+    first, second = names[:len(names) // 2], names[len(names) // 2:]
+    save_safetensors(folder / "model-00001-of-00002.safetensors", {n: tensors[n] for n in first})
+    save_safetensors(folder / "model-00002-of-00002.safetensors", {n: tensors[n] for n in second})
+    index = {"metadata": {}, "weight_map": {**{n: "model-00001-of-00002.safetensors" for n in first},
+                                            **{n: "model-00002-of-00002.safetensors" for n in second}}}
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    (folder / "model.safetensors").unlink()
+    sharded = load_into(DecoderModel(build_spec(load_config(folder)), CPU), folder)
+    for (_, a), (_, b) in zip(whole.named_parts(), sharded.named_parts()):
+        for name, value in vars(a).items():
+            if isinstance(value, torch.Tensor):
+                assert torch.equal(value, getattr(b, name)), name
+    # a tensor that the second shard lacks is reported by name, as for a single file
+    save_safetensors(folder / "model-00002-of-00002.safetensors", {n: tensors[n] for n in second[1:]})
+    with pytest.raises(WeightsError) as info:
+        load_into(DecoderModel(build_spec(load_config(folder)), CPU), folder)
+    assert info.value.missing == [second[0]]

@@ -6,7 +6,7 @@ import torch
 
 import plain_llama
 import tiny_models
-from engine_checks import TOL, assert_close, first_wrong, load_pair
+from engine_checks import TOL, assert_close, first_wrong, greedy_ok, load_pair
 
 pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
@@ -14,7 +14,7 @@ DTYPES = [torch.float32, torch.bfloat16]
 
 def requests_for(which, cfg):
     lens = {"A": [5, 11, 17, 100, 64, 65, 128], "B": [1, 9, 33, 70, 200, 256, 63],
-            "C": [300, 40, 129, 7, 1000]}[which]
+            "C": [300, 40, 129, 7, 1000], "D": [260, 33, 129, 1, 700]}[which]
     return [tiny_models.random_tokens(n, cfg["vocab_size"], seed=100 + i) for i, n in enumerate(lens)]
 
 
@@ -24,7 +24,7 @@ def tmp(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 def test_whole_tail_and_batched(tmp, which, dtype):
     from dotllm_b200 import StepEntry
     model, cfg, weights, _ = load_pair(tmp, which, dtype)
@@ -186,7 +186,7 @@ def test_greedy_generation_through_the_entry_point(tmp, which, dtype):
         ref = plain_llama.forward(cfg, weights, p + o.generated_token_ids)
         for i, tok in enumerate(o.generated_token_ids):
             row = ref[len(p) - 1 + i]
-            assert float(row.max() - row[tok]) <= 2 * TOL[dtype], (i, tok, int(row.argmax()))
+            assert greedy_ok(row, tok, dtype), (i, tok, int(row.argmax()), float(row.max() - row[tok]))
     if dtype == torch.float32:
         for p, o in zip(prompts, outs):
             want, _ = plain_llama.greedy_generate(cfg, weights, p, n_new)
@@ -200,6 +200,65 @@ def test_greedy_generation_through_the_entry_point(tmp, which, dtype):
     alone = model.generate(prompts[-1], opts)
     if dtype == torch.float32:
         assert alone.generated_token_ids == outs[-1].generated_token_ids
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which,n_seqs", [("A", 40), ("D", 64), ("C", 33)])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_decoding_many_sequences_at_once(tmp, which, n_seqs, dtype, graphs):
+    """Decode steps of 33, 40 and 64 sequences of unequal lengths that end at different steps (the
+    batch shrinks through 17 and 16 rows, where the decode products change kernels), eagerly and
+    through captured graphs, every logit against the plain implementation."""
+    from dotllm_b200 import StepEntry
+    model, cfg, weights, _ = load_pair(tmp, which, dtype)
+    vocab, positions = cfg["vocab_size"], cfg["max_position_embeddings"]
+    lens = [min(positions - 14, 3 + (37 * i) % 90 + (130 if i % 11 == 0 else 0)) for i in range(n_seqs)]
+    n_decode = [2 + (5 * i) % 11 for i in range(n_seqs)]               # 2 to 12 decoded tokens each
+    reqs = [tiny_models.random_tokens(n + d, vocab, seed=900 + i) for i, (n, d) in enumerate(zip(lens, n_decode))]
+    refs = [plain_llama.forward(cfg, weights, r) for r in reqs]
+    cache = model.new_cache(max_tokens=sum((len(r) + 63) // 64 * 64 for r in reqs))
+    cache.fill_free_pages(float("nan"))
+    seqs = [cache.open_sequence() for _ in reqs]
+    out = model.step(cache, [StepEntry(s, r[:n]) for s, r, n in zip(seqs, reqs, lens)])
+    for i, (ref, n) in enumerate(zip(refs, lens)):
+        assert_close(out[i], ref[n - 1], dtype, f"prefill of sequence {i}")
+    done = [0] * n_seqs
+    live = list(range(n_seqs))
+    sizes = set()
+    while live:
+        sizes.add(len(live))
+        out = model.step(cache, [StepEntry(seqs[i], [reqs[i][lens[i] + done[i]]]) for i in live], graphs=graphs).clone()
+        for row, i in enumerate(live):
+            assert_close(out[row], refs[i][lens[i] + done[i]], dtype,
+                         f"{len(live)} live: sequence {i} position {lens[i] + done[i]}")
+            done[i] += 1
+        for i in list(live):
+            if done[i] == n_decode[i]:
+                cache.close_sequence(seqs[i])
+                live.remove(i)
+        cache.fill_free_pages(float("nan"))
+    assert max(sizes) == n_seqs and min(sizes) <= 16 and any(16 < n <= 32 for n in sizes)
+    cache.check()
+
+
+def test_a_sampled_request_gives_the_same_tokens_alone_and_in_any_batch(tmp):
+    """A request's draws depend on its own seed and step only: the same prompt, options and seed give
+    the same tokens alone, as the first of a batch and as the last of another (float32, where the
+    logits do not depend on the batch either)."""
+    from dotllm_b200 import InferenceOptions
+    model, cfg, _, _ = load_pair(tmp, "A", torch.float32)
+    vocab = cfg["vocab_size"]
+    mine = tiny_models.random_tokens(12, vocab, 77)
+    others = [tiny_models.random_tokens(n, vocab, 80 + n) for n in (5, 20, 9)]
+    o_mine = InferenceOptions(temperature=0.8, top_k=40, top_p=0.9, seed=1234, max_tokens=12, stop_token_ids=[])
+    o_other = InferenceOptions(temperature=1.1, seed=99, max_tokens=7, stop_token_ids=[])
+    alone = model.generate(mine, o_mine).generated_token_ids
+    first = model.generate([mine] + others, [o_mine] + [o_other] * 3)[0].generated_token_ids
+    last = model.generate(others + [mine], [o_other] * 3 + [o_mine])[3].generated_token_ids
+    assert alone == first == last
+    # the same seed on two requests of one batch: the same stream for both (they differ by their logits only)
+    twice = model.generate([mine, mine], o_mine)
+    assert twice[0].generated_token_ids == twice[1].generated_token_ids == alone
 
 
 def test_seeded_sampling_is_reproducible_and_batch_independent(tmp):
@@ -325,3 +384,76 @@ def test_graph_step_after_pages_changed_at_the_same_length(tmp):
 
     eager, graphed = run(False), run(True)
     assert torch.equal(eager, graphed), f"max diff {(eager - graphed).abs().max()}"
+
+
+REAL_SIZES = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 131072, "hidden_act": "silu",
+}
+
+
+def test_two_layers_at_the_benchmark_models_sizes(tmp_path):
+    """Two layers with the layer sizes of the benchmark model (hidden 4096, 32 / 8 heads of 128,
+    feed-forward 14336, vocabulary 128256): three unequal prompts that cross page boundaries in one
+    step, then eight decode steps, in float32 (bound 1e-3 and the plain implementation's arg-max at
+    every step) and in bfloat16, every logit against the plain implementation.  The kernels run at
+    the sizes they are tuned for, which the tiny models never reach (cut tiles in the products, the
+    tcgen05 prefill attention, the LM head's 1002 tiles)."""
+    from dotllm_b200 import Model, StepEntry
+    from dotllm_b200.config import config_from_dict
+    from dotllm_b200.weights import write_random_model
+    folder = write_random_model(tmp_path / "real", config_from_dict(REAL_SIZES), seed=21, dtype=torch.bfloat16)
+    cfg, weights = plain_llama.read_model_folder(folder)       # bfloat16 numbers widened to float32: both sides read the same
+    vocab, n_new = cfg["vocab_size"], 8
+    prompts = [tiny_models.random_tokens(n, vocab, seed=50 + n) for n in (70, 130, 193)]
+
+    def plain_rows(tokens, rows):
+        """Plain logits of ``tokens`` at ``rows`` only (the head over 128256 outputs is the costly part)."""
+        cos, sin = plain_llama.rope_tables(range(len(tokens)), cfg["head_dim"], cfg["rope_theta"], cfg["rope_scaling"])
+        h = plain_llama.embed(weights["model.embed_tokens.weight"], tokens)
+        for layer in range(cfg["num_hidden_layers"]):
+            h = plain_llama.block(h, weights, layer, cfg, cos, sin)
+        h = plain_llama.rms_norm(h[rows], weights["model.norm.weight"], cfg["rms_norm_eps"])
+        return plain_llama.linear(h, weights["lm_head.weight"])
+
+    forced = None
+    # bfloat16 at these sizes: the plain implementation itself, with its activations rounded to bfloat16
+    # between parts, moves by 7.1e-2 at most and by 1.1e-2 of a row's rms (the embedding's rows are
+    # tiny, so the stream is made of branch outputs and their rounding); the engine shows 7.5e-2 and 1.3e-2.
+    for dtype, bound, rel_bound in ((torch.float32, 1e-3, 1e-4), (torch.bfloat16, 0.15, 2.5e-2)):
+        model = Model.load(folder, dtype=dtype)
+        cache = model.new_cache(max_tokens=1024)
+        seqs = [cache.open_sequence() for _ in prompts]
+        got = [model.step(cache, [StepEntry(s, p) for s, p in zip(seqs, prompts)]).cpu()]
+        if forced is None:
+            # float32 first: its own greedy tokens are the continuation, checked against the plain arg-max below
+            tokens = [[int(t)] for t in got[0].argmax(dim=-1)]
+            for step in range(1, n_new):
+                got.append(model.step(cache, [StepEntry(s, [t[-1]]) for s, t in zip(seqs, tokens)]).cpu())
+                for t, row in zip(tokens, got[-1]):
+                    t.append(int(row.argmax()))
+            forced = tokens
+        else:
+            for step in range(1, n_new):
+                got.append(model.step(cache, [StepEntry(s, [t[step - 1]]) for s, t in zip(seqs, forced)], graphs=True).cpu().clone())
+        for s in seqs:
+            cache.close_sequence(s)
+        del model, cache
+        torch.cuda.empty_cache()
+        worst = 0.0
+        for i, (p, cont) in enumerate(zip(prompts, forced)):
+            rows = [len(p) - 1 + j for j in range(n_new)]
+            ref = plain_rows(p + cont[:n_new - 1], rows)
+            mine = torch.stack([g[i] for g in got])
+            err = float((mine - ref).abs().max())
+            worst = max(worst, err)
+            rel = float(((mine - ref).norm(dim=1) / ref.norm(dim=1)).max())
+            assert rel <= rel_bound, f"{dtype}: request {i}: a row's rms error is {rel:.3e} of its rms"
+            assert err <= bound, f"{dtype}: request {i} differs from the plain implementation by {err:.3e}"
+            if dtype == torch.float32:
+                assert [int(r.argmax()) for r in ref] == cont, f"request {i}: greedy tokens differ from the plain arg-max"
+        print(f"real sizes {dtype}: max |logit difference| {worst:.3e}")

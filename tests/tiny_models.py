@@ -46,8 +46,21 @@ TINY_C = {
     "hidden_act": "silu",
 }
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-GAIN_INIT = {"A": ("one_plus_uniform", 0.1), "B": ("ones",), "C": ("one_plus_uniform", 0.1)}
+# A fourth with the benchmark model's head size (128) and grouping (4:1): the head size that the
+# tcgen05 prefill kernel and the decode kernel's own rotation are written for.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 512, "num_attention_heads": 4, "num_key_value_heads": 1,
+    "head_dim": 128, "intermediate_size": 1376, "vocab_size": 512,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 1024,
+    "hidden_act": "silu",
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+GAIN_INIT = {"A": ("one_plus_uniform", 0.1), "B": ("ones",), "C": ("one_plus_uniform", 0.1), "D": ("one_plus_uniform", 0.1)}
 
 
 def make_folder(tmp_path, which, seed=0, dtype=torch.float32):
