@@ -1,12 +1,19 @@
 """Decode and prefill throughput of the Llama-3.1-8B-shaped model with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
+                    [--dtype bfloat16|float32] [--shape 8b|1b|13b] [--repeats 5]
+    python bench.py --shape 1b --workload unequal     # 64 prompts of 16..2048 tokens in one step, then 256 decode steps
+    python bench.py --impl plain-cpu                  # the plain implementation under tests/, timed on the CPU
 
 A "step" is one decode step: one new token for each of ``batch`` sequences that already hold
 ``context`` tokens.  ``value`` is decoded tokens per second, timed on the device with CUDA events
 over K consecutive steps (every step reads all weights, far more than the L2 holds).  ``e2e`` is
 the same through the public entry point with host token ids in and out every step.  The line also
-carries a 2,048-token prefill, decode at batch 1 and 64, and the decode step's HBM roofline.
+carries a 2,048-token prefill, decode at batch 1 and 64, the decode step's HBM roofline, the share
+of an eager step's kernel time per kernel family, and tokens per second of ``Model.generate`` itself
+(the loop users call: prompts in, 256 new tokens each out, stop tokens off).  Every timed region is
+repeated ``--repeats`` times; the best repetition is reported with the coefficient of variation over
+all of them (the reference's protocol, benchmarks/DotLLM.Benchmarks/InferenceBenchmarks.cs:30).
 
 The cache contents are random numbers written directly into the pages: a decode step's time does
 not depend on the values it reads, and filling 64 x 8192 positions through the model would take
@@ -53,6 +60,7 @@ SHAPES = {"8b": ("Llama-3.1-8B-shaped", LLAMA_31_8B), "1b": ("Llama-3.2-1B-shape
           "13b": ("Llama-2-13B-shaped", LLAMA_2_13B)}
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FP32_TFLOPS_NOMINAL = 74.5      # 148 multiprocessors x 128 FMA a clock x 2 x 1.965 GHz: no measured float32 peak exists
 
 
 def peaks():
@@ -113,7 +121,12 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--repeats", type=int, default=5, help="repetitions of every timed region (best and CV are reported)")
+    ap.add_argument("--workload", default="steady", choices=["steady", "unequal"],
+                    help="unequal: 64 prompts of 16..2048 tokens in one prefill step, then 256 decode steps")
+    ap.add_argument("--no-generate", action="store_true", help="skip the Model.generate cells")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: the 8B default, or 1b / 13b")
@@ -127,6 +140,8 @@ def main():
                           "unavailable": "kkokosa/dotLLM is a .NET 10 program reading GGUF checkpoints; no .NET SDK, "
                                          "no checkpoint and no network exist here, so it cannot be installed or run"}))
         return 0
+    if args.impl == "plain-cpu":
+        return plain_cpu_baseline()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
@@ -134,7 +149,7 @@ def main():
         args.warmup = 3
 
     import torch
-    from dotllm_b200 import Model, StepEntry
+    from dotllm_b200 import InferenceOptions, Model, StepEntry
     from dotllm_b200.config import config_from_dict
     from dotllm_b200.kernels import library, ops
 
@@ -144,16 +159,20 @@ def main():
     cfg = config_from_dict(cfg_dict)
     torch.cuda.set_device(0)
     t0 = time.time()
-    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+    model = Model.random(cfg, seed=0, dtype=args.dtype, device="cuda:0", on_device=True)
+    esize = 2 if args.dtype == "bfloat16" else 4
+    dtype_name = "bf16" if args.dtype == "bfloat16" else "fp32"
+    compute_peak = pk["bf16_tflops"] if args.dtype == "bfloat16" else FP32_TFLOPS_NOMINAL
     torch.cuda.synchronize()
     print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 
     steps, warmup, ctx = args.steps, args.warmup, args.context
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
-    room = ctx + 4 * (steps + warmup) + 128
+    reps = max(1, args.repeats)
+    room = ctx + 2 * reps * steps + warmup + 128        # every timed step grows every sequence by one token
     # The cache must fit beside the weights: a batch whose sequences of `ctx` tokens would not fit
     # runs at the longest context that does (reported with its point).
-    per_token = 2 * 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim
+    per_token = 2 * esize * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim
     free_bytes, _ = torch.cuda.mem_get_info()
     fit_tokens = int(0.85 * free_bytes) // per_token
     ctx_of = {b: min(ctx, max(256, fit_tokens // b - (room - ctx)) // 64 * 64) for b in batches}
@@ -176,6 +195,10 @@ def main():
         return real_call(name, *a)
     library.call = counting_call                           # every kernel module calls through library.call
 
+    def spread(values):
+        """Coefficient of variation of the repetitions (0 for a single one)."""
+        return round(statistics.pstdev(values) / statistics.mean(values), 4) if len(values) > 1 else 0.0
+
     def decode_point(batch, measure_e2e):
         ctx = ctx_of[batch]
         seqs = [cache.open_sequence() for _ in range(batch)]
@@ -194,38 +217,80 @@ def main():
             ops.sample(graphs.run(entries, device_tokens=True), out=tok_buf)
         torch.cuda.synchronize()
         sampler = ClockSampler()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            ops.sample(graphs.run(entries, device_tokens=True), out=tok_buf)
-        stop.record()
-        torch.cuda.synchronize()
+        times = []
+        for _ in range(reps):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(steps):
+                ops.sample(graphs.run(entries, device_tokens=True), out=tok_buf)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) / steps)
         clocks = sampler.stop()
-        ms = start.elapsed_time(stop) / steps
+        ms = min(times)
         result = {"ms": ms, "tok_s": batch * 1000.0 / ms, "clocks": clocks, "launches": steps * (per_replay + 1),
-                  "mean_len": sum(s.length for s in seqs) / batch}
+                  "mean_len": sum(s.length for s in seqs) / batch, "cv": spread(times)}
         if measure_e2e:
             host_tokens = tok_buf.tolist()
             copied = graphs.captured[batch].h2d_bytes         # counted where the copies are issued
-            torch.cuda.synchronize()
-            t_a = time.perf_counter()
-            for _ in range(steps):
-                lg = model.step(cache, [StepEntry(s, [t]) for s, t in zip(seqs, host_tokens)], graphs=True)
-                host_tokens = ops.sample(lg).tolist()        # device -> host read of the step's result
-            torch.cuda.synchronize()
-            e2e_ms = (time.perf_counter() - t_a) * 1e3 / steps
+            e2e_times = []
+            for _ in range(reps):
+                torch.cuda.synchronize()
+                t_a = time.perf_counter()
+                for _ in range(steps):
+                    lg = model.step(cache, [StepEntry(s, [t]) for s, t in zip(seqs, host_tokens)], graphs=True)
+                    host_tokens = ops.sample(lg).tolist()        # device -> host read of the step's result
+                torch.cuda.synchronize()
+                e2e_times.append((time.perf_counter() - t_a) * 1e3 / steps)
+            e2e_ms = min(e2e_times)
             result["e2e"] = {"value": batch * 1000.0 / e2e_ms, "unit": "tokens/s", "ms_per_step": e2e_ms,
-                             "h2d_bytes_per_step": (graphs.captured[batch].h2d_bytes - copied) // steps,
-                             "d2h_bytes_per_step": 4 * batch}
+                             "h2d_bytes_per_step": (graphs.captured[batch].h2d_bytes - copied) // (steps * reps),
+                             "d2h_bytes_per_step": 4 * batch, "cv": spread(e2e_times)}
+            result["shares"] = family_shares(seqs, host_tokens)
         for s in seqs:
             cache.close_sequence(s)
         return result
 
+    FAMILIES = (("products", ("gemm", "swiglu")), ("attention", ("attention", "rope")),
+                ("norm_embed_sample", ("rmsnorm", "gather", "sample", "penalty")))
+
+    def family_shares(seqs, host_tokens):
+        """One eager decode step with a CUDA event on either side of every kernel of this library: the
+        share of the summed kernel time per family.  (Eager launches do not overlap as a replayed
+        graph's do, so these are shares of kernel time, not of the step's wall time.)"""
+        spans = []
+
+        def timed_call(name, *a):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            counting_call(name, *a)
+            a1.record()
+            spans.append((name, a0, a1))
+        library.call = timed_call
+        try:
+            lg = model.step(cache, [StepEntry(s, [t]) for s, t in zip(seqs, host_tokens)])
+            ops.sample(lg)
+            torch.cuda.synchronize()
+        finally:
+            library.call = counting_call
+        total = sum(a0.elapsed_time(a1) for _, a0, a1 in spans) or 1.0
+        shares = {}
+        for family, keys in FAMILIES:
+            shares[family] = round(sum(a0.elapsed_time(a1) for n, a0, a1 in spans if any(k in n for k in keys)) / total, 3)
+        shares["other"] = round(max(0.0, 1.0 - sum(shares.values())), 3)
+        return shares
+
+    def prefill_flops(T, rows_out):
+        per_layer = 2 * T * (cfg.hidden_size * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.hidden_size
+                             + 3 * cfg.hidden_size * cfg.intermediate_size)
+        return cfg.num_hidden_layers * per_layer + 2 * rows_out * cfg.hidden_size * vocab
+
     def prefill_point():
-        """One prompt of PREFILL_TOKENS tokens through model.step: best of three after three warm-ups."""
-        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        """One prompt of PREFILL_TOKENS tokens through model.step: best of ``reps`` after three warm-ups."""
+        import numpy as np
+        prompt = np.asarray(torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen))
         times = []
-        for it in range(3 + 3):
+        for it in range(3 + reps):
             s = cache.open_sequence()
             torch.cuda.synchronize()
             a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -238,11 +303,35 @@ def main():
             cache.close_sequence(s)
         p_ms = min(times)
         T = PREFILL_TOKENS
-        per_layer = 2 * T * (cfg.hidden_size * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.hidden_size
-                             + 3 * cfg.hidden_size * cfg.intermediate_size) + 2 * T * T * cfg.q_dim
-        flops = cfg.num_hidden_layers * per_layer + 2 * cfg.hidden_size * vocab
+        flops = prefill_flops(T, 1) + cfg.num_hidden_layers * 2 * T * T * cfg.q_dim
         return {"value": round(T * 1000.0 / p_ms, 1), "tokens": T, "ms": round(p_ms, 3),
-                "frac": round(flops / (p_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "peak": pk["source"]}
+                "frac": round(flops / (p_ms * 1e-3) / (compute_peak * 1e12), 4),
+                "peak": pk["source"] if args.dtype == "bfloat16" else "nominal fp32", "cv": spread(times)}
+
+    def generate_point(batch, prompt_len=128, new_tokens=256):
+        """Tokens per second of Model.generate itself: host prompts in, host tokens out, stop tokens off."""
+        prompts = [torch.randint(0, vocab, (prompt_len,), generator=gen).tolist() for _ in range(batch)]
+        need = batch * ((prompt_len + new_tokens + 63) // 64 * 64)
+        if need > cache.max_tokens:
+            return None
+        generator = model.generator(cache=cache, max_batch=batch)
+        options = InferenceOptions(temperature=0.0, max_tokens=new_tokens, stop_token_ids=[])
+        generator.generate(prompts[:batch], options)          # warm-up: captures the graph of this batch size
+        times = []
+        for _ in range(min(reps, 3)):
+            torch.cuda.synchronize()
+            t_a = time.perf_counter()
+            out = generator.generate(prompts, options)
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t_a)
+        assert all(o.generated_token_count == new_tokens for o in out)
+        t = out[0].timings
+        return {"value": round(batch * new_tokens / min(times), 1), "prompt_tokens": prompt_len, "new_tokens": new_tokens,
+                "decode_tok_s": round(batch * t.decode_steps / (t.decode_ms / 1e3), 1), "prefill_ms": round(t.prefill_ms, 2),
+                "sampling_ms": round(t.sampling_ms, 2), "cv": spread(times)}
+
+    if args.workload == "unequal":
+        return unequal_workload(args, model, cache, cfg, gen, pk, shape_name, dtype_name, compute_peak, weight_bytes, prefill_flops)
 
     if args.only_prefill:
         print(json.dumps({"prefill": prefill_point(), "layers": cfg.num_hidden_layers}))
@@ -251,6 +340,7 @@ def main():
     main_point = decode_point(args.batch, True)
     points = {}
     prefill = None
+    generate = {}
     if not args.no_points:
         for b in batches:
             if b != args.batch:
@@ -258,34 +348,151 @@ def main():
                 points[name] = round(decode_point(b, False)["tok_s"], 1)
         points[f"decode_b{args.batch}"] = round(main_point["tok_s"], 1)
         prefill = prefill_point()
+        if not args.no_generate:
+            for b in sorted({args.batch, 64}):
+                g = generate_point(b)
+                if g is not None:
+                    generate[f"b{b}"] = g
 
     step_bytes = weight_bytes + args.batch * main_point["mean_len"] * kv_bytes_per_token
     achieved = step_bytes / (main_point["ms"] * 1e-3) / 1e9
     line = {
         "metric": "decode tokens/s", "value": round(main_point["tok_s"], 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(main_point["ms"], 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_name,
         "data": "synthetic: seeded random weights, random token ids, random cache contents",
         "config": {"model": shape_name, "layers": cfg.num_hidden_layers,
                    "layers_full": shape["num_hidden_layers"], "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": vocab,
                    "global_batch": args.batch, "seq_len": ctx_of[args.batch], "parallelism": "none (1 GPU)",
-                   "weights": "bf16", "cache": "bf16 pages of 64 tokens",
+                   "weights": dtype_name, "cache": f"{dtype_name} pages of 64 tokens",
                    "l2": "inputs larger than L2 (all weights are read every step)",
                    "decode": "CUDA graph replay, one captured graph per batch size",
                    "prefill_tokens": PREFILL_TOKENS},
+        "repeats": reps, "cv": main_point["cv"],
         "clocks": main_point["clocks"],
         "e2e": main_point.get("e2e"),
         "gpu_launches": main_point["launches"],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"],
                      "bytes_per_step": int(step_bytes)},
+        "shares": main_point.get("shares"),
     }
     if prefill is not None:
         line["prefill"] = prefill
         line["points"] = points
+    if generate:
+        line["generate"] = generate
     print(json.dumps(line))
+    return 0
+
+
+def unequal_workload(args, model, cache, cfg, gen, pk, shape_name, dtype_name, compute_peak, weight_bytes, prefill_flops):
+    """64 prompts with lengths uniform in [16, 2048] in ONE prefill step, then 256 decode steps at batch
+    64 (the Llama-3.2-1B-shaped workload).  Prints its own JSON line."""
+    import numpy as np
+    import torch
+    from dotllm_b200 import StepEntry
+    from dotllm_b200.kernels import ops
+    n_seqs, n_decode = 64, 256
+    lens = torch.randint(16, 2049, (n_seqs,), generator=gen).tolist()
+    prompts = [np.asarray(torch.randint(0, cfg.vocab_size, (n,), generator=gen)) for n in lens]
+    need = sum((n + n_decode + 63) // 64 * 64 for n in lens)
+    big = model.new_cache(max_tokens=need, max_sequences=n_seqs) if need > cache.max_tokens else cache
+    results = {"prefill_ms": [], "decode_ms": [], "plan_ms": []}
+    from dotllm_b200.engine.step import plan_step
+    for rep in range(1 + min(args.repeats, 3)):
+        seqs = [big.open_sequence() for _ in prompts]
+        entries = [StepEntry(s, p) for s, p in zip(seqs, prompts)]
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_host = time.perf_counter()
+        a.record()
+        logits = model.step(big, entries)
+        b.record()
+        torch.cuda.synchronize()
+        graphs = model.decode_graphs(big)
+        tokens = ops.sample(logits).tolist()
+        dec = [StepEntry(s, [t]) for s, t in zip(seqs, tokens)]
+        lg = graphs.run(dec)
+        tok_buf = graphs.token_buffer(n_seqs)
+        ops.sample(lg, out=tok_buf)
+        torch.cuda.synchronize()
+        c, d = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c.record()
+        for _ in range(n_decode - 1):
+            ops.sample(graphs.run(dec, device_tokens=True), out=tok_buf)
+        d.record()
+        torch.cuda.synchronize()
+        mean_len = sum(s.length for s in seqs) / n_seqs - n_decode / 2
+        for s in seqs:
+            big.close_sequence(s)
+        # what planning alone costs on the host, without the model
+        seqs = [big.open_sequence() for _ in prompts]
+        t0 = time.perf_counter()
+        plan_step([StepEntry(s, p) for s, p in zip(seqs, prompts)], big, cfg.vocab_size, 1 << 30, model.runtime.device)
+        plan_ms = (time.perf_counter() - t0) * 1e3
+        for s in seqs:
+            big.close_sequence(s)
+        if rep:                                              # the first round warms up (captures the graph)
+            results["prefill_ms"].append(a.elapsed_time(b))
+            results["decode_ms"].append(c.elapsed_time(d) / (n_decode - 1))
+            results["plan_ms"].append(plan_ms)
+    total = sum(lens)
+    p_ms, d_ms = min(results["prefill_ms"]), min(results["decode_ms"])
+    flops = prefill_flops(total, n_seqs) + cfg.num_hidden_layers * sum(2 * n * n * cfg.q_dim for n in lens)
+    step_bytes = weight_bytes + n_seqs * mean_len * big.bytes_per_token()
+    print(json.dumps({
+        "metric": "unequal batch: prefill tokens/s and decode tokens/s", "model": shape_name, "dtype": dtype_name,
+        "sequences": n_seqs, "prompt_tokens": total, "decode_steps": n_decode,
+        "prefill": {"value": round(total * 1e3 / p_ms, 1), "ms": round(p_ms, 2), "planning_ms": round(min(results["plan_ms"]), 2),
+                    "frac": round(flops / (p_ms * 1e-3) / (compute_peak * 1e12), 4)},
+        "decode": {"value": round(n_seqs * 1e3 / d_ms, 1), "ms_per_step": round(d_ms, 4),
+                   "roofline_frac": round(step_bytes / (d_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+        "data": "synthetic: seeded random weights, seeded prompt lengths and token ids"}))
+    return 0
+
+
+def plain_cpu_baseline():
+    """The plain implementation (tests/plain_llama.py, float32, PyTorch on the host's cores) timed on the
+    tiny test models and on a short prompt through one Llama-3.2-1B-shaped layer stack: the CPU line
+    that stands where the reference's own CPU numbers would."""
+    import tempfile
+    from pathlib import Path
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_llama
+    import tiny_models
+    from dotllm_b200.config import config_from_dict
+    from dotllm_b200.weights import write_random_model
+    out = {"impl": "plain-cpu", "threads": torch.get_num_threads(), "cells": {}}
+    with tempfile.TemporaryDirectory() as tmp:
+        for which, lens, n_new in (("A", tiny_models.TINY_A_PROMPTS, tiny_models.TINY_A_DECODE),
+                                   ("B", tiny_models.TINY_B_PROMPTS, tiny_models.TINY_B_DECODE)):
+            folder = tiny_models.make_folder(Path(tmp), which, seed=0)
+            cfg, weights = plain_llama.read_model_folder(folder)
+            prompts = [tiny_models.random_tokens(n, cfg["vocab_size"], 3 + n) for n in lens]
+            t0 = time.perf_counter()
+            for p in prompts:
+                plain_llama.forward(cfg, weights, p)
+            prefill_s = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            for p in prompts:
+                plain_llama.greedy_generate(cfg, weights, p, n_new)
+            out["cells"][f"tiny_{which}"] = {"prefill_tok_s": round(sum(lens) / prefill_s, 1),
+                                             "generate_tok_s_no_cache": round(len(lens) * n_new / (time.perf_counter() - t0), 1)}
+        one_b = dict(LLAMA_32_1B, num_hidden_layers=2, max_position_embeddings=4096)
+        folder = write_random_model(Path(tmp) / "1b", config_from_dict(one_b), seed=0, dtype=torch.bfloat16)
+        cfg, weights = plain_llama.read_model_folder(folder)
+        prompt = tiny_models.random_tokens(128, cfg["vocab_size"], 9)
+        plain_llama.forward(cfg, weights, prompt[:8])
+        t0 = time.perf_counter()
+        plain_llama.forward(cfg, weights, prompt)
+        dt = time.perf_counter() - t0
+        out["cells"]["llama_3.2_1b_shape_2_of_16_layers"] = {"prefill_tokens": 128, "seconds": round(dt, 3),
+                                                             "prefill_tok_s_2_layers_and_head": round(128 / dt, 1)}
+    print(json.dumps(out))
     return 0
 
 

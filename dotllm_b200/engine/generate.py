@@ -93,15 +93,30 @@ def plan_batches(requests, cache_tokens, max_batch, max_positions):
     return batches
 
 
+class HostClock:
+    """Marks are host times: right for step and sampling functions that return when their work is done."""
+
+    def mark(self):
+        return time.perf_counter()
+
+    @staticmethod
+    def ms(a, b):
+        return (b - a) * 1e3
+
+
 class TextGenerator:
     """Drives a step function over batches of requests.
 
     ``step_fn(entries) -> logits``: rows in entry order, one per entry (the last token's).
     ``sample_fn(logits, pipelines, generated, sequence_indices, steps) -> ids`` (host ints or a
-    tensor).  ``cache`` opens and closes sequences and says how many tokens it can hold."""
+    tensor).  ``cache`` opens and closes sequences and says how many tokens it can hold.
+    ``fetch(ids) -> list of ints`` brings a step's sampled ids to the host; it is the one point of a
+    step where the host waits for the device (the default takes ids that are already host values).
+    ``clock`` marks the boundaries between a step's forward pass and its sampling for the timings:
+    ``clock.mark()`` now, ``clock.ms(a, b)`` once the batch is over (so marks may be device events)."""
 
     def __init__(self, step_fn: Callable, sample_fn: Callable, cache, *, max_positions, vocab_size,
-                 default_stop_ids=(), bos_token_id=None, max_batch=None, synchronize=None):
+                 default_stop_ids=(), bos_token_id=None, max_batch=None, fetch=None, clock=None):
         self.step_fn = step_fn
         self.sample_fn = sample_fn
         self.cache = cache
@@ -110,7 +125,8 @@ class TextGenerator:
         self.default_stop_ids = tuple(default_stop_ids)
         self.bos_token_id = bos_token_id
         self.max_batch = max_batch or cache.n_slots
-        self.synchronize = synchronize or (lambda: None)
+        self.fetch = fetch or (lambda ids: [int(t) for t in (ids.tolist() if hasattr(ids, "tolist") else ids)])
+        self.clock = clock or HostClock()
 
     # ---------------------------------------------------------------- api
     def generate(self, prompts, options=None, on_token=None):
@@ -184,46 +200,47 @@ class TextGenerator:
         return True
 
     def _sample(self, logits, live):
-        ids = self.sample_fn(logits, [r.pipeline for r in live], [r.generated for r in live],
-                             [r.index for r in live], [len(r.generated) for r in live])
-        return [int(t) for t in (ids.tolist() if hasattr(ids, "tolist") else ids)]
+        return self.sample_fn(logits, [r.pipeline for r in live], [r.generated for r in live],
+                              [r.index for r in live], [len(r.generated) for r in live])
 
     def _run_batch(self, batch, on_token):
-        timings = {}
+        clock = self.clock
+        marks = []                                           # per step: before the forward pass, after it, after sampling
         try:
             for r in batch:
                 r.sequence = self.cache.open_sequence()
-            self.synchronize()
-            t0 = time.perf_counter()
+            t0 = clock.mark()
             logits = self.step_fn([StepEntry(r.sequence, r.prompt) for r in batch])
-            self.synchronize()
-            t1 = time.perf_counter()
-            tokens = self._sample(logits, batch)
-            t2 = time.perf_counter()
-            prefill_ms, sampling_ms, decode_ms = (t1 - t0) * 1e3, (t2 - t1) * 1e3, 0.0
+            t1 = clock.mark()
+            ids = self._sample(logits, batch)
+            t2 = clock.mark()
+            marks.append((t0, t1, t2, None))
+            tokens = self.fetch(ids)                         # the step's one wait for the device
             live = [r for r, tok in zip(batch, tokens) if self._accept(r, tok, on_token)]
             while live:
-                t0 = time.perf_counter()
+                t0 = clock.mark()
                 logits = self.step_fn([StepEntry(r.sequence, [r.generated[-1]]) for r in live])
-                self.synchronize()
-                t1 = time.perf_counter()
-                tokens = self._sample(logits, live)
-                t2 = time.perf_counter()
-                decode_ms += (t1 - t0) * 1e3
-                sampling_ms += (t2 - t1) * 1e3
-                for r in live:
-                    r.decode_ms = decode_ms
+                t1 = clock.mark()
+                ids = self._sample(logits, live)
+                t2 = clock.mark()
+                marks.append((t0, t1, t2, list(live)))
+                tokens = self.fetch(ids)
                 live = [r for r, tok in zip(live, tokens) if self._accept(r, tok, on_token)]
-            timings = dict(prefill_ms=prefill_ms, sampling_ms=sampling_ms)
         finally:
             for r in batch:                                  # an error must not leak slots
                 if r.sequence is not None and r.sequence.open:
                     self.cache.close_sequence(r.sequence)
+        prefill_ms = clock.ms(marks[0][0], marks[0][1])
+        sampling_ms = sum(clock.ms(t1, t2) for _, t1, t2, _ in marks)
+        for t0, t1, _, live in marks[1:]:
+            step_ms = clock.ms(t0, t1)
+            for r in live:
+                r.decode_ms += step_ms
         total_prompt = sum(len(r.prompt) for r in batch)
         for r in batch:
             r.response = InferenceResponse(
                 list(r.generated), r.finish_reason, len(r.prompt), len(r.generated),
-                InferenceTimings(prefill_ms=timings["prefill_ms"], decode_ms=r.decode_ms,
-                                 sampling_ms=timings["sampling_ms"], prefill_tokens=len(r.prompt),
+                InferenceTimings(prefill_ms=prefill_ms, decode_ms=r.decode_ms,
+                                 sampling_ms=sampling_ms, prefill_tokens=len(r.prompt),
                                  decode_steps=max(0, len(r.generated) - 1), batch_size=len(batch),
                                  batch_prefill_tokens=total_prompt))

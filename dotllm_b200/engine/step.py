@@ -15,6 +15,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Optional
 
+import numpy as np
 import torch
 
 from ..errors import StepError
@@ -67,13 +68,16 @@ class StepContext:
 
 def plan_step(entries, cache, vocab_size, max_positions, device):
     """Validate the entries, reserve cache room, and build the device-side description with one
-    host-to-device copy.  Returns (StepContext, new lengths)."""
+    host-to-device copy.  Returns (StepContext, new lengths).  Per-token work is done on arrays, not
+    in Python loops: a step may bring tens of thousands of prompt tokens."""
     if not entries:
         raise StepError("a step needs at least one sequence")
+    B = len(entries)
     seen = set()
-    tokens, token_seq, token_pos, want_rows = [], [], [], []
-    starts, news, slots = [], [], []
-    offset = 0
+    starts = np.empty(B, dtype=np.int64)
+    news = np.empty(B, dtype=np.int64)
+    slots = np.empty(B, dtype=np.int64)
+    token_arrays, want_arrays = [], []
     for b, e in enumerate(entries):
         seq = e.sequence
         if not getattr(seq, "open", False):
@@ -81,66 +85,73 @@ def plan_step(entries, cache, vocab_size, max_positions, device):
         if seq.slot in seen:
             raise StepError(f"entry {b}: slot {seq.slot} occurs twice in one step")
         seen.add(seq.slot)
-        n = len(e.tokens)
+        try:
+            toks = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+        except (TypeError, ValueError, OverflowError):
+            raise StepError(f"entry {b}: its tokens are not integers") from None
+        n = toks.size
         if n < 1:
             raise StepError(f"entry {b}: a sequence must bring at least one token")
         start = seq.length
         if start + n > max_positions:
             raise StepError(f"entry {b}: position {start + n - 1} is beyond the model's "
                             f"max positions {max_positions}")
-        for t in e.tokens:
-            if not 0 <= int(t) < vocab_size:
-                raise StepError(f"entry {b}: token id {t} is outside the vocabulary [0, {vocab_size})")
-        want = [n - 1] if e.want is None else list(e.want)
-        for w in want:
-            if not 0 <= int(w) < n:
-                raise StepError(f"entry {b}: wanted offset {w} is outside its {n} tokens")
-        tokens.extend(int(t) for t in e.tokens)
-        token_seq.extend([b] * n)
-        token_pos.extend(range(start, start + n))
-        want_rows.extend(offset + int(w) for w in want)
-        starts.append(start)
-        news.append(n)
-        slots.append(seq.slot)
-        offset += n
-    cache.reserve([(e.sequence, s + n) for e, s, n in zip(entries, starts, news)])
+        if toks.min() < 0 or toks.max() >= vocab_size:
+            bad = toks[(toks < 0) | (toks >= vocab_size)][0]
+            raise StepError(f"entry {b}: token id {int(bad)} is outside the vocabulary [0, {vocab_size})")
+        want = np.asarray([n - 1] if e.want is None else e.want, dtype=np.int64).reshape(-1)
+        if want.size and (want.min() < 0 or want.max() >= n):
+            bad = want[(want < 0) | (want >= n)][0]
+            raise StepError(f"entry {b}: wanted offset {int(bad)} is outside its {n} tokens")
+        token_arrays.append(toks)
+        want_arrays.append(want)
+        starts[b], news[b], slots[b] = start, n, seq.slot
+    totals = starts + news
+    cache.reserve([(e.sequence, int(t)) for e, t in zip(entries, totals)])
 
-    T, B, R = offset, len(entries), len(want_rows)
+    cu = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(news, out=cu[1:])
+    T = int(cu[-1])
+    tokens = np.concatenate(token_arrays)
+    token_seq = np.repeat(np.arange(B, dtype=np.int64), news)
+    token_pos = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1] - starts, news)
+    want_rows = np.concatenate([w + cu[b] for b, w in enumerate(want_arrays)]) if want_arrays else np.zeros(0, np.int64)
+    R = int(want_rows.size)
     seqs = [e.sequence for e in entries]
     tables = {}
     for g in cache.kv_groups:
-        rows, width = cache.block_table_rows(g.index, seqs)
-        tables[g.index] = (rows, width)
-    cu = [0]
-    for n in news:
-        cu.append(cu[-1] + n)
+        width = max(1, max(len(s.pages[g.index]) for s in seqs))
+        rows = np.full((B, width), -1, dtype=np.int64)
+        for r, s in enumerate(seqs):
+            pages = s.pages[g.index]
+            rows[r, :len(pages)] = pages
+        tables[g.index] = rows
     # one packed int32 buffer, one copy
-    totals = [s + n for s, n in zip(starts, news)]
-    parts = [tokens, token_seq, token_pos, slots, starts, news, cu, want_rows, totals]
-    for rows, width in tables.values():
-        parts.append([p for row in rows for p in row])
-    flat = [v for part in parts for v in part]
-    host = torch.tensor(flat, dtype=torch.int32)
-    if device.type == "cuda":
-        host = host.pin_memory()
+    parts = [tokens, token_seq, token_pos, slots, starts, news, cu, want_rows, totals] + [t.reshape(-1) for t in tables.values()]
+    sizes = [p.size for p in parts]
+    host = torch.empty(sum(sizes), dtype=torch.int32, pin_memory=device.type == "cuda")
+    view = host.numpy()
+    at = 0
+    for p, n in zip(parts, sizes):
+        view[at:at + n] = p
+        at += n
     dev = host.to(device, non_blocking=True)
     views = []
     at = 0
-    for part in parts:
-        views.append(dev[at:at + len(part)])
-        at += len(part)
+    for n in sizes:
+        views.append(dev[at:at + n])
+        at += n
     d_tokens, d_seq, d_pos, d_slots, d_starts, d_news, d_cu, d_want, d_totals = views[:9]
-    block_tables = {}
-    for (gi, (rows, width)), view in zip(tables.items(), views[9:]):
-        block_tables[gi] = view.view(B, width)
-    plan = AttentionPlan(n_seqs=B, max_new=max(news), max_total=max(totals),
-                         all_single=all(n == 1 for n in news), seq_start=d_starts, seq_new=d_news,
-                         cu_new=d_cu, seq_total=d_totals, starts=starts, news=news)
+    block_tables = {gi: v.view(B, rows.shape[1]) for (gi, rows), v in zip(tables.items(), views[9:])}
+    starts_l, news_l = starts.tolist(), news.tolist()
+    plan = AttentionPlan(n_seqs=B, max_new=int(news.max()), max_total=int(totals.max()),
+                         all_single=bool((news == 1).all()), seq_start=d_starts, seq_new=d_news,
+                         cu_new=d_cu, seq_total=d_totals, starts=starts_l, news=news_l)
     ctx = StepContext(n_tokens=T, n_seqs=B, tokens=d_tokens, token_seq=d_seq, token_pos=d_pos,
                       slots=d_slots, block_tables=block_tables, want_rows=d_want, n_wanted=R,
-                      want_all=(R == T and want_rows == list(range(T))), attention_plan=plan,
+                      want_all=bool(R == T and np.array_equal(want_rows, np.arange(T))), attention_plan=plan,
                       seq_start=d_starts, seq_new=d_news, cu_new=d_cu)
-    return ctx, totals
+    return ctx, totals.tolist()
 
 
 def run_step(model, cache, entries):

@@ -25,11 +25,41 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
            "fp32": torch.float32, "f32": torch.float32}
 
 
-def _synchronize():
-    """Wait for the device and surface any kernel that gave up on a bounded wait."""
-    from .kernels import library
-    torch.cuda.synchronize()
-    library.check_status()
+class _IdFetcher:
+    """Brings a step's sampled ids to the host together with the kernels' status word: one small
+    device-to-host copy into pinned memory and one wait per step (no device-wide synchronisation,
+    no second read for the status)."""
+
+    def __init__(self, device):
+        self.device = device
+        self.pinned = torch.empty(4096, dtype=torch.int32).pin_memory()
+
+    def __call__(self, ids):
+        from .kernels import library
+        n = ids.numel()
+        if n + 1 > self.pinned.numel():
+            self.pinned = torch.empty(2 * (n + 1), dtype=torch.int32).pin_memory()
+        both = torch.cat([ids.to(torch.int32).reshape(-1), library.status_word(self.device)])
+        self.pinned[:n + 1].copy_(both, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        values = self.pinned[:n + 1].tolist()
+        if values[n]:
+            library.check_status()                           # raises with the kernel's reason and clears the word
+        return values[:n]
+
+
+class _EventClock:
+    """Marks are CUDA events on the current stream; their distances are read when the batch is over."""
+
+    def mark(self):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
+
+    @staticmethod
+    def ms(a, b):
+        b.synchronize()
+        return a.elapsed_time(b)
 
 
 def parse_dtype(dtype):
@@ -125,7 +155,7 @@ class Model:
         return TextGenerator(lambda entries: self.step(cache, entries, graphs=use_graphs), sample_rows, cache,
                              max_positions=self.spec.max_positions, vocab_size=self.spec.vocab_size,
                              default_stop_ids=self.spec.stop_token_ids, bos_token_id=self.spec.bos_token_id,
-                             max_batch=max_batch, synchronize=_synchronize)
+                             max_batch=max_batch, fetch=_IdFetcher(self.runtime.device), clock=_EventClock())
 
     def generate(self, prompts, options=None, on_token=None, **option_fields):
         """Generate for one prompt (a list of ints) or many.  Options as an InferenceOptions (or
