@@ -8,7 +8,8 @@ Here one object serves a batch:
   when it closes, with the sequence's own length;
 * per *group* of layer executions with equal needs, storage of its own.  A "kv" group holds keys
   and values in pages of 64 tokens taken from the group's pool as the sequence grows (K page
-  ``[kv_head][token][dim]``, V page ``[kv_head][dim][token]``); a group with a window gives pages
+  ``[kv_head][token][key width]``, V page ``[kv_head][value width][token]``, in the group's own
+  storage type when its mixer asks for one); a group with a window gives pages
   back once every token in them is older than the window.  A "state" group holds a fixed-size
   tensor per slot, zeroed when a sequence opens;
 * an execution that reads another execution's cache gets a view of that storage and never writes.
@@ -61,10 +62,9 @@ class CacheGroup:
         if self.kind == "kv":
             self.window = need.window
             self.pages = IdPool(n_pages, "page")
-            self.k = torch.zeros((n, n_pages, need.n_kv_heads, PAGE, need.head_dim),
-                                 dtype=runtime.dtype, device=runtime.device)
-            self.v = torch.zeros((n, n_pages, need.n_kv_heads, need.head_dim, PAGE),
-                                 dtype=runtime.dtype, device=runtime.device)
+            dtype = need.dtype or runtime.dtype
+            self.k = torch.zeros((n, n_pages, need.n_kv_heads, PAGE, need.key_width()), dtype=dtype, device=runtime.device)
+            self.v = torch.zeros((n, n_pages, need.n_kv_heads, need.value_width(), PAGE), dtype=dtype, device=runtime.device)
             self.state = None
         elif self.kind == "state":
             self.window = None
@@ -84,7 +84,7 @@ class CacheGroup:
         """Bytes of keys and values one cached token takes in this group."""
         if self.kind != "kv":
             return 0
-        return 2 * len(self.entries) * self.need.n_kv_heads * self.need.head_dim * self.k.element_size()
+        return len(self.entries) * self.need.n_kv_heads * (self.need.key_width() + self.need.value_width()) * self.k.element_size()
 
 
 class ModelCache:

@@ -26,13 +26,35 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class LayerPart:
+    """One part of a layer: the name its arrangement knows it by, its family ("mixer",
+    "feed_forward" or "norm") and its description."""
+    name: str
+    family: str
+    spec: PartSpec
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """One layer that owns weights: an arrangement of a mixer, a feed-forward and their norms."""
+    """One layer that owns weights: an arrangement and the named parts it wires together, in the order
+    their tensors are declared.  An arrangement asks for the names it needs: "pre_norm" wants
+    ``mixer_norm``, ``mixer``, ``feed_forward_norm`` and ``feed_forward``; a layer without a
+    feed-forward, or one with four norms, is another arrangement over another list."""
     arrangement: str            # registered block arrangement, e.g. "pre_norm"
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: tuple                # of LayerPart
+
+    def part(self, name):
+        for p in self.parts:
+            if p.name == name:
+                return p.spec
+        raise KeyError(name)
+
+
+def pre_norm_layer(mixer, feed_forward, mixer_norm, feed_forward_norm, arrangement="pre_norm"):
+    """The usual layer: norm -> mixer -> norm -> feed-forward, each branch added to the stream."""
+    return LayerSpec(arrangement, (LayerPart("mixer_norm", "norm", mixer_norm), LayerPart("mixer", "mixer", mixer),
+                                   LayerPart("feed_forward_norm", "norm", feed_forward_norm),
+                                   LayerPart("feed_forward", "feed_forward", feed_forward)))
 
 
 @dataclass(frozen=True)
@@ -61,11 +83,21 @@ class ModelSpec:
     head: PartSpec
     stop_token_ids: tuple = ()
     bos_token_id: Optional[int] = None
+    # (tensor a part declares, tensor it is the same as): the first is not looked for in a
+    # checkpoint, its part is handed the second's tensor (a head tied to the embedding table)
+    shared_weights: tuple = ()
 
     def validate(self) -> None:
         from ..errors import ConfigError
         if not self.schedule:
             raise ConfigError("the schedule names no layer")
+        for layer in self.layers:
+            names = [p.name for p in layer.parts]
+            if len(set(names)) != len(names):
+                raise ConfigError(f"a layer names a part twice: {names}")
+            for p in layer.parts:
+                if p.family not in ("mixer", "feed_forward", "norm"):
+                    raise ConfigError(f"layer part {p.name!r} has unknown family {p.family!r}")
         for n, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ConfigError(f"schedule entry {n} names layer {entry.layer}, "

@@ -12,6 +12,12 @@
 // only on its position, never on how the tokens were cut into steps or batched: this is
 // the kernel of the float32 path and the fallback of the bfloat16 path for sizes that the
 // tensor-core kernels do not take.
+//
+// It is also the one kernel that honours a change of the scores before the softmax, the place where
+// the reference's seam for position encodings that bias scores sits
+// (src/DotLLM.Core/PositionEncoding/IPositionEncoding.cs:10-34): with `softcap` > 0 a score becomes
+// softcap * tanh(score / softcap), and with `slopes` (one float per query head) slope * (key position -
+// query position) is added after that (a penalty that grows with distance).
 #include "common.cuh"
 
 #define AG_WARPS 4
@@ -23,7 +29,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const T* __restrict__ k_pool, const T* __restrict__ v_pool, int n_pages,
                          const int32_t* __restrict__ token_seq, const int32_t* __restrict__ token_pos,
                          const int32_t* __restrict__ block_table, int bt_stride, int nh, int nkv, int hd,
-                         float scale, int window) {
+                         float scale, int window, float softcap, const float* __restrict__ slopes) {
     extern __shared__ float q_smem[];                 // [AG_WARPS][hd]
     const int lane = threadIdx.x;
     const int t = blockIdx.x;
@@ -38,6 +44,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int seq = token_seq[t];
     const int kvh = h / (nh / nkv);
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const float slope = slopes != nullptr ? slopes[h] : 0.f;
     const int32_t* pages = block_table + (size_t)seq * bt_stride;
 
     float m = -INFINITY, l = 0.f;
@@ -57,6 +64,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
             float dot = 0.f;
             for (int d = 0; d < hd; ++d) dot += qs[d] * dl_to_f32<T>(kr[d]);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+            if (slopes != nullptr) s += slope * (float)(j - pos);
         }
         const float m_new = fmaxf(m, dl_warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -92,12 +101,13 @@ extern "C" int dl_attention_generic(const void* q, int q_stride, void* out, int 
                                     const void* k_pool, const void* v_pool, int n_pages,
                                     const int32_t* token_seq, const int32_t* token_pos,
                                     const int32_t* block_table, int bt_stride, int n_tokens, int nh, int nkv,
-                                    int hd, float scale, int window, void* stream) {
+                                    int hd, float scale, int window, float softcap, const float* slopes, void* stream) {
     DL_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0 && n_pages > 0, "attention: bad sizes");
     DL_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d KV heads", nh, nkv);
     DL_REQUIRE(hd <= AG_MAX_HD, "attention: head_dim %d exceeds the supported maximum %d", hd, AG_MAX_HD);
     DL_REQUIRE(q_stride >= nh * hd && out_stride >= nh * hd, "attention: row strides shorter than the rows");
     DL_REQUIRE(window >= 0, "attention: window must be 0 (none) or positive");
+    DL_REQUIRE(softcap >= 0.f, "attention: softcap must be 0 (none) or positive");
     if (n_tokens == 0) return DL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, (nh + AG_WARPS - 1) / AG_WARPS), block(32, AG_WARPS);
@@ -105,12 +115,12 @@ extern "C" int dl_attention_generic(const void* q, int q_stride, void* out, int 
     if (dtype == DL_F32)
         attention_generic_kernel<float><<<grid, block, smem, s>>>(
             (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
-            n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, scale, window);
+            n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd, scale, window, softcap, slopes);
     else if (dtype == DL_BF16)
         attention_generic_kernel<__nv_bfloat16><<<grid, block, smem, s>>>(
             (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, n_pages, token_seq, token_pos, block_table, bt_stride, nh, nkv, hd,
-            scale, window);
+            scale, window, softcap, slopes);
     else
         return dl_fail(DL_ERR_UNSUPPORTED, "attention: dtype %d", dtype);
     DL_CHECK_LAUNCH("attention_generic");

@@ -207,14 +207,30 @@ def _check_pools(k_pool, v_pool, n_kv_heads, head_dim):
 
 
 # ------------------------------------------------------------------ attention
+class ScoreHook:
+    """A change of the attention scores before the softmax: ``softcap`` > 0 turns a score s into
+    softcap * tanh(s / softcap); ``slopes`` (float32 [n_heads] on the device) then adds
+    slope * (key position - query position).  Only the generic kernel honours a hook: the
+    tensor-core kernels take none, so a mixer that sets one runs on the generic kernel."""
+
+    def __init__(self, softcap=0.0, slopes=None):
+        self.softcap = float(softcap)
+        self.slopes = slopes
+        if self.softcap < 0:
+            raise KernelError("a score hook's softcap must be 0 (none) or positive")
+
+    def __bool__(self):
+        return self.softcap > 0 or self.slopes is not None
+
+
 def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads,
-              head_dim, scale, window=0, plan=None):
+              head_dim, scale, window=0, plan=None, score_hook=None):
     """Causal attention of the step's tokens over their sequences' cached keys and values.
 
     q [T, nh*hd] (row-contiguous view); returns [T, nh*hd] of q's dtype.  ``window`` 0 means
     every earlier key; w > 0 means the last w keys.  ``plan`` carries the per-step layout
-    (sequence lengths, chunking) that the tensor-core kernels need; without one, or for sizes
-    they do not take, the generic kernel runs."""
+    (sequence lengths, chunking) that the tensor-core kernels need; without one, for sizes
+    they do not take, or with a ``score_hook``, the generic kernel runs."""
     _need_cuda(q, k_pool, v_pool, token_seq, token_pos, block_table)
     T = q.shape[0]
     qs = _rows_view(q, "attention q")
@@ -227,7 +243,13 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
     _int32(token_pos, "token_pos")
     _int32(block_table, "block_table")
     out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
-    if plan is not None and q.dtype == torch.bfloat16:
+    softcap, slopes = 0.0, None
+    if score_hook:
+        softcap, slopes = score_hook.softcap, score_hook.slopes
+        if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (n_heads,) or not slopes.is_contiguous()
+                                   or not slopes.is_cuda):
+            raise KernelError(f"attention: a score hook's slopes must be contiguous float32 [{n_heads}] on the device")
+    if plan is not None and q.dtype == torch.bfloat16 and not score_hook:
         from . import attention_fast
         if attention_fast.run(q, qs, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_table,
                               n_heads, n_kv_heads, head_dim, float(scale), int(window), plan):
@@ -235,17 +257,17 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
     _library.call("dl_attention_generic", _ptr(q), qs, _ptr(out), out.stride(0), _code(q.dtype),
                   _ptr(k_pool), _ptr(v_pool), n_pages, _ptr(token_seq), _ptr(token_pos),
                   _ptr(block_table), block_table.shape[1], T, n_heads, n_kv_heads, head_dim,
-                  float(scale), int(window), _stream())
+                  float(scale), int(window), float(softcap), _ptr(slopes), _stream())
     return out
 
 
 def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
-                         n_heads, n_kv_heads, head_dim, scale, window=0, plan=None):
+                         n_heads, n_kv_heads, head_dim, scale, window=0, plan=None, score_hook=None):
     """``rope_cache_write`` followed by ``attention`` (same arguments, same result).  A bfloat16
     decode step (one new token per sequence) with a full-width rotation of head size 64 or 128, or
     with no rotation, runs as one kernel that rotates q, puts the new keys and values into the
     cache and attends; everything else runs the two kernels one after the other."""
-    if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and k is not None:
+    if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and k is not None and not score_hook:
         from . import attention_fast
         out = attention_fast.decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_heads,
                                           n_kv_heads, head_dim, float(scale), int(window), plan)
@@ -254,7 +276,7 @@ def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, bl
     rope_cache_write(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
                      n_heads, n_kv_heads, head_dim, write_cache=k is not None)
     return attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
-                     scale, window, plan=plan)
+                     scale, window, plan=plan, score_hook=score_hook)
 
 
 # ---------------------------------------------------------------- feed-forward

@@ -26,13 +26,9 @@ class DecoderModel:
         self.blocks = []
         self._named_parts = [(spec.embedding.prefix, self.embedding)]
         for layer in spec.layers:
-            mixer = make_part("mixer", layer.mixer, h, runtime)
-            ffn = make_part("feed_forward", layer.feed_forward, h, runtime)
-            n1 = make_part("norm", layer.mixer_norm, h, runtime)
-            n2 = make_part("norm", layer.feed_forward_norm, h, runtime)
-            self.blocks.append(make_arrangement(layer.arrangement, mixer, ffn, n1, n2))
-            self._named_parts += [(layer.mixer_norm.prefix, n1), (layer.mixer.prefix, mixer),
-                                  (layer.feed_forward_norm.prefix, n2), (layer.feed_forward.prefix, ffn)]
+            built = {p.name: make_part(p.family, p.spec, h, runtime) for p in layer.parts}
+            self.blocks.append(make_arrangement(layer.arrangement, built))
+            self._named_parts += [(p.spec.prefix, built[p.name]) for p in layer.parts]
         self.final_norm = make_part("norm", spec.final_norm, h, runtime)
         self.head = make_part("head", spec.head, h, runtime)
         self._named_parts += [(spec.final_norm.prefix, self.final_norm), (spec.head.prefix, self.head)]
@@ -50,6 +46,13 @@ class DecoderModel:
             for local, spec in part.weight_specs().items():
                 expected[prefix + local] = spec
             optional |= {prefix + local for local in part.optional_names()}
+        for name, source in self.spec.shared_weights:
+            if name not in expected or source not in expected:
+                raise ValueError(f"shared weight {name!r} = {source!r}: both must be tensors that parts declare")
+            if tuple(expected[name].shape) != tuple(expected[source].shape) or expected[name].role != expected[source].role:
+                raise ValueError(f"shared weight {name!r} and {source!r} differ in shape or role")
+            del expected[name]                              # not looked for in a checkpoint ...
+            optional.add(name)                              # ... and a copy stored there is tolerated
         return expected, optional
 
     def convert(self, spec, tensor):
@@ -65,12 +68,17 @@ class DecoderModel:
 
     def bind(self, fetch):
         """Give every part its tensors.  ``fetch(full_name)`` returns the stored tensor."""
+        shared = dict(self.spec.shared_weights)
+        converted = {}                                      # full name -> tensor, so that a shared tensor is one object
+
+        def get(name, spec):
+            name = shared.get(name, name)
+            if name not in converted:
+                converted[name] = self.convert(spec, fetch(name))
+            return converted[name]
+
         for prefix, part in self._named_parts:
-            tensors = {local: self.convert(spec, fetch(prefix + local))
-                       for local, spec in part.weight_specs().items()}
-            part.bind(tensors)
-        if getattr(self.head, "tied", False):
-            self.head.tie(self.embedding.table)
+            part.bind({local: get(prefix + local, spec) for local, spec in part.weight_specs().items()})
         self.bound = True
 
     def weight_bytes_per_step(self):
@@ -80,7 +88,7 @@ class DecoderModel:
 
     # --------------------------------------------------------------- cache
     def cache_needs(self):
-        return [self.blocks[e.layer].mixer.cache_need() for e in self.spec.schedule]
+        return [self.blocks[e.layer].cache_need() for e in self.spec.schedule]
 
     def new_cache(self, max_tokens, max_sequences=None):
         return ModelCache(self.cache_needs(), [e.cache_of for e in self.spec.schedule], self.runtime,
@@ -89,7 +97,7 @@ class DecoderModel:
     # ------------------------------------------------------------- forward
     def forward(self, step, cache):
         """Logits float32 [wanted rows, vocab] of one step (see engine.step)."""
-        residual = self.embedding.forward(step.tokens)
+        residual = self.embedding.forward(step)
         pending = None
         for e, entry in enumerate(self.spec.schedule):
             view = cache.view(e, step.block_tables, step.slots)

@@ -12,7 +12,7 @@ from dataclasses import asdict
 
 from ..config.llama import LlamaConfig
 from ..config.registry import register_architecture
-from ..config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from ..config.spec import ModelSpec, PartSpec, ScheduleEntry, pre_norm_layer
 
 
 def build_llama_spec(cfg: LlamaConfig, norm_gain_init=("ones",)) -> ModelSpec:
@@ -24,8 +24,7 @@ def build_llama_spec(cfg: LlamaConfig, norm_gain_init=("ones",)) -> ModelSpec:
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        layers.append(LayerSpec(
-            arrangement="pre_norm",
+        layers.append(pre_norm_layer(
             mixer=PartSpec("attention", {"n_heads": cfg.num_attention_heads,
                                          "n_kv_heads": cfg.num_key_value_heads,
                                          "head_dim": cfg.head_dim, "window": None,
@@ -43,10 +42,11 @@ def build_llama_spec(cfg: LlamaConfig, norm_gain_init=("ones",)) -> ModelSpec:
         layers=tuple(layers),
         schedule=tuple(ScheduleEntry(i) for i in range(cfg.num_hidden_layers)),
         final_norm=PartSpec("rmsnorm", norm_params, "model.norm."),
-        head=PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "tied": cfg.tie_word_embeddings},
-                      "lm_head."),
+        head=PartSpec("linear_head", {"vocab_size": cfg.vocab_size}, "lm_head."),
         stop_token_ids=tuple(cfg.eos_token_id),
-        bos_token_id=cfg.bos_token_id)
+        bos_token_id=cfg.bos_token_id,
+        # src/DotLLM.Models/Architectures/TransformerWeights.cs:213-220: no output matrix, use the embedding's
+        shared_weights=(("lm_head.weight", "model.embed_tokens.weight"),) if cfg.tie_word_embeddings else ())
 
 
 register_architecture("LlamaForCausalLM", LlamaConfig, build_llama_spec, model_types=("llama",))

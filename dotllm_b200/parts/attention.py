@@ -24,7 +24,9 @@ BRANCH_DTYPE = torch.float32
 
 class AttentionMixer(Mixer):
     """params: ``n_heads``, ``n_kv_heads``, ``head_dim``, ``window`` (None = all keys),
-    ``position`` ({"kind", "params"} of a position encoding), optional ``scale``."""
+    ``position`` ({"kind", "params"} of a position encoding), optional ``scale``, optional ``score``
+    ({"softcap": c, "slopes": [one per head]}: scores are capped and biased by distance before the
+    softmax, which sends the mixer to the generic attention kernel)."""
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
@@ -38,6 +40,13 @@ class AttentionMixer(Mixer):
         pos = params.get("position") or {"kind": "none", "params": {}}
         self.position = make_part("position_encoding", PartSpec(pos["kind"], pos.get("params", {})),
                                   hidden_size, runtime)
+        score = params.get("score") or {}
+        slopes = score.get("slopes")
+        if slopes is not None and len(slopes) != self.n_heads:
+            raise ConfigError(f"score slopes: {len(slopes)} values for {self.n_heads} heads")
+        self.score_hook = ops.ScoreHook(score.get("softcap", 0.0),
+                                        None if slopes is None else torch.tensor(list(slopes), dtype=torch.float32,
+                                                                                 device=runtime.device))
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv_heads * self.head_dim
         self.w_qkv = None
@@ -81,7 +90,8 @@ class AttentionMixer(Mixer):
         a = ops.rope_cache_attention(q, k, v, cos, sin, rotary_dim, step.token_seq, step.token_pos,
                                      cache_view.block_table, cache_view.k, cache_view.v,
                                      self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
-                                     int(self.window or 0), plan=step.attention_plan)
+                                     int(self.window or 0), plan=step.attention_plan,
+                                     score_hook=self.score_hook if self.score_hook else None)
         return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
 
 

@@ -53,7 +53,10 @@ class CacheNeed:
     """What one execution of a mixer keeps per sequence.
 
     kind "kv": keys and values per token, ``n_kv_heads`` x ``head_dim`` each; ``window`` None
-    keeps every token, an integer keeps the last ``window``.
+    keeps every token, an integer keeps the last ``window``.  ``k_dim`` / ``v_dim`` give keys and
+    values widths of their own (a compressed or latent cache) and ``dtype`` a storage type of its own
+    (default: the run's); the built-in attention kernels take equal widths in the run's type, a mixer
+    with other needs reads and writes its pages itself.
     kind "state": a fixed-size tensor of ``state_shape`` / ``state_dtype`` per sequence, zero
     when the sequence starts.
     """
@@ -63,10 +66,19 @@ class CacheNeed:
     window: Optional[int] = None
     state_shape: tuple = ()
     state_dtype: torch.dtype = torch.float32
+    k_dim: Optional[int] = None
+    v_dim: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+
+    def key_width(self):
+        return self.k_dim or self.head_dim
+
+    def value_width(self):
+        return self.v_dim or self.head_dim
 
     def group_key(self, run_dtype):
         if self.kind == "kv":
-            return ("kv", self.n_kv_heads, self.head_dim, self.window, run_dtype)
+            return ("kv", self.n_kv_heads, self.key_width(), self.value_width(), self.window, self.dtype or run_dtype)
         return ("state", tuple(self.state_shape), self.state_dtype)
 
 
@@ -162,13 +174,24 @@ class FeedForward(Part):
 
 
 class Arrangement:
-    """How a layer's parts and the residual stream are wired."""
+    """How a layer's parts and the residual stream are wired.  ``parts`` maps the names of the
+    layer's description to the built parts; ``needs`` lists the names this arrangement cannot do
+    without.  ``cached_mixer`` names the part whose ``cache_need()`` the layer's cache is made for
+    (None: the layer keeps nothing)."""
+    needs = ()
+    cached_mixer = "mixer"
 
-    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+    def __init__(self, parts: dict):
+        lacking = [n for n in self.needs if n not in parts]
+        if lacking:
+            raise ConfigError(f"arrangement {type(self).__name__} needs parts {list(self.needs)}; the layer lacks {lacking}")
+        self.parts = dict(parts)
+        for name, part in parts.items():                    # the usual names as attributes
+            setattr(self, name, part)
+
+    def cache_need(self):
+        mixer = self.parts.get(self.cached_mixer) if self.cached_mixer else None
+        return mixer.cache_need() if mixer is not None else None
 
     def forward(self, residual, pending, step, cache_view):
         """Returns (residual, pending): the float32 stream and a branch output not yet added."""
@@ -232,11 +255,12 @@ def make_part(family, spec, hidden_size, runtime):
     return cls(spec.params, hidden_size, runtime)
 
 
-def make_arrangement(kind, mixer, feed_forward, mixer_norm, feed_forward_norm):
+def make_arrangement(kind, parts):
+    """``parts``: name -> built part, in the layer description's order."""
     _ensure_builtin()
     try:
         cls = _REGISTRIES["arrangement"][kind]
     except KeyError:
         raise ConfigError(f"no block arrangement {kind!r}; registered: "
                           f"{sorted(_REGISTRIES['arrangement'])}") from None
-    return cls(mixer, feed_forward, mixer_norm, feed_forward_norm)
+    return cls(parts)

@@ -12,6 +12,8 @@ from .base import Arrangement, normalised_for, register_arrangement
 
 
 class PreNormBlock(Arrangement):
+    needs = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+
     def forward(self, residual, pending, step, cache_view):
         n = normalised_for(self.mixer, self.mixer_norm, residual, pending)
         a = self.mixer.forward(n, step, cache_view)

@@ -27,32 +27,28 @@ class TokenEmbedding(Part):
     def bind(self, tensors):
         self.table = tensors["weight"].contiguous()
 
-    def forward(self, token_ids):
-        """int32 [T] -> float32 [T, H]: the start of the residual stream."""
-        return ops.gather_rows(self.table, token_ids)
+    def forward(self, step):
+        """The step's tokens (``step.tokens`` int32 [T]) -> float32 [T, H]: the start of the residual
+        stream.  An embedding gets the whole StepContext: one that also encodes positions reads
+        ``step.token_pos``."""
+        return ops.gather_rows(self.table, step.tokens)
 
 
 class LinearHead(Part):
-    """params: ``vocab_size``, ``tied`` (use the embedding table)."""
+    """params: ``vocab_size``.  Whether its matrix is the embedding table is the model description's
+    business (``ModelSpec.shared_weights``): the part is handed a [vocab, hidden] matrix either way."""
 
     def __init__(self, params, hidden_size, runtime):
         super().__init__(params, hidden_size, runtime)
         self.vocab_size = int(params["vocab_size"])
-        self.tied = bool(params.get("tied", False))
         self.weight = None
 
     def weight_specs(self):
-        return {} if self.tied else {"weight": WeightSpec((self.vocab_size, self.hidden_size))}
-
-    def optional_names(self):
-        return {"weight"} if self.tied else set()
+        return {"weight": WeightSpec((self.vocab_size, self.hidden_size))}
 
     def bind(self, tensors):
-        if not self.tied:
-            self.weight = tensors["weight"].contiguous()
-
-    def tie(self, table):
-        self.weight = table
+        w = tensors["weight"]
+        self.weight = w if w.is_contiguous() else w.contiguous()
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()

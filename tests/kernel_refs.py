@@ -62,7 +62,10 @@ def gather_kv(k_pool, v_pool, pages, length):
 
 
 def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads,
-              head_dim, scale, window=0, plan=None):
+              head_dim, scale, window=0, plan=None, score_hook=None):
+    if score_hook:
+        return _attention_with_hook(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim,
+                                    scale, window, score_hook)
     T = q.shape[0]
     out = torch.empty((T, n_heads * head_dim), dtype=torch.float32, device=q.device)
     for t in range(T):
@@ -79,6 +82,28 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
         # one query at the last of these keys: the causal mask hides nothing
         out[t] = plain_llama.causal_attention(q[t:t + 1].to(torch.float32), k, v, n_heads, n_kv_heads,
                                               scale, position_offset=len(ks) - 1)[0]
+    return out.to(q.dtype)
+
+
+def _attention_with_hook(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_kv_heads, head_dim, scale,
+                         window, hook):
+    """Scores capped (softcap * tanh(s / softcap)) and then biased by slope * (key - query position)."""
+    T = q.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.float32, device=q.device)
+    group = n_heads // n_kv_heads
+    for t in range(T):
+        pos = int(token_pos[t])
+        first = max(0, pos - window + 1) if window else 0
+        k, v = gather_kv(k_pool, v_pool, block_table[int(token_seq[t])], pos + 1)
+        for h in range(n_heads):
+            qh = q[t, h * head_dim:(h + 1) * head_dim].to(torch.float32)
+            s = (k[first:, h // group] @ qh) * scale
+            if hook.softcap > 0:
+                s = hook.softcap * torch.tanh(s / hook.softcap)
+            if hook.slopes is not None:
+                s = s + float(hook.slopes[h]) * (torch.arange(first, pos + 1, dtype=torch.float32) - pos)
+            w = torch.softmax(s, dim=0)
+            out[t, h * head_dim:(h + 1) * head_dim] = w @ v[first:, h // group]
     return out.to(q.dtype)
 
 

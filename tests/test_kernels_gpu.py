@@ -829,3 +829,27 @@ def test_attention_decode_long_runs(monkeypatch, blocks):
     close(fast, generic, 2 ** -9 * v_max + 1e-3, 2 ** -7)
     from dotllm_b200.kernels import library
     library.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_score_hook(dtype):
+    """Scores capped by softcap * tanh(s / softcap) and biased by a slope per head times the distance,
+    on the generic kernel (the tensor-core kernels take no hook: with one the op must not use them)."""
+    o = ops()
+    nh, nkv, hd = 4, 2, 32
+    lengths = [70, 5, 130]
+    k_pool, v_pool, table, _ = make_paged(3, lengths, nkv, hd, dtype, seed=31)
+    g = torch.Generator().manual_seed(32)
+    q = (torch.randn(3, nh * hd, generator=g) * 2).to(dtype)
+    seqs = torch.arange(3, dtype=torch.int32)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32)
+    slopes = torch.tensor([0.3, 0.0, 0.02, 1.0])
+    hook = o.ScoreHook(softcap=2.5, slopes=slopes.to(DEV))
+    plan = _decode_plan(lengths)                              # a plan is at hand: the hook alone keeps the fast kernels out
+    got = o.attention(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), seqs.to(DEV), pos.to(DEV), table.to(DEV), nh, nkv, hd,
+                      0.2, 0, plan=plan, score_hook=hook)
+    want = kernel_refs.attention(q, k_pool, v_pool, seqs, pos, table, nh, nkv, hd, 0.2, 0,
+                                 score_hook=o.ScoreHook(2.5, slopes))
+    close(got, want, 2e-5 if dtype == torch.float32 else 2e-2, 0.0)
+    plain = o.attention(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), seqs.to(DEV), pos.to(DEV), table.to(DEV), nh, nkv, hd, 0.2, 0)
+    assert float((plain.float() - got.float()).abs().max()) > 1e-2     # the hook does change the result

@@ -125,12 +125,12 @@ def test_embedding_and_head_parts(dtype):
     from dotllm_b200.config import PartSpec
     from dotllm_b200.parts import make_part
     emb = make_part("embedding", PartSpec("token_embedding", {"vocab_size": 300}), 48, runtime(dtype))
-    head = make_part("head", PartSpec("linear_head", {"vocab_size": 300, "tied": True}), 48, runtime(dtype))
+    from types import SimpleNamespace
+    head = make_part("head", PartSpec("linear_head", {"vocab_size": 300}), 48, runtime(dtype))
     w = bind_random(emb, 4, dtype)
-    head.bind({})
-    head.tie(emb.table)
+    head.bind({"weight": emb.table})                              # a tied head is handed the embedding's table
     ids = torch.tensor([0, 299, 5, 5], dtype=torch.int32)
-    h = emb.forward(ids.to(DEV))
+    h = emb.forward(SimpleNamespace(tokens=ids.to(DEV)))          # an embedding sees the step; this one reads its tokens
     assert h.dtype == torch.float32 and torch.equal(h.cpu(), w["weight"][ids.long()])
     logits = head.forward(h.to(dtype))
     want = w["weight"][ids.long()] @ w["weight"].T
@@ -233,7 +233,7 @@ class ToyConfig:
 
 
 def toy_spec(cfg):
-    from dotllm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from dotllm_b200.config import ModelSpec, PartSpec, ScheduleEntry, pre_norm_layer
     norm = lambda p: PartSpec("rmsnorm", {"eps": 1e-5, "gain_init": ("one_plus_uniform", 0.1)}, p)
     ffn = lambda p, i: PartSpec("gated_mlp", {"intermediate_size": i, "activation": "silu"}, p)
     attn = PartSpec("attention", {"n_heads": 3, "n_kv_heads": 1, "head_dim": 16, "window": 40,
@@ -241,13 +241,13 @@ def toy_spec(cfg):
                     "l0.attn.")
     decay = PartSpec("toy_decay", {"state_width": 24, "decay": 0.9}, "l1.mix.")
     routed = PartSpec("toy_routed", {"n_experts": 3, "inner": 40}, "l1.moe.")
-    layers = (LayerSpec("pre_norm", attn, ffn("l0.ffn.", 80), norm("l0.n1."), norm("l0.n2.")),
-              LayerSpec("pre_norm", decay, routed, norm("l1.n1."), norm("l1.n2.")))
+    layers = (pre_norm_layer(attn, ffn("l0.ffn.", 80), norm("l0.n1."), norm("l0.n2.")),
+              pre_norm_layer(decay, routed, norm("l1.n1."), norm("l1.n2.")))
     # layer 0, layer 1, layer 1 again (its own state), layer 0 again reading the first run's cache
     schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(0, cache_of=0))
     return ModelSpec("ToyForCausalLM", cfg.hidden_size, cfg.vocab_size, 512,
                      PartSpec("token_embedding", {"vocab_size": cfg.vocab_size}, "emb."), layers, schedule,
-                     norm("final."), PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "tied": False}, "head."))
+                     norm("final."), PartSpec("linear_head", {"vocab_size": cfg.vocab_size}, "head."))
 
 
 def toy_plain(w, tokens):
@@ -330,3 +330,179 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path):
     out = model.step(cache, [StepEntry(sc, b[:30], list(range(30)))])
     assert float((out.cpu() - rb[:30]).abs().max()) < 5e-5
     cache.check()
+
+
+# ------------------------------------------------------- a second toy: other shapes of layer and cache
+def second_toy_parts():
+    """Defined in the test, none of it in the package: a layer that is a mixer and nothing else (with
+    two norms around it), an embedding that adds a learned position row, a mixer whose cache holds
+    narrow latent keys and wide values in float32 whatever the run's type, and an attention mixer
+    with capped scores and a penalty per head that grows with distance."""
+    from dotllm_b200.kernels import ops
+    from dotllm_b200.parts import (Arrangement, CacheNeed, Mixer, Part, WeightSpec, register_arrangement,
+                                   register_embedding, register_mixer)
+
+    class MixerOnly(Arrangement):
+        """h = h + post(mixer(pre(h))): no feed-forward, a norm on either side of the mixer."""
+        needs = ("pre", "mixer", "post")
+
+        def forward(self, residual, pending, step, view):
+            if pending is not None:
+                residual += ops.resolve(pending).float()
+            branch = self.mixer.forward(self.pre.forward(residual), step, view)
+            return residual, self.post.forward(ops.resolve(branch).float().contiguous()).float()
+
+    class PositionedEmbedding(Part):
+        """h[t] = E[token[t]] + P[position[t]]: needs the step's positions, not only its tokens."""
+
+        def weight_specs(self):
+            return {"tokens.weight": WeightSpec((int(self.params["vocab_size"]), self.hidden_size)),
+                    "positions.weight": WeightSpec((int(self.params["max_positions"]), self.hidden_size))}
+
+        def bind(self, tensors):
+            self.tokens, self.positions = tensors["tokens.weight"], tensors["positions.weight"]
+
+        def forward(self, step):
+            return ops.gather_rows(self.tokens, step.tokens) + ops.gather_rows(self.positions, step.token_pos)
+
+    class LatentMixer(Mixer):
+        """One head; keys are 8 numbers a token, values 24, kept in float32 pages.  Causal softmax
+        attention over the latent keys, read and written by the mixer itself (plain tensor code)."""
+
+        def weight_specs(self):
+            h = self.hidden_size
+            return {"q.weight": WeightSpec((8, h)), "k.weight": WeightSpec((8, h)), "v.weight": WeightSpec((24, h)),
+                    "o.weight": WeightSpec((h, 24))}
+
+        def bind(self, tensors):
+            self.w = {k.split(".")[0]: v.float() for k, v in tensors.items()}
+
+        def cache_need(self):
+            return CacheNeed("kv", n_kv_heads=1, head_dim=8, k_dim=8, v_dim=24, dtype=torch.float32)
+
+        def forward(self, x, step, view):
+            assert view.k.dtype == torch.float32 and view.k.shape[1:] == (1, 64, 8) and view.v.shape[1:] == (1, 24, 64)
+            xf = x.float()
+            q, k, v = xf @ self.w["q"].T, xf @ self.w["k"].T, xf @ self.w["v"].T
+            seqs, poss, table = step.token_seq.tolist(), step.token_pos.tolist(), view.block_table.tolist()
+            out = torch.empty(x.shape[0], 24, device=x.device)
+            for t, (b, pos) in enumerate(zip(seqs, poss)):
+                view.k[table[b][pos // 64], 0, pos % 64] = k[t]
+                view.v[table[b][pos // 64], 0, :, pos % 64] = v[t]
+                keys = torch.stack([view.k[table[b][j // 64], 0, j % 64] for j in range(pos + 1)])
+                vals = torch.stack([view.v[table[b][j // 64], 0, :, j % 64] for j in range(pos + 1)])
+                out[t] = torch.softmax(keys @ q[t] * 0.5, dim=0) @ vals
+            return out @ self.w["o"].T
+
+    register_arrangement("toy_mixer_only", MixerOnly)
+    register_embedding("toy_positioned", PositionedEmbedding)
+    register_mixer("toy_latent", LatentMixer)
+
+
+@dataclass(frozen=True)
+class SecondToyConfig:
+    vocab_size: int = 61
+    hidden_size: int = 32
+    architecture: str = "SecondToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(int(d["vocab_size"]), int(d["hidden_size"]))
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size}
+
+
+SLOPES = (0.5, 0.05)
+
+
+def second_toy_spec(cfg):
+    from dotllm_b200.config import LayerPart, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, pre_norm_layer
+    norm = lambda p: PartSpec("rmsnorm", {"eps": 1e-6, "gain_init": ("one_plus_uniform", 0.2)}, p)
+    latent = LayerSpec("toy_mixer_only", (LayerPart("pre", "norm", norm("a.pre.")),
+                                          LayerPart("mixer", "mixer", PartSpec("toy_latent", {}, "a.mix.")),
+                                          LayerPart("post", "norm", norm("a.post."))))
+    capped = pre_norm_layer(PartSpec("attention", {"n_heads": 2, "n_kv_heads": 2, "head_dim": 16, "window": None, "position": None,
+                                                   "score": {"softcap": 3.0, "slopes": SLOPES}}, "b.attn."),
+                            PartSpec("gated_mlp", {"intermediate_size": 56, "activation": "silu"}, "b.ffn."),
+                            norm("b.n1."), norm("b.n2."))
+    return ModelSpec("SecondToyForCausalLM", cfg.hidden_size, cfg.vocab_size, 200,
+                     PartSpec("toy_positioned", {"vocab_size": cfg.vocab_size, "max_positions": 200}, "emb."),
+                     (latent, capped), (ScheduleEntry(0), ScheduleEntry(1)), norm("final."),
+                     PartSpec("linear_head", {"vocab_size": cfg.vocab_size}, "head."),
+                     shared_weights=(("head.weight", "emb.tokens.weight"),))      # the head's matrix is the token table
+
+
+def second_toy_plain(w, tokens):
+    n = len(tokens)
+    pos = torch.arange(n)
+    h = w["emb.tokens.weight"][torch.tensor(tokens)] + w["emb.positions.weight"][pos]
+    x = plain_llama.rms_norm(h, w["a.pre.weight"], 1e-6)
+    q, k, v = x @ w["a.mix.q.weight"].T, x @ w["a.mix.k.weight"].T, x @ w["a.mix.v.weight"].T
+    s = (q @ k.T) * 0.5
+    s = s.masked_fill(pos[None, :] > pos[:, None], float("-inf"))
+    h = h + plain_llama.rms_norm(torch.softmax(s, dim=1) @ v @ w["a.mix.o.weight"].T, w["a.post.weight"], 1e-6)
+    x = plain_llama.rms_norm(h, w["b.n1.weight"], 1e-6)
+    q, k, v = (x @ w[f"b.attn.{n_}_proj.weight"].T for n_ in "qkv")
+    heads = []
+    for hd in range(2):
+        sl = slice(16 * hd, 16 * hd + 16)
+        s = (q[:, sl] @ k[:, sl].T) * 0.25
+        s = 3.0 * torch.tanh(s / 3.0) + SLOPES[hd] * (pos[None, :] - pos[:, None]).float()
+        s = s.masked_fill(pos[None, :] > pos[:, None], float("-inf"))
+        heads.append(torch.softmax(s, dim=1) @ v[:, sl])
+    h = h + torch.cat(heads, dim=1) @ w["b.attn.o_proj.weight"].T
+    x = plain_llama.rms_norm(h, w["b.n2.weight"], 1e-6)
+    h = h + plain_llama.swiglu(x @ w["b.ffn.gate_proj.weight"].T, x @ w["b.ffn.up_proj.weight"].T) @ w["b.ffn.down_proj.weight"].T
+    return plain_llama.rms_norm(h, w["final.weight"], 1e-6) @ w["emb.tokens.weight"].T
+
+
+def test_second_toy_other_layer_shapes_cache_widths_and_score_hook(tmp_path):
+    """A mixer-only layer with norms of its own names, an embedding that reads positions, a cache
+    group with narrow keys, wide values and its own storage type, scores capped and biased before
+    the softmax, and a head that shares the embedding's matrix through the description: all of it
+    registered, built, loaded and stepped (prompt, then token by token, two sequences) without a
+    change to the package, and equal to plain code."""
+    from dotllm_b200 import Model, StepEntry
+    from dotllm_b200.config import register_architecture
+    from dotllm_b200.weights import write_random_model
+    second_toy_parts()
+    register_architecture("SecondToyForCausalLM", SecondToyConfig, second_toy_spec)
+    folder = write_random_model(tmp_path / "toy2", SecondToyConfig(), seed=4, dtype=torch.float32)
+    _, w = plain_llama.read_model_folder(folder)
+    assert "head.weight" not in w                                       # a shared tensor is stored once
+    for dtype, bound in (("float32", 5e-5), ("bfloat16", 6e-2)):
+        model = Model.load(folder, dtype=dtype)
+        assert model.decoder.head.weight is model.decoder.embedding.tokens
+        cache = model.new_cache(64 * 8, max_sequences=2)
+        latent = [g for g in cache.kv_groups if g.k.shape[-1] == 8][0]
+        assert latent.k.dtype == torch.float32 and latent.v.shape[-2] == 24 and latent.bytes_per_token() == 4 * 32
+        a, b = tiny_models.random_tokens(90, 61, 11), tiny_models.random_tokens(70, 61, 12)
+        ra, rb = second_toy_plain(w, a), second_toy_plain(w, b)
+        sa, sb = cache.open_sequence(), cache.open_sequence()
+        got_a = [model.step(cache, [StepEntry(sa, a[:70], list(range(70))), StepEntry(sb, b[:50], [49])])[:70]]
+        got_b = []
+        for t in range(20):
+            out = model.step(cache, [StepEntry(sb, [b[50 + t]]), StepEntry(sa, [a[70 + t]])])
+            got_b.append(out[:1])
+            got_a.append(out[1:2])
+        assert float((torch.cat(got_a).cpu() - ra).abs().max()) < bound
+        assert float((torch.cat(got_b).cpu() - rb[50:70]).abs().max()) < bound
+        cache.close_sequence(sa)
+        cache.close_sequence(sb)
+        cache.check()
+
+
+def test_random_model_in_memory_equals_the_folder_it_would_write(tmp_path):
+    """Model.random(config, seed) and write_random_model(config, seed) loaded back are the same model."""
+    from dotllm_b200 import Model
+    from dotllm_b200.config import config_from_dict
+    from dotllm_b200.weights import write_random_model
+    cfg = config_from_dict(tiny_models.TINY_B)
+    for dtype in (torch.bfloat16, torch.float32):
+        folder = write_random_model(tmp_path / f"b_{dtype}", cfg, seed=9, dtype=dtype)
+        loaded, made = Model.load(folder, dtype=dtype), Model.random(cfg, seed=9, dtype=dtype)
+        for (_, p), (_, q) in zip(loaded.decoder.named_parts(), made.decoder.named_parts()):
+            for name, value in vars(p).items():
+                if isinstance(value, torch.Tensor):
+                    assert torch.equal(value, getattr(q, name)), name
