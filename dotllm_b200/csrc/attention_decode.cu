@@ -456,6 +456,28 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
             float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;   // maxima in units of log2
 
             const int i_first = ((warp - n0) % n_stages + n_stages) % n_stages;   // first i with (n0 + i) % n_stages == warp
+            // The warp that will meet the page of the step's own token asks for that token's key, value
+            // and table rows now, so that they are in registers when the page arrives.
+            const int i_new = fresh.k != nullptr ? (w.len - 1) / DL_PAGE - w.page0 : -1;
+            const bool mine_new = i_new >= 0 && i_new < w.n_pages && (n0 + i_new) % n_stages == warp;
+            uint2 kn_lo = make_uint2(0u, 0u), kn_hi = make_uint2(0u, 0u);
+            float4 kn_c = make_float4(1.f, 1.f, 1.f, 1.f), kn_s = make_float4(0.f, 0.f, 0.f, 0.f);
+            __nv_bfloat16 vn_r[HD / 32];
+            if (mine_new) {
+                const __nv_bfloat16* kn = fresh.k + (size_t)w.b * fresh.k_stride + (size_t)w.kvh * HD;
+                const __nv_bfloat16* vn = fresh.v + (size_t)w.b * fresh.v_stride + (size_t)w.kvh * HD;
+                const int pos = min(w.len - 1, fresh.table_rows - 1);
+                if (lane * 4 < HD / 2) {                         // four rotation pairs per lane (HD <= 256)
+                    kn_lo = *reinterpret_cast<const uint2*>(kn + lane * 4);
+                    kn_hi = *reinterpret_cast<const uint2*>(kn + HD / 2 + lane * 4);
+                    if (fresh.rotate) {
+                        kn_c = *reinterpret_cast<const float4*>(fresh.cos_t + (size_t)pos * (HD / 2) + lane * 4);
+                        kn_s = *reinterpret_cast<const float4*>(fresh.sin_t + (size_t)pos * (HD / 2) + lane * 4);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < HD / 32; ++j) vn_r[j] = vn[lane + 32 * j];
+            }
             for (int i = i_first; i < w.n_pages; i += n_stages) {
                 const int n = n0 + i;
                 const int s = warp;
@@ -473,17 +495,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                     // (rotated) key and the value there, in the stage and in the cache.
                     const int in_page = (w.len - 1) - base;
                     const int page = block_table[(size_t)w.b * bt_stride + (w.len - 1) / DL_PAGE];
-                    const __nv_bfloat16* kn = fresh.k + (size_t)w.b * fresh.k_stride + (size_t)w.kvh * HD;
-                    const __nv_bfloat16* vn = fresh.v + (size_t)w.b * fresh.v_stride + (size_t)w.kvh * HD;
-                    const int pos = min(w.len - 1, fresh.table_rows - 1);
-                    for (int i4 = lane * 4; i4 < HD / 2; i4 += 128) {            // four rotation pairs per lane
+                    if (lane * 4 < HD / 2) {
+                        const int i4 = lane * 4;
                         __nv_bfloat16 lo[4], hi[4];
-                        *reinterpret_cast<uint2*>(lo) = *reinterpret_cast<const uint2*>(kn + i4);
-                        *reinterpret_cast<uint2*>(hi) = *reinterpret_cast<const uint2*>(kn + HD / 2 + i4);
+                        *reinterpret_cast<uint2*>(lo) = kn_lo;
+                        *reinterpret_cast<uint2*>(hi) = kn_hi;
                         if (fresh.rotate) {
-                            const float4 c = *reinterpret_cast<const float4*>(fresh.cos_t + (size_t)pos * (HD / 2) + i4);
-                            const float4 sn = *reinterpret_cast<const float4*>(fresh.sin_t + (size_t)pos * (HD / 2) + i4);
-                            const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+                            const float cc[4] = {kn_c.x, kn_c.y, kn_c.z, kn_c.w}, ss[4] = {kn_s.x, kn_s.y, kn_s.z, kn_s.w};
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const float f0 = __bfloat162float(lo[e]), f1 = __bfloat162float(hi[e]);
@@ -499,19 +517,28 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                             *reinterpret_cast<uint2*>(kg + HD / 2 + i4) = *reinterpret_cast<uint2*>(hi);
                         }
                     }
-                    for (int d = lane; d < HD; d += 32) {
-                        const __nv_bfloat16 val = vn[d];
-                        vp[d * DL_PAGE + in_page] = val;
-                        if (page >= 0 && page < n_pages) v_pool[dl_v_offset(page, nkv, w.kvh, d, HD) + in_page] = val;
+#pragma unroll
+                    for (int j = 0; j < HD / 32; ++j) {
+                        const int d = lane + 32 * j;
+                        vp[d * DL_PAGE + in_page] = vn_r[j];
+                        if (page >= 0 && page < n_pages) v_pool[dl_v_offset(page, nkv, w.kvh, d, HD) + in_page] = vn_r[j];
                     }
                     __syncwarp();
                 }
                 if (ragged) {
                     // Keys outside [first, len) may hold anything (even NaN): make their values exact
                     // zeros in the stage once, so that the product below needs no special case.
-                    for (int idx = lane; idx < HD * DL_PAGE; idx += 32) {
-                        const int key = base + (idx & (DL_PAGE - 1));
-                        if (key < w.first_key || key >= w.len) vp[idx] = __float2bfloat16_rn(0.f);
+                    // The invalid keys are a run at the page's start (older than the window) and a run at
+                    // its end (beyond the sequence): each lane clears those runs in its rows of V, eight
+                    // keys (16 bytes) at a time where a run covers whole groups of eight.
+                    const int lo_end = min(DL_PAGE, max(0, w.first_key - base));       // keys [0, lo_end) are too old
+                    const int hi_begin = max(0, min(DL_PAGE, w.len - base));             // keys [hi_begin, 64) do not exist yet
+                    for (int d = lane; d < HD; d += 32) {
+                        __nv_bfloat16* row = vp + d * DL_PAGE;
+                        for (int k = 0; k < lo_end; ++k) row[k] = __float2bfloat16_rn(0.f);
+                        int k = hi_begin;
+                        for (; k < DL_PAGE && (k & 7); ++k) row[k] = __float2bfloat16_rn(0.f);
+                        for (; k < DL_PAGE; k += 8) *reinterpret_cast<uint4*>(row + k) = make_uint4(0u, 0u, 0u, 0u);
                     }
                     __syncwarp();
                 }
@@ -687,20 +714,34 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
 
             const int tid = threadIdx.x;                     // 0 .. 32*n_stages-1
             const size_t part_row = ((size_t)blockIdx.x * 2 + w.slot) * group;
-            for (int idx = tid; idx < group * HD; idx += 32 * n_stages) {
-                const int r = idx / HD, d = idx - r * HD;
+            // thread -> (row of the group, four dims): the warps' factors once per thread, float4 loads
+            for (int idx = tid; idx < group * (HD / 4); idx += 32 * n_stages) {
+                const int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
                 float m = -INFINITY;
-                for (int cw = 0; cw < n_stages; ++cw) m = fmaxf(m, sm_m[cw][r]);
-                float acc = 0.f, l = 0.f;
-                for (int cw = 0; cw < n_stages; ++cw) {
-                    const float f = (sm_m[cw][r] == -INFINITY) ? 0.f : ad_ex2(sm_m[cw][r] - m);
-                    acc += merge_o[((size_t)cw * group + r) * (HD + 4) + d] * f;
-                    l += sm_l[cw][r] * f;
+#pragma unroll
+                for (int cw = 0; cw < AD_MAX_STAGES; ++cw)
+                    if (cw < n_stages) m = fmaxf(m, sm_m[cw][r]);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float l = 0.f;
+#pragma unroll
+                for (int cw = 0; cw < AD_MAX_STAGES; ++cw) {  // warp order: fixed
+                    if (cw < n_stages) {
+                        const float f = (sm_m[cw][r] == -INFINITY) ? 0.f : ad_ex2(sm_m[cw][r] - m);
+                        const float4 o4 = *reinterpret_cast<const float4*>(merge_o + ((size_t)cw * group + r) * (HD + 4) + d);
+                        acc.x += o4.x * f, acc.y += o4.y * f, acc.z += o4.z * f, acc.w += o4.w * f;
+                        l += sm_l[cw][r] * f;
+                    }
                 }
                 if (w.whole) {
-                    out[(size_t)w.b * out_stride + (size_t)(w.kvh * group + r) * HD + d] = __float2bfloat16_rn(acc / l);
+                    const float inv = 1.f / l;
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                    uint2 packed;
+                    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(out + (size_t)w.b * out_stride + (size_t)(w.kvh * group + r) * HD + d) = packed;
                 } else {
-                    part_o[(part_row + r) * HD + d] = acc;
+                    *reinterpret_cast<float4*>(part_o + (part_row + r) * HD + d) = acc;
                     if (d == 0) {
                         part_ml[(part_row + r) * 2] = m;
                         part_ml[(part_row + r) * 2 + 1] = l;
