@@ -286,7 +286,8 @@ def main():
         return cfg.num_hidden_layers * per_layer + 2 * rows_out * cfg.hidden_size * vocab
 
     def prefill_point():
-        """One prompt of PREFILL_TOKENS tokens through model.step: best of ``reps`` after three warm-ups."""
+        """One prompt of PREFILL_TOKENS tokens through model.step: best of ``reps`` after three warm-ups
+        (the first is eager, the second captures the step's graph, the rest replay it)."""
         import numpy as np
         prompt = np.asarray(torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen))
         times = []
@@ -295,7 +296,7 @@ def main():
             torch.cuda.synchronize()
             a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            model.step(cache, [StepEntry(s, prompt)])
+            model.step(cache, [StepEntry(s, prompt)], graphs=True)       # the step's shape repeats: replayed from its graph
             b_.record()
             torch.cuda.synchronize()
             if it >= 3:

@@ -64,12 +64,25 @@ class StepContext:
     seq_start: torch.Tensor       # int32 [B]
     seq_new: torch.Tensor         # int32 [B]
     cu_new: torch.Tensor          # int32 [B+1]
+    packed: Optional[torch.Tensor] = None     # the one int32 device buffer all of the above are views of
 
 
-def plan_step(entries, cache, vocab_size, max_positions, device):
+def shape_key(entries, cache):
+    """What two steps must share for one captured graph to serve both: how many tokens each sequence
+    brings, where it starts, which rows are wanted, and how many pages each block table is wide after
+    the step (launch shapes depend on all of these; the tokens, slots and page ids do not enter)."""
+    news = tuple(len(e.tokens) for e in entries)
+    starts = tuple(e.sequence.length for e in entries)
+    wants = tuple(None if e.want is None else tuple(int(w) for w in e.want) for e in entries)
+    widths = tuple(max(1, max((s + n + 63) // 64 for s, n in zip(starts, news))) for _ in cache.kv_groups)
+    return news, starts, wants, widths
+
+
+def plan_step(entries, cache, vocab_size, max_positions, device, into=None):
     """Validate the entries, reserve cache room, and build the device-side description with one
     host-to-device copy.  Returns (StepContext, new lengths).  Per-token work is done on arrays, not
-    in Python loops: a step may bring tens of thousands of prompt tokens."""
+    in Python loops: a step may bring tens of thousands of prompt tokens.  ``into``: an int32 device
+    buffer of exactly the description's size that receives it instead of a fresh one."""
     if not entries:
         raise StepError("a step needs at least one sequence")
     B = len(entries)
@@ -135,7 +148,15 @@ def plan_step(entries, cache, vocab_size, max_positions, device):
     for p, n in zip(parts, sizes):
         view[at:at + n] = p
         at += n
-    dev = host.to(device, non_blocking=True)
+    if into is not None:
+        # a captured step: the description goes into the buffer its graph reads (same layout: the
+        # caller keys its graphs by `shape_key`)
+        if into.numel() != host.numel():
+            raise StepError("a captured step's buffer does not fit this step's description")
+        into.copy_(host, non_blocking=True)
+        dev = into
+    else:
+        dev = host.to(device, non_blocking=True)
     views = []
     at = 0
     for n in sizes:
@@ -150,7 +171,7 @@ def plan_step(entries, cache, vocab_size, max_positions, device):
     ctx = StepContext(n_tokens=T, n_seqs=B, tokens=d_tokens, token_seq=d_seq, token_pos=d_pos,
                       slots=d_slots, block_tables=block_tables, want_rows=d_want, n_wanted=R,
                       want_all=bool(R == T and np.array_equal(want_rows, np.arange(T))), attention_plan=plan,
-                      seq_start=d_starts, seq_new=d_news, cu_new=d_cu)
+                      seq_start=d_starts, seq_new=d_news, cu_new=d_cu, packed=dev)
     return ctx, totals.tolist()
 
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from .config.registry import build_spec, load_config
-from .engine.decode_graph import DecodeGraphs
+from .engine.decode_graph import DecodeGraphs, StepGraphs
 from .engine.generate import TextGenerator
 from .engine.step import StepEntry, run_step
 from .errors import ConfigError, KernelError
@@ -131,13 +131,16 @@ class Model:
         Returns float32 logits [wanted, vocab].
 
         With ``graphs`` a step that brings one token per sequence and wants each one's logits is
-        replayed as a CUDA graph (captured once per batch size); the returned tensor is then a
-        buffer that the next such step overwrites."""
+        replayed as a CUDA graph (captured once per batch size), and any other step is replayed from a
+        graph of its exact shape once that shape has been seen twice (prompts of equal lengths, chunks
+        of a fixed size); the returned tensor is then a buffer that the next such step overwrites."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if graphs:
             runner = self.decode_graphs(cache)
             if runner.takes(entries):
-                return runner.run(entries)
+                # graphs="lazy": a batch size earns its graph by coming eight times (the generation loop's choice)
+                return runner.run(entries, capture_after=8 if graphs == "lazy" else 0)
+            return self.step_graphs(cache).run(entries)
         return run_step(self.decoder, cache, entries)
 
     def decode_graphs(self, cache):
@@ -148,11 +151,19 @@ class Model:
             cache._decode_graphs = runner
         return runner
 
+    def step_graphs(self, cache):
+        """The captured steps of other shapes that belong to ``cache``."""
+        runner = getattr(cache, "_step_graphs", None)
+        if runner is None or runner.model is not self.decoder:
+            runner = StepGraphs(self.decoder, cache)
+            cache._step_graphs = runner
+        return runner
+
     def generator(self, cache=None, max_tokens=None, max_batch=None, use_graphs=True):
         """A TextGenerator over this model.  Without a cache one is made for ``max_tokens``."""
         if cache is None:
             cache = self.new_cache(max_tokens or min(self.spec.max_positions * 8, 1 << 16))
-        return TextGenerator(lambda entries: self.step(cache, entries, graphs=use_graphs), sample_rows, cache,
+        return TextGenerator(lambda entries: self.step(cache, entries, graphs="lazy" if use_graphs else False), sample_rows, cache,
                              max_positions=self.spec.max_positions, vocab_size=self.spec.vocab_size,
                              default_stop_ids=self.spec.stop_token_ids, bos_token_id=self.spec.bos_token_id,
                              max_batch=max_batch, fetch=_IdFetcher(self.runtime.device), clock=_EventClock())

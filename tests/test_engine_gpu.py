@@ -457,3 +457,35 @@ def test_two_layers_at_the_benchmark_models_sizes(tmp_path):
             if dtype == torch.float32:
                 assert [int(r.argmax()) for r in ref] == cont, f"request {i}: greedy tokens differ from the plain arg-max"
         print(f"real sizes {dtype}: max |logit difference| {worst:.3e}")
+
+
+def test_prompt_steps_replayed_from_graphs_of_their_shape(tmp):
+    """A step of any shape is captured when its shape comes a second time and replayed from then on:
+    the same bits as eager steps (float32), for other tokens, other slots and other pages than the
+    captured ones, with the least recently used graph dropped beyond the capacity."""
+    from dotllm_b200 import StepEntry
+    model, cfg, _, _ = load_pair(tmp, "B", torch.float32)
+    vocab = cfg["vocab_size"]
+
+    def run(graphs):
+        cache = model.new_cache(max_tokens=2048)
+        outs = []
+        for rnd in range(4):                                 # the same two shapes four times, with other tokens
+            seqs = [cache.open_sequence() for _ in range(3)]
+            if rnd % 2:
+                seqs = seqs[::-1]                            # other slots and pages under the same shape
+            prompts = [tiny_models.random_tokens(n, vocab, seed=1000 + 10 * rnd + i) for i, n in enumerate((70, 9, 33))]
+            outs.append(model.step(cache, [StepEntry(s, p, [0, len(p) - 1]) for s, p in zip(seqs, prompts)], graphs=graphs).clone())
+            chunk = [tiny_models.random_tokens(16, vocab, seed=2000 + 10 * rnd + i) for i in range(3)]
+            outs.append(model.step(cache, [StepEntry(s, c) for s, c in zip(seqs, chunk)], graphs=graphs).clone())
+            outs.append(model.step(cache, [StepEntry(s, [c[0]]) for s, c in zip(seqs, chunk)], graphs=graphs).clone())
+            for s in seqs:
+                cache.close_sequence(s)
+        cache.check()
+        if graphs:
+            g = model.step_graphs(cache)
+            assert g.captures == 2 and g.replays == 4        # each shape: eager, captured, replayed twice
+        return torch.cat(outs)
+
+    eager, graphed = run(False), run(True)
+    assert torch.equal(eager, graphed), f"max diff {(eager - graphed).abs().max()}"
