@@ -455,6 +455,23 @@ def unequal_workload(args, model, cache, cfg, gen, pk, shape_name, dtype_name, c
     return 0
 
 
+def cpp_model_tokens_per_second(tmp, folder, cfg, tokens):
+    """The one-file C++ float32 model under tests/cpu_reference, compiled here and timed on one prompt."""
+    import shutil
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        return None
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from test_cpu_reference import SOURCE, arguments
+    exe = tmp / "llama_f32"
+    if subprocess.run([cxx, "-O2", "-std=c++17", "-o", str(exe), str(SOURCE)], capture_output=True).returncode != 0:
+        return None
+    (tmp / "tokens.txt").write_text(" ".join(str(t) for t in tokens))
+    res = subprocess.run([str(exe), str(folder / "model.safetensors"), str(tmp / "tokens.txt"), str(tmp / "out.f32"), *arguments(cfg)],
+                         capture_output=True, text=True)
+    return json.loads(res.stdout)["tokens_per_second"] if res.returncode == 0 else None
+
+
 def plain_cpu_baseline():
     """The plain implementation (tests/plain_llama.py, float32, PyTorch on the host's cores) timed on the
     tiny test models and on a short prompt through one Llama-3.2-1B-shaped layer stack: the CPU line
@@ -483,6 +500,9 @@ def plain_cpu_baseline():
                 plain_llama.greedy_generate(cfg, weights, p, n_new)
             out["cells"][f"tiny_{which}"] = {"prefill_tok_s": round(sum(lens) / prefill_s, 1),
                                              "generate_tok_s_no_cache": round(len(lens) * n_new / (time.perf_counter() - t0), 1)}
+            cpp = cpp_model_tokens_per_second(Path(tmp), folder, cfg, prompts[-1])
+            if cpp is not None:
+                out["cells"][f"tiny_{which}"]["cpp_f32_prefill_tok_s"] = cpp
         one_b = dict(LLAMA_32_1B, num_hidden_layers=2, max_position_embeddings=4096)
         folder = write_random_model(Path(tmp) / "1b", config_from_dict(one_b), seed=0, dtype=torch.bfloat16)
         cfg, weights = plain_llama.read_model_folder(folder)
