@@ -71,9 +71,10 @@ def gather_rows(table, ids, out=None):
 
 # ------------------------------------------------- products not yet launched
 class PendingProduct:
-    """x W^T of a decode step that ``linear(..., lazy=True)`` has not launched yet.  Given to
-    ``add_rmsnorm`` as the delta, the product itself adds its result into the stream; anyone else
-    calls ``tensor()`` (or ``resolve``) and gets the plain float32 product."""
+    """x W^T (float32 result of bfloat16 operands) that ``linear(..., lazy=True)`` has not launched
+    yet.  Given to ``add_rmsnorm`` as the delta, the product itself adds its result into the stream
+    (the decode kernels in their epilogue, the library product as its accumulate operand); anyone
+    else calls ``tensor()`` (or ``resolve``) and gets the plain float32 product."""
 
     def __init__(self, x, w, resident):
         self.x, self.w, self.resident = x, w, resident
@@ -81,6 +82,20 @@ class PendingProduct:
 
     def tensor(self):
         return linear(self.x, self.w, out_dtype=torch.float32, resident=self.resident)
+
+    def add_into(self, residual):
+        """residual += x W^T by the library product with the stream as its accumulate operand (one
+        rounding of accumulator + stream, as the separate addition has; no [T, N] product is
+        written and read back).  False when the sizes belong to the decode kernels or the
+        tensors do not fit; nothing has happened then."""
+        from . import gemm_skinny
+        x = self.x
+        if isinstance(x, ScaledRows) or x.dtype != torch.bfloat16 or not x.is_cuda or x.dim() != 2 \
+                or residual.dtype != torch.float32 or not residual.is_contiguous() \
+                or tuple(residual.shape) != self.shape or gemm_skinny.takes(x, self.w):
+            return False
+        torch.addmm(residual, x, self.w.t(), out_dtype=torch.float32, out=residual)
+        return True
 
 
 class ScaledRows:
@@ -120,7 +135,7 @@ def add_rmsnorm(residual, delta, gain, eps, out_dtype, lazy=False):
         fused = _add_product_scaled(residual, delta, gain, eps, out_dtype) if lazy else None
         if fused is not None:
             return fused
-        delta = delta.tensor()
+        delta = None if delta.add_into(residual) else delta.tensor()
     _need_cuda(residual, delta, gain)
     if residual.dtype != torch.float32 or residual.dim() != 2 or not residual.is_contiguous():
         raise KernelError("rmsnorm: the residual stream must be contiguous float32 [T, H]")
@@ -298,7 +313,7 @@ def swiglu(gate_up):
 def linear(x, w, out_dtype=None, resident=False, lazy=False):
     """y = x W^T for W [N, K].  ``resident``: the caller vouches that nothing still pending on the
     stream writes W (a model's weights), which lets the decode kernel start streaming W while
-    the kernel before it finishes.  ``lazy`` (float32 results of a few bfloat16 rows): return a
+    the kernel before it finishes.  ``lazy`` (float32 results of bfloat16 rows): return a
     PendingProduct, for a caller whose result goes to ``add_rmsnorm`` as the delta.  x may be a
     ScaledRows.
 
@@ -320,12 +335,11 @@ def linear(x, w, out_dtype=None, resident=False, lazy=False):
     out_dtype = out_dtype or x.dtype
     M, K = x.shape
     N = w.shape[0]
-    if rows is not None or (lazy and out_dtype == torch.float32 and M > 0):
+    if lazy and out_dtype == torch.float32 and x.dtype == torch.bfloat16 and M > 0:
+        return PendingProduct(given, w, resident)
+    if rows is not None:
         from . import gemm_skinny
-        if lazy and out_dtype == torch.float32 and gemm_skinny.takes(x, w):
-            return PendingProduct(given, w, resident)
-        if rows is not None:
-            return gemm_skinny.run(x, w, out_dtype, resident=resident, row_sums=rows)
+        return gemm_skinny.run(x, w, out_dtype, resident=resident, row_sums=rows)
     if x.dtype == torch.float32:
         if out_dtype != torch.float32:
             raise KernelError("linear: the float32 product writes float32")

@@ -105,6 +105,8 @@ class DecoderModel:
         if step.n_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
         if not step.want_all:
+            if isinstance(pending, ops.PendingProduct) and pending.add_into(residual):
+                pending = None                    # the last product added itself into the stream
             residual = ops.gather_rows(residual, step.want_rows)
             pending = ops.gather_rows(ops.resolve(pending), step.want_rows) if pending is not None else None
         return self.head.forward(normalised_for(self.head, self.final_norm, residual, pending))

@@ -120,6 +120,36 @@ def test_unlaunched_products_and_parts_that_do_not_fuse():
     assert isinstance(got, torch.Tensor) and torch.equal(s3, want_stream)
 
 
+@pytest.mark.parametrize("rows", [40, 300])
+def test_unlaunched_product_of_many_rows_adds_into_the_stream(rows):
+    """Beyond the decode kernels' row counts an unlaunched product is the library's, with the stream as
+    its accumulate operand: the stream and the normalised rows must equal a float64 product added in
+    float32, and the values the separate way gives (product written, then added by the norm kernel)."""
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, 176, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(72, 176, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    gain = (1 + 0.1 * torch.randn(72, generator=g)).to(DEV)
+    stream0 = torch.randn(rows, 72, generator=g).to(DEV)
+    pending = ops.linear(x, w, out_dtype=torch.float32, resident=True, lazy=True)
+    assert isinstance(pending, ops.PendingProduct)
+    separate_stream = stream0.clone()
+    separate = ops.add_rmsnorm(separate_stream, pending.tensor(), gain, 1e-5, torch.bfloat16)
+    stream = stream0.clone()
+    got = ops.add_rmsnorm(stream, pending, gain, 1e-5, torch.bfloat16, lazy=True)
+    assert isinstance(got, torch.Tensor)
+    want_stream = (stream0.double() + x.double() @ w.double().t()).float()
+    assert torch.allclose(stream, want_stream, atol=2e-5, rtol=1e-5)
+    assert torch.allclose(stream, separate_stream, atol=2e-6, rtol=1e-6)
+    want = plain_llama.rms_norm(want_stream.cpu(), gain.cpu(), 1e-5)
+    assert torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(got.float(), separate.float(), atol=1e-2, rtol=1e-2)
+    # a stream that is a view with gaps between its rows is not the library's operand: the separate way runs
+    wide = torch.zeros(rows, 80, device=DEV)
+    wide[:, :72] = stream0
+    view = wide[:, :72]
+    assert not pending.add_into(view) and torch.equal(view, stream0)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embedding_and_head_parts(dtype):
     from dotllm_b200.config import PartSpec
