@@ -281,9 +281,13 @@ def main():
         return shares
 
     def prefill_flops(T, rows_out):
-        per_layer = 2 * T * (cfg.hidden_size * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.hidden_size
-                             + 3 * cfg.hidden_size * cfg.intermediate_size)
-        return cfg.num_hidden_layers * per_layer + 2 * rows_out * cfg.hidden_size * vocab
+        """The products the step runs: Q/K/V for every token in every layer; the output projection and
+        the feed-forward for every token in all layers but the last, which runs them (and the head) for
+        the ``rows_out`` rows whose logits are wanted only."""
+        qkv = 2 * cfg.hidden_size * (cfg.q_dim + 2 * cfg.kv_dim)
+        rest = 2 * (cfg.q_dim * cfg.hidden_size + 3 * cfg.hidden_size * cfg.intermediate_size)
+        L = cfg.num_hidden_layers
+        return T * (L * qkv + (L - 1) * rest) + rows_out * (rest + 2 * cfg.hidden_size * vocab)
 
     def prefill_point():
         """One prompt of PREFILL_TOKENS tokens through model.step: best of ``reps`` after three warm-ups

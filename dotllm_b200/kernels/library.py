@@ -16,7 +16,7 @@ _F = ctypes.c_float
 
 # name -> argument types (every function returns int status)
 _SIGNATURES = {
-    "dl_gather_rows": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "dl_gather_rows": [_P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
     "dl_add_rmsnorm": [_P, _P, _I, _P, _P, _I, _I, _I, _F, _P],
     "dl_rope_cache_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I,
                             _I, _I, _I, _I, _I, _P],

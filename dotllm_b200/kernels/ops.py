@@ -52,19 +52,21 @@ def _int32(t, what):
 
 
 # ------------------------------------------------------------------ embedding
-def gather_rows(table, ids, out=None):
-    """out[r] = float32(table[ids[r]]).  table [n, width] float32 or bfloat16; ids int32 [R]."""
+def gather_rows(table, ids, out=None, out_dtype=torch.float32):
+    """out[r] = table[ids[r]] as ``out_dtype``.  table [n, width] float32 or bfloat16 (rows contiguous,
+    possibly with gaps between them); ids int32 [R]; float32 out, or bfloat16 from a bfloat16 table."""
     _need_cuda(table, ids, out)
-    if table.dim() != 2 or not table.is_contiguous():
-        raise KernelError("gather_rows: table must be a contiguous matrix")
+    stride = _rows_view(table, "gather_rows table")
     _int32(ids, "gather_rows ids")
     n, width = table.shape
     rows = ids.numel()
     if out is None:
-        out = torch.empty((rows, width), dtype=torch.float32, device=table.device)
-    elif out.shape != (rows, width) or out.dtype != torch.float32 or not out.is_contiguous():
-        raise KernelError("gather_rows: out must be contiguous float32 [rows, width]")
-    _library.call("dl_gather_rows", _ptr(table), _code(table.dtype), _ptr(ids), _ptr(out),
+        out = torch.empty((rows, width), dtype=out_dtype, device=table.device)
+    elif out.shape != (rows, width) or out.dtype != out_dtype or not out.is_contiguous():
+        raise KernelError(f"gather_rows: out must be contiguous {out_dtype} [rows, width]")
+    if out_dtype != torch.float32 and out_dtype != table.dtype:
+        raise KernelError(f"gather_rows: rows of {table.dtype} are gathered as float32 or as they are, not as {out_dtype}")
+    _library.call("dl_gather_rows", _ptr(table), _code(table.dtype), stride, _ptr(ids), _ptr(out), _code(out_dtype),
                   rows, width, n, _stream())
     return out
 
@@ -121,6 +123,18 @@ class ScaledRows:
 def resolve(value):
     """The tensor behind a PendingProduct or ScaledRows; tensors and None pass through."""
     return value.tensor() if isinstance(value, (PendingProduct, ScaledRows)) else value
+
+
+def narrow_rows(value, ids):
+    """The rows ``ids`` (int32 on the device) of a branch output, in its own dtype.  Of a product not
+    yet launched only those rows of x are kept, so that the product is computed for them alone."""
+    if value is None:
+        return None
+    if isinstance(value, PendingProduct):
+        x = resolve(value.x)
+        return PendingProduct(gather_rows(x, ids, out_dtype=x.dtype), value.w, value.resident)
+    value = resolve(value)
+    return gather_rows(value, ids, out_dtype=value.dtype)
 
 
 # ----------------------------------------------------------------------- norm

@@ -99,14 +99,24 @@ class DecoderModel:
         """Logits float32 [wanted rows, vocab] of one step (see engine.step)."""
         residual = self.embedding.forward(step)
         pending = None
+        # Logits are wanted at some rows only (a prompt's last token): the last layer in the order of
+        # running still caches every token, but may hand on the wanted rows alone.
+        some = 0 < step.n_wanted and not step.want_all
+        narrowed = False
+        last = len(self.spec.schedule) - 1
         for e, entry in enumerate(self.spec.schedule):
             view = cache.view(e, step.block_tables, step.slots)
-            residual, pending = self.blocks[entry.layer].forward(residual, pending, step, view)
+            block = self.blocks[entry.layer]
+            if e == last and some and block.narrows:
+                residual, pending = block.forward(residual, pending, step, view, keep_rows=step.want_rows)
+                narrowed = True
+            else:
+                residual, pending = block.forward(residual, pending, step, view)
         if step.n_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
-        if not step.want_all:
+        if some and not narrowed:
             if isinstance(pending, ops.PendingProduct) and pending.add_into(residual):
                 pending = None                    # the last product added itself into the stream
             residual = ops.gather_rows(residual, step.want_rows)
-            pending = ops.gather_rows(ops.resolve(pending), step.want_rows) if pending is not None else None
+            pending = ops.narrow_rows(pending, step.want_rows)
         return self.head.forward(normalised_for(self.head, self.final_norm, residual, pending))

@@ -177,9 +177,14 @@ class Arrangement:
     """How a layer's parts and the residual stream are wired.  ``parts`` maps the names of the
     layer's description to the built parts; ``needs`` lists the names this arrangement cannot do
     without.  ``cached_mixer`` names the part whose ``cache_need()`` the layer's cache is made for
-    (None: the layer keeps nothing)."""
+    (None: the layer keeps nothing).  ``narrows``: ``forward`` also takes ``keep_rows`` (int32 row
+    indices on the device): when the model gives them (the last layer of a step whose logits are
+    wanted at some rows only), the arrangement returns the stream and the pending branch for those rows
+    alone, in their order, and may skip whatever only the other rows would need - but it must still put
+    every token's keys, values and state into the cache."""
     needs = ()
     cached_mixer = "mixer"
+    narrows = False
 
     def __init__(self, parts: dict):
         lacking = [n for n in self.needs if n not in parts]
@@ -194,7 +199,8 @@ class Arrangement:
         return mixer.cache_need() if mixer is not None else None
 
     def forward(self, residual, pending, step, cache_view):
-        """Returns (residual, pending): the float32 stream and a branch output not yet added."""
+        """Returns (residual, pending): the float32 stream and a branch output not yet added.
+        (An arrangement that ``narrows`` also accepts ``keep_rows=None``.)"""
         raise NotImplementedError
 
 

@@ -99,6 +99,42 @@ def test_whole_tail_and_batched(tmp, which, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["B", "C"])
+def test_wanting_some_rows_changes_no_logit_and_no_cache(tmp, which, dtype):
+    """When logits are wanted at some rows only, the last layer hands on those rows alone.  The logits
+    must be those of a step that wants every row, in the order asked for (also out of order and twice),
+    every token must still reach the cache (decoding on from either step gives the same logits), and
+    two prompts in one step must each get their own rows."""
+    from dotllm_b200 import StepEntry
+    model, cfg, weights, _ = load_pair(tmp, which, dtype)
+    a = tiny_models.random_tokens(150, cfg["vocab_size"], seed=31)
+    b = tiny_models.random_tokens(70, cfg["vocab_size"], seed=32)
+    ref_a, ref_b = plain_llama.forward(cfg, weights, list(a) + [5, 6]), plain_llama.forward(cfg, weights, b)
+    cache = model.new_cache(max_tokens=1024)
+    cache.fill_free_pages(float("nan"))
+    s_all, s_some, s_b = cache.open_sequence(), cache.open_sequence(), cache.open_sequence()
+    everything = model.step(cache, [StepEntry(s_all, a, list(range(len(a))))])
+    wants = [149, 3, 64, 3, 0]
+    some = model.step(cache, [StepEntry(s_some, a, wants), StepEntry(s_b, b, [69, 10])])
+    assert some.shape[0] == len(wants) + 2
+    assert_close(some[:len(wants)], ref_a[wants], dtype, "wanted rows of the first prompt")
+    assert_close(some[len(wants):], ref_b[[69, 10]], dtype, "wanted rows of the second prompt")
+    if dtype == torch.float32:      # one kernel whatever the number of rows: the same bits
+        assert torch.equal(some[:len(wants)], everything[wants])
+    # the cache holds every token of both steps: two more tokens give the plain logits from either
+    for s in (s_all, s_some):
+        out = torch.cat([model.step(cache, [StepEntry(s, [5])]), model.step(cache, [StepEntry(s, [6])])])
+        assert_close(out, ref_a[150:152], dtype, "decoding on after the prompt")
+    # no rows wanted at all: nothing returned, the cache still filled
+    s_none = cache.open_sequence()
+    assert model.step(cache, [StepEntry(s_none, a, [])]).shape[0] == 0
+    assert_close(model.step(cache, [StepEntry(s_none, [5])]), ref_a[150:151], dtype, "after a prompt that wanted nothing")
+    for s in (s_all, s_some, s_b, s_none):
+        cache.close_sequence(s)
+    cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_float32_cuts_give_the_same_bits(tmp, dtype):
     """In float32 every kernel's order of operations for a position is fixed, so whole, one by one
     and batched give identical bits.  (bfloat16 uses library products whose rounding depends on

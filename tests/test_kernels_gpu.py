@@ -36,6 +36,16 @@ def test_gather_rows(dtype, rows, width, vocab):
     out = ops().gather_rows(table, ids)
     assert out.dtype == torch.float32
     assert torch.equal(out.cpu(), kernel_refs.gather_rows(table.cpu(), ids.cpu()))
+    # rows kept in their own dtype, and rows of a table that is a column slice of a wider matrix
+    same = ops().gather_rows(table, ids, out_dtype=dtype)
+    assert same.dtype == dtype and torch.equal(same.cpu(), table.cpu()[ids.cpu().long()])
+    wide = torch.randn(vocab, width + 24, generator=g).to(dtype).to(DEV)
+    part = wide[:, 8:8 + width]
+    assert torch.equal(ops().gather_rows(part, ids, out_dtype=dtype).cpu(), part.cpu()[ids.cpu().long()])
+    if dtype == torch.float32:
+        from dotllm_b200.errors import KernelError
+        with pytest.raises(KernelError):
+            ops().gather_rows(table, ids, out_dtype=torch.bfloat16)
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
