@@ -33,12 +33,19 @@
 // returns.  The host reads `status` at its next synchronisation point.
 #include "common.cuh"
 
-// One ring stage per consumer warp: warp w owns stage w and sees every phase of its barriers in
-// order.  (A warp that shared stages with others could fall two phases behind a barrier and
+// The ring has `depth` stages per consumer warp: page n of a block's stream goes to stage n % (warps *
+// depth) and to warp n % warps, so warp w owns stages w, w + warps, ... and sees every phase of their
+// barriers in order.  (A warp that shared stages with others could fall two phases behind a barrier and
 // mistake an old completion for the one it waits for: mbarrier waits tell phases apart by parity only.)
+// A stage is asked for again only when its warp has used it up, so the bytes a multiprocessor has in
+// flight are the ring's: with the 32 KB pages of head size 128 six stages fill the shared memory; the
+// smaller pages of smaller heads take a deeper ring, or the copies' latency bounds the kernel
+// (head size 64, depth 1: 96 KB in flight, 2.9 TB/s over the whole GPU).
 #ifndef AD_MAX_STAGES
-#define AD_MAX_STAGES 6                        // consumer warps = stages, as many as fit in shared memory
+#define AD_MAX_STAGES 6                        // consumer warps, as many as fit in shared memory
 #endif
+#define AD_MAX_DEPTH 4                         // ring stages per consumer warp, at most
+#define AD_MAX_RING (AD_MAX_STAGES * AD_MAX_DEPTH)
 #define AD_THREADS (32 * (AD_MAX_STAGES + 1))  // the last warp is the producer
 #define AD_WAIT_CYCLES (1ll << 31)
 
@@ -90,9 +97,16 @@ __device__ __forceinline__ bool ad_mbar_wait(uint64_t* bar, uint32_t parity, vol
     }
     return true;
 }
-__device__ __forceinline__ void ad_bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(ad_smem(dst)),
-                 "l"(src), "r"(bytes), "r"(ad_smem(bar))
+// The pages are read once per step and together exceed the L2: they are brought in to be evicted
+// first, so that what the step reads again (queries, tables, partial results, the kernels' code) stays.
+__device__ __forceinline__ uint64_t ad_stream_policy() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void ad_bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(ad_smem(dst)),
+                 "l"(src), "r"(bytes), "r"(ad_smem(bar)), "l"(policy)
                  : "memory");
 }
 __device__ __forceinline__ void ad_consumer_sync(int n_consumers) {
@@ -319,7 +333,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         int out_stride, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, int n_pages,
                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_table,
-                        int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int n_stages,
+                        int bt_stride, int n_seqs, int nh, int nkv, float scale, int window, int n_stages, int n_ring,
                         float* __restrict__ part_o,
                         float* __restrict__ part_ml, int* __restrict__ pair_counters, const AdFresh fresh,
                         int* __restrict__ status) {
@@ -331,8 +345,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(ad_smem_raw);      // [stage][K page | V page]
     const int group = nh / nkv;
     // after the stages: each consumer warp's partial output [group][HD + 4]
-    float* merge_o = reinterpret_cast<float*>(ad_smem_raw + (size_t)n_stages * 2 * PAGE_BYTES);
-    __shared__ uint64_t full_bar[AD_MAX_STAGES], empty_bar[AD_MAX_STAGES];
+    // n_stages: consumer warps; n_ring: stages of the ring, a multiple of n_stages
+    float* merge_o = reinterpret_cast<float*>(ad_smem_raw + (size_t)n_ring * 2 * PAGE_BYTES);
+    __shared__ uint64_t full_bar[AD_MAX_RING], empty_bar[AD_MAX_RING];
     __shared__ float sm_m[AD_MAX_STAGES][16], sm_l[AD_MAX_STAGES][16];
     __shared__ volatile int gave_up;
     __shared__ int last_of_pair;
@@ -344,14 +359,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     uint32_t smem_bytes;
     asm("mov.u32 %0, %dynamic_smem_size;" : "=r"(smem_bytes));
     const uint32_t smem_lo = ad_smem(ad_smem_raw), smem_hi = smem_lo + smem_bytes;
-    if ((size_t)n_stages * 2 * PAGE_BYTES + (size_t)n_stages * group * (HD + 4) * 4 > smem_bytes) {
+    if ((size_t)n_ring * 2 * PAGE_BYTES + (size_t)n_stages * group * (HD + 4) * 4 > smem_bytes || n_ring > AD_MAX_RING ||
+        n_stages > AD_MAX_STAGES || n_ring % n_stages != 0) {
         if (threadIdx.x == 0) atomicExch(status, 11);
         return;
     }
 
     if (threadIdx.x == 0) {
         gave_up = 0;
-        for (int s = 0; s < n_stages; ++s) {
+        for (int s = 0; s < n_ring; ++s) {
             ad_mbar_init(&full_bar[s], 1);
             ad_mbar_init(&empty_bar[s], 1);
         }
@@ -371,6 +387,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
         // the consumer overwrites in the stage, and the producer never waits.)
         int n = 0;                                           // pages issued so far, over all runs
         bool stop = false, waited = false;
+        const uint64_t policy = ad_stream_policy();
         const AdCut cut = ad_cut(seq_len, n_seqs, nkv, window, gridDim.x, lane);
         AdWalk walk = ad_walk_begin(cut, seq_len, n_seqs, nkv, window, blockIdx.x, lane);
         AdSeg w;
@@ -383,10 +400,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                     const int page = __shfl_sync(0xffffffffu, mine, j);
                     int bad = 0;
                     if (lane == 0) {
-                        const int s = n % n_stages;
+                        const int s = n % n_ring;
                         if (page < 0 || page >= n_pages) {   // host-validated
                             bad = 2;
-                        } else if (n >= n_stages && !ad_mbar_wait(&empty_bar[s], ((n / n_stages) - 1) & 1, &gave_up)) {
+                        } else if (n >= n_ring && !ad_mbar_wait(&empty_bar[s], ((n / n_ring) - 1) & 1, &gave_up)) {
                             bad = 1;
                         } else {
                             if (!waited && fresh.k == nullptr && w.page0 + i0 + j == (w.len - 1) / DL_PAGE) {
@@ -395,8 +412,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                             }
                             __nv_bfloat16* dst = stage_mem + (size_t)s * 2 * PAGE_ELEMS;
                             ad_mbar_expect(&full_bar[s], 2 * PAGE_BYTES);
-                            ad_bulk_copy(dst, k_pool + dl_k_offset(page, nkv, w.kvh, 0, HD), PAGE_BYTES, &full_bar[s]);
-                            ad_bulk_copy(dst + PAGE_ELEMS, v_pool + dl_v_offset(page, nkv, w.kvh, 0, HD), PAGE_BYTES, &full_bar[s]);
+                            ad_bulk_copy(dst, k_pool + dl_k_offset(page, nkv, w.kvh, 0, HD), PAGE_BYTES, &full_bar[s], policy);
+                            ad_bulk_copy(dst + PAGE_ELEMS, v_pool + dl_v_offset(page, nkv, w.kvh, 0, HD), PAGE_BYTES, &full_bar[s], policy);
                         }
                     }
                     bad = __shfl_sync(0xffffffffu, bad, 0);
@@ -410,13 +427,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
         }
         if (stop && lane == 0) {
             // copies already issued must land before the block's shared memory is released
-            for (int i = max(0, n - n_stages); i < n; ++i) {
+            for (int i = max(0, n - n_ring); i < n; ++i) {
                 const long long t0 = clock64();
-                while (!ad_mbar_try(&full_bar[i % n_stages], (i / n_stages) & 1) && clock64() - t0 < AD_WAIT_CYCLES) {}
+                while (!ad_mbar_try(&full_bar[i % n_ring], (i / n_ring) & 1) && clock64() - t0 < AD_WAIT_CYCLES) {}
             }
         }
     } else if (warp < n_stages) {
-        // ------------------------------------------------------------ consumers (warp w owns stage w)
+        // ------------------------------------------------------------ consumers (warp w owns stages w, w + n_stages, ...)
         dl_grid_dependency_wait();       // q comes from the kernel before this one; out and the scratch may be in use by it
         float* my_o = merge_o + (size_t)warp * group * (HD + 4);
         const float scale2 = scale * 1.4426950408889634f;    // scores in units of log2
@@ -480,8 +497,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
             }
             for (int i = i_first; i < w.n_pages; i += n_stages) {
                 const int n = n0 + i;
-                const int s = warp;
-                if (!ad_mbar_wait(&full_bar[s], (n / n_stages) & 1, &gave_up)) {
+                const int s = n % n_ring;
+                if (!ad_mbar_wait(&full_bar[s], (n / n_ring) & 1, &gave_up)) {
                     if (!gave_up) atomicExch(status, 3);
                     gave_up = 1;
                     continue;                                 // keep walking so that every barrier below is reached
@@ -786,9 +803,12 @@ static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int
     cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     const size_t stage = (size_t)2 * DL_PAGE * HD * 2;
     const size_t merge_per = (size_t)group * (HD + 4) * sizeof(float);     // one consumer warp's partial output
-    int n_stages = AD_MAX_STAGES;
+    int n_stages = AD_MAX_STAGES;                            // consumer warps
     while (n_stages > 2 && n_stages * (stage + merge_per) + 2048 > (size_t)max_smem) --n_stages;
-    const size_t smem = n_stages * (stage + merge_per);
+    int depth = 1;                                           // ring stages per warp: what the shared memory holds
+    while (depth < AD_MAX_DEPTH && n_stages * ((depth + 1) * stage + merge_per) + 2048 <= (size_t)max_smem) ++depth;
+    const int n_ring = n_stages * depth;
+    const size_t smem = n_stages * (depth * stage + merge_per);
     if (smem + 2048 > (size_t)max_smem)
         return dl_fail(DL_ERR_UNSUPPORTED, "attention_decode: head_dim %d with %d heads per group needs %zu bytes of shared memory", HD, group, smem);
     static int configured = 0;
@@ -808,7 +828,7 @@ static int ad_launch(cudaStream_t s, const void* q, int q_stride, void* out, int
     cudaError_t le = dl_launch_dependent(
         attention_decode_kernel<HD, WIDE>, dim3(blocks), dim3(AD_THREADS), smem, s, (const __nv_bfloat16*)q, q_stride,
         (__nv_bfloat16*)out, out_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, seq_len,
-        block_table, bt_stride, n_seqs, nh, nkv, scale, window, n_stages, part_o, part_ml, pair_counters, fresh, status);
+        block_table, bt_stride, n_seqs, nh, nkv, scale, window, n_stages, n_ring, part_o, part_ml, pair_counters, fresh, status);
     if (le != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "attention_decode: %s", cudaGetErrorString(le));
     return DL_OK;
 }

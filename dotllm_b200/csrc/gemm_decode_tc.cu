@@ -238,12 +238,13 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         if (lane == 0) {
             const int n_mine = end - begin;
             const uint32_t stage_bytes = (uint32_t)work.stage_bytes;
+            const uint64_t policy = dl_stream_policy();     // W is read once a step: first out of the L2
             auto load_w = [&](int unit, int s) {
                 const int tile = unit / cpt, kc = unit - tile * cpt;
                 unsigned char* a = tiles + (size_t)s * stage_bytes;
                 const int row0 = tile * GD_BM;
-                dl_tma_load_2d(a, &tmap_w, kc * GD_BK, row0, &full_bar[s]);
-                if (GATED) dl_tma_load_2d(a + GD_A_BYTES, &tmap_w, kc * GD_BK, row0 + work.N, &full_bar[s]);
+                dl_tma_load_2d_hint(a, &tmap_w, kc * GD_BK, row0, &full_bar[s], policy);
+                if (GATED) dl_tma_load_2d_hint(a + GD_A_BYTES, &tmap_w, kc * GD_BK, row0 + work.N, &full_bar[s], policy);
             };
             auto load_x = [&](int unit, int s) {
                 const int kc = unit % cpt;

@@ -215,6 +215,7 @@ __device__ __forceinline__ bool gs_produce(const CUtensorMap* tmap, const GsWork
     const int gw = blockIdx.x * GS_CONSUMERS + lane;
     int cur = min(w.total_chunks, gw * w.share);
     const int end = min(w.total_chunks, (gw + 1) * w.share);
+    const uint64_t policy = dl_stream_policy();             // W is read once a step: first out of the L2
     for (; cur < end; ++cur, ++cnt) {
         const int slot = cnt % GS_SLOTS;
         if (cnt >= GS_SLOTS && !gs_mbar_wait(&r.empty_bar[lane][slot], ((cnt / GS_SLOTS) - 1) & 1, r.gave_up)) {
@@ -227,10 +228,10 @@ __device__ __forceinline__ bool gs_produce(const CUtensorMap* tmap, const GsWork
         // a box is always written whole: parts outside the matrix arrive as zeros
         gs_mbar_expect(&r.full_bar[lane][slot], GS_STAGE_ELEMS * 2);
         if (FUSE_SWIGLU) {
-            dl_tma_load_2d(dst, tmap, kc * GS_BK, tile * 8, &r.full_bar[lane][slot]);
-            dl_tma_load_2d(dst + 8 * GS_BK, tmap, kc * GS_BK, w.up_offset + tile * 8, &r.full_bar[lane][slot]);
+            dl_tma_load_2d_hint(dst, tmap, kc * GS_BK, tile * 8, &r.full_bar[lane][slot], policy);
+            dl_tma_load_2d_hint(dst + 8 * GS_BK, tmap, kc * GS_BK, w.up_offset + tile * 8, &r.full_bar[lane][slot], policy);
         } else {
-            dl_tma_load_2d(dst, tmap, kc * GS_BK, tile * 16, &r.full_bar[lane][slot]);
+            dl_tma_load_2d_hint(dst, tmap, kc * GS_BK, tile * 16, &r.full_bar[lane][slot], policy);
         }
     }
     return true;

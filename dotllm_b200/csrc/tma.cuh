@@ -38,6 +38,23 @@ __device__ __forceinline__ void dl_tma_load_2d(void* smem_dst, const CUtensorMap
         ::"r"(dst), "l"(map), "r"(col), "r"(row), "r"(mbar)
         : "memory");
 }
+// A cache policy for data that is read once and is larger than the L2 (a decode step's weights): the
+// lines are the first to be evicted, so that what is read again (activations, partial sums, code) stays.
+__device__ __forceinline__ uint64_t dl_stream_policy() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// dl_tma_load_2d with a cache policy for the lines it brings into the L2.
+__device__ __forceinline__ void dl_tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, int col, int row,
+                                                    uint64_t* bar, uint64_t policy) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const uint32_t mbar = (uint32_t)__cvta_generic_to_shared(bar);
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(dst), "l"(map), "r"(col), "r"(row), "r"(mbar), "l"(policy)
+        : "memory");
+}
 // Copy `bytes` (a multiple of 16, both addresses 16-byte aligned) of contiguous global memory into
 // shared memory; `bar` receives the bytes.
 __device__ __forceinline__ void dl_bulk_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
