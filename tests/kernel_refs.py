@@ -15,8 +15,8 @@ import plain_llama
 PAGE = 64
 
 
-def gather_rows(table, ids, out=None):
-    res = table[ids.long()].to(torch.float32)
+def gather_rows(table, ids, out=None, out_dtype=torch.float32):
+    res = table[ids.long()].to(out_dtype)
     if out is not None:
         out.copy_(res)
         return out
