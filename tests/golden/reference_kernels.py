@@ -70,9 +70,15 @@ extern "C" int ref_embedding(const float* table, const int* ids, float* out, int
 '''
 
 
+def reference_checkout():
+    """The reference's source tree: $DOTLLM_REFERENCE_ROOT, or a folder `reference` beside the repository."""
+    root = os.environ.get("DOTLLM_REFERENCE_ROOT")
+    return Path(root) if root else Path(__file__).resolve().parents[3] / "reference"
+
+
 def kernel_sources():
     """Folder with the reference's kernel files, or None."""
-    for cand in (Path("/root/reference/native/kernels"), REF_DIR / "native_kernels"):
+    for cand in (reference_checkout() / "native" / "kernels", REF_DIR / "native_kernels"):
         if all((cand / f).is_file() for f in KERNEL_FILES):
             return cand
     return None
@@ -81,7 +87,7 @@ def kernel_sources():
 def stage_sources():
     """Copy the kernel files (unchanged) into baseline/_ref/native_kernels so that they travel with
     the working tree to a machine that has no reference checkout.  True if they are there."""
-    src = Path("/root/reference/native/kernels")
+    src = reference_checkout() / "native" / "kernels"
     dst = REF_DIR / "native_kernels"
     if all((src / f).is_file() for f in KERNEL_FILES):
         dst.mkdir(parents=True, exist_ok=True)
