@@ -400,11 +400,13 @@ def gated_linear(x, w_gate_up, resident=False):
 
 
 # ------------------------------------------------------------------- sampling
-def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None, out=None):
+def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None, out=None, split=None):
     """One token per row of float32 logits [R, V].  With ``temperature`` None every row is
     greedy (first index of the maximum).  Otherwise per-row float32/int32 tensors [R] give the
     chain temperature -> top-k -> top-p -> min-p and ``uniform`` the draw in [0, 1);
-    a row with temperature <= 0 is greedy."""
+    a row with temperature <= 0 is greedy.  ``split``: None lets the library choose between one
+    block per row and a cluster of blocks per row (long rows, few of them); False / True force
+    one or the other - they give the same tokens."""
     _need_cuda(logits, temperature, top_k, top_p, min_p, uniform)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 [rows, vocab] with contiguous rows")
@@ -420,7 +422,7 @@ def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform
         raise KernelError("sample: out must be a contiguous int32 CUDA tensor of one id per row")
     _library.call("dl_sample", _ptr(logits), logits.stride(0) if rows > 1 else vocab, rows, vocab,
                   _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(out),
-                  _stream())
+                  0 if split is None else (2 if split else 1), _stream())
     return out
 
 

@@ -130,7 +130,7 @@ def repetition_penalty(logits, prev, prev_len, penalty, window):
     return logits
 
 
-def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None, out=None):
+def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform=None, out=None, split=None):
     out = []
     for r in range(logits.shape[0]):
         row = logits[r].detach().cpu()

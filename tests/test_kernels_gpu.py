@@ -312,6 +312,43 @@ def test_sample_chain(vocab):
         assert _sampled_ok(x[i], out[i], float(u[i]), **settings[i % len(settings)]), (i, settings[i % len(settings)])
 
 
+@pytest.mark.parametrize("vocab", [8195, 32003, 128256])
+def test_sample_by_a_cluster_of_blocks_gives_the_same_tokens(vocab):
+    """Long rows are sampled by a cluster of blocks that keep the row in their shared memories.  Its sums
+    are the same integers as the one-block kernel's, so every token must be the same: over every
+    setting of the chain, greedy rows, rows with ties at the top-k threshold that straddle slices,
+    NaN and -inf entries, a row with nothing finite, and draws at both ends of [0, 1)."""
+    g = torch.Generator().manual_seed(vocab)
+    settings = [dict(temperature=1.0), dict(temperature=0.7), dict(temperature=1.3, top_k=5),
+                dict(temperature=0.9, top_p=0.8), dict(temperature=1.0, min_p=0.1),
+                dict(temperature=0.8, top_k=40, top_p=0.9, min_p=0.05), dict(temperature=2.0, top_k=1),
+                dict(temperature=1.0, top_p=0.01), dict(temperature=0.0), dict(temperature=1.0, top_k=600, top_p=0.97),
+                dict(temperature=0.6, top_p=0.5, min_p=0.3)]
+    rows = len(settings) * 6
+    x = torch.randn(rows, vocab, generator=g) * 3
+    x[3] = torch.round(x[3])                                   # many exact ties everywhere in the row
+    x[5, :] = -4.0
+    x[5, [7, vocab // 8 + 1, vocab // 2, vocab - 3]] = 2.0     # k = 40 .. cuts a run of equal values lying in several slices
+    x[16, ::3] = float("nan")
+    x[17, 100:] = float("-inf")
+    x[20] = float("-inf")                                       # nothing finite: index 0
+    x[27, vocab - 1] = 40.0                                     # all the mass in the last slice's last entry
+    u = torch.rand(rows, generator=g)
+    u[0], u[1], u[2] = 0.0, 0.99999994, 0.5
+    pick = lambda name, default: [settings[i % len(settings)].get(name, default) for i in range(rows)]
+    temp, top_p, min_p = torch.tensor(pick("temperature", 1.0)), torch.tensor(pick("top_p", 1.0)), torch.tensor(pick("min_p", 0.0))
+    top_k = torch.tensor(pick("top_k", 0), dtype=torch.int32)
+    args = [t.to(DEV) for t in (x, temp, top_k, top_p, min_p, u)]
+    one = ops().sample(*args, split=False).tolist()
+    many = ops().sample(*args, split=True).tolist()
+    assert many == one, [(i, settings[i % len(settings)], a, b) for i, (a, b) in enumerate(zip(one, many)) if a != b][:5]
+    assert ops().sample(*args).tolist() == one                  # whichever the library chooses
+    assert one[20] == 0 and one[27] == vocab - 1
+    for i in range(rows):                                       # and both are the plain sampler's tokens
+        if all(torch.isfinite(x[i])) and settings[i % len(settings)].get("temperature", 1.0) > 0:
+            assert _sampled_ok(x[i], one[i], float(u[i]), **settings[i % len(settings)]), (i, settings[i % len(settings)])
+
+
 def test_sample_top_k_ties_in_index_order():
     """Five logits tie at the k-th value; only the first of them (by index) may be drawn
     (src/DotLLM.Engine/Samplers/TopKSampler.cs:58-78)."""
