@@ -321,19 +321,31 @@ sample_kernel(const float* __restrict__ logits, int row_stride, int V, const flo
     if (threadIdx.x == 0) out[row] = sh.found >= 0 ? sh.found : arg_max;
 }
 
-// One block per row.  `prev` holds each row's generated ids, row r in prev[r*prev_stride ..
-// +prev_len[r]).  The last `window[r]` of them (0 = all) are penalised once per distinct id.
+// One block per row.  `prev` holds generated ids, those of step row r in row row_map[r] (r itself
+// without a map), ids [0, prev_len[r]).  With `append_pos`, the block first writes append_token[r] at
+// append_pos[r] of its history row (< 0: nothing to write): a caller that keeps the histories on the
+// device sends one id per row and step instead of the whole history.  The last `window[r]` of the ids
+// (0 = all) are penalised once per distinct id.
 __global__ void __launch_bounds__(256)
-repetition_penalty_kernel(float* __restrict__ logits, int row_stride, int V, const int32_t* __restrict__ prev,
-                          int prev_stride, const int32_t* __restrict__ prev_len,
-                          const float* __restrict__ penalty, const int32_t* __restrict__ window) {
+repetition_penalty_kernel(float* __restrict__ logits, int row_stride, int V, int32_t* __restrict__ prev,
+                          int prev_stride, int prev_rows, const int32_t* __restrict__ row_map,
+                          const int32_t* __restrict__ append_pos, const int32_t* __restrict__ append_token,
+                          const int32_t* __restrict__ prev_len, const float* __restrict__ penalty,
+                          const int32_t* __restrict__ window) {
     const int row = blockIdx.x;
+    const int hrow = row_map ? row_map[row] : row;
+    if (hrow < 0 || hrow >= prev_rows) return;                // host-validated
+    int32_t* ids = prev + (size_t)hrow * prev_stride;
+    if (append_pos != nullptr) {
+        const int at = append_pos[row];
+        if (threadIdx.x == 0 && at >= 0 && at < prev_stride) ids[at] = append_token[row];
+        __syncthreads();
+    }
     const float pen = penalty[row];
-    const int n = prev_len[row];
+    const int n = min(prev_len[row], prev_stride);
     if (pen == 1.0f || n <= 0) return;
     const int w = window[row];
     const int start = (w > 0 && n - w > 0) ? n - w : 0;
-    const int32_t* ids = prev + (size_t)row * prev_stride;
     float* x = logits + (size_t)row * row_stride;
     for (int i = start + threadIdx.x; i < n; i += blockDim.x) {
         const int id = ids[i];
@@ -915,13 +927,16 @@ extern "C" int dl_sample(const float* logits, int row_stride, int rows, int V, c
     return DL_OK;
 }
 
-extern "C" int dl_repetition_penalty(float* logits, int row_stride, int rows, int V, const int32_t* prev,
-                                     int prev_stride, const int32_t* prev_len, const float* penalty,
-                                     const int32_t* window, void* stream) {
-    DL_REQUIRE(rows >= 0 && V > 0 && row_stride >= V && prev_stride >= 0, "repetition_penalty: bad sizes");
+// prev: int32 [prev_rows, prev_stride]; row_map, append_pos, append_token: int32 [rows] or NULL (see the kernel).
+extern "C" int dl_repetition_penalty(float* logits, int row_stride, int rows, int V, int32_t* prev, int prev_stride, int prev_rows,
+                                     const int32_t* row_map, const int32_t* append_pos, const int32_t* append_token,
+                                     const int32_t* prev_len, const float* penalty, const int32_t* window, void* stream) {
+    DL_REQUIRE(rows >= 0 && V > 0 && row_stride >= V && prev_stride >= 0 && prev_rows >= 0, "repetition_penalty: bad sizes");
+    DL_REQUIRE(row_map != nullptr || prev_rows >= rows, "repetition_penalty: %d rows of history for %d rows", prev_rows, rows);
+    DL_REQUIRE((append_pos == nullptr) == (append_token == nullptr), "repetition_penalty: a position and an id to append go together");
     if (rows == 0 || prev_stride == 0) return DL_OK;
-    repetition_penalty_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(logits, row_stride, V, prev, prev_stride,
-                                                                     prev_len, penalty, window);
+    repetition_penalty_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(logits, row_stride, V, prev, prev_stride, prev_rows, row_map,
+                                                                     append_pos, append_token, prev_len, penalty, window);
     DL_CHECK_LAUNCH("repetition_penalty");
     return DL_OK;
 }

@@ -24,7 +24,7 @@ _SIGNATURES = {
     "dl_swiglu": [_P, _P, _I, _P, _I, _I, _I, _P],
     "dl_gemm_f32": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
     "dl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
-    "dl_repetition_penalty": [_P, _I, _I, _I, _P, _I, _P, _P, _P, _P],
+    "dl_repetition_penalty": [_P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P],
 }
 
 _lock = threading.Lock()

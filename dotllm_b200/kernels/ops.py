@@ -426,19 +426,35 @@ def sample(logits, temperature=None, top_k=None, top_p=None, min_p=None, uniform
     return out
 
 
-def repetition_penalty(logits, prev, prev_len, penalty, window):
+def repetition_penalty(logits, prev, prev_len, penalty, window, row_map=None, append=None):
     """In place: each distinct id among the last ``window[r]`` (0 = all) of row r's
-    ``prev[r, :prev_len[r]]`` has its logit divided (if positive) or multiplied by ``penalty[r]``."""
-    _need_cuda(logits, prev, prev_len, penalty, window)
+    ``prev[r, :prev_len[r]]`` has its logit divided (if positive) or multiplied by ``penalty[r]``.
+    ``row_map`` (int32 [rows]): row r's ids are in ``prev[row_map[r]]`` instead.  ``append`` =
+    (positions, ids), int32 [rows] each: before anything else id r is written at ``prev[row, positions[r]]``
+    (a position < 0: nothing), for callers that keep the histories on the device and send one id a step."""
+    _need_cuda(logits, prev, prev_len, penalty, window, row_map)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("repetition_penalty: logits must be float32 [rows, vocab]")
     rows, vocab = logits.shape
-    if prev.dtype != torch.int32 or prev.dim() != 2 or prev.shape[0] != rows or not prev.is_contiguous():
+    if prev.dtype != torch.int32 or prev.dim() != 2 or not prev.is_contiguous() or (row_map is None and prev.shape[0] < rows):
         raise KernelError("repetition_penalty: prev must be contiguous int32 [rows, n]")
     _int32(prev_len, "prev_len")
     _int32(window, "window")
+    if row_map is not None:
+        _int32(row_map, "row_map")
+    pos = tok = None
+    if append is not None:
+        pos, tok = append
+        _need_cuda(pos, tok)
+        _int32(pos, "append positions")
+        _int32(tok, "append ids")
     if penalty.dtype != torch.float32 or not penalty.is_contiguous():
         raise KernelError("repetition_penalty: penalty must be float32 [rows]")
+    for name, t in (("prev_len", prev_len), ("window", window), ("penalty", penalty), ("row_map", row_map), ("append positions", pos),
+                    ("append ids", tok)):
+        if t is not None and t.numel() != rows:
+            raise KernelError(f"repetition_penalty: {name} must hold one value per row ({rows}), got {t.numel()}")
     _library.call("dl_repetition_penalty", _ptr(logits), logits.stride(0) if rows > 1 else vocab, rows,
-                  vocab, _ptr(prev), prev.shape[1], _ptr(prev_len), _ptr(penalty), _ptr(window), _stream())
+                  vocab, _ptr(prev), prev.shape[1], prev.shape[0], _ptr(row_map), _ptr(pos), _ptr(tok), _ptr(prev_len),
+                  _ptr(penalty), _ptr(window), _stream())
     return logits

@@ -176,6 +176,7 @@ class SamplerPipeline:
         self.penalty = float(options.repetition_penalty) if p["use_penalty"] else 1.0
         self.penalty_window = int(options.repetition_penalty_window)
         self.context = SamplerContext(options.temperature, options.top_k, options.top_p, options.min_p, self.seed)
+        self.history, self.history_row = None, -1            # the batch's PenaltyHistory and this request's row in it
 
     def row_temperature(self):
         """What the kernel gets: <= 0 means argmax.  In an explicit chain a temperature <= 0
@@ -183,6 +184,82 @@ class SamplerPipeline:
         if self.greedy:
             return 0.0
         return self.temperature if self.temperature > 0 else 1.0
+
+
+class PenaltyHistory:
+    """The ids that the requests of one batch have generated, kept on the device for the repetition
+    penalty: a request's pipeline is given a row when the penalty first sees it, and every step sends
+    the one new id per row (the kernel writes it into the row before it reads the row) instead of all
+    ids generated so far.  A row whose request's list does not continue what the row holds (a
+    caller's own list, a token taken back) is written again as a whole."""
+
+    def __init__(self, device, rows=8, tokens=256):
+        self.device = device
+        self.ids = torch.zeros((rows, tokens), dtype=torch.int32, device=device)
+        self.held = []                                       # per row: the ids the device row holds (host copy)
+
+    def _grow(self, rows, tokens):
+        have_r, have_t = self.ids.shape
+        if rows <= have_r and tokens <= have_t:
+            return
+        new_r, new_t = max(have_r, rows), have_t
+        while new_t < tokens:
+            new_t *= 2
+        if new_r > have_r:
+            new_r = max(new_r, 2 * have_r)
+        bigger = torch.zeros((new_r, new_t), dtype=torch.int32, device=self.device)
+        bigger[:have_r, :have_t] = self.ids
+        self.ids = bigger
+
+    def row_of(self, pipe):
+        if pipe.history is not self:
+            pipe.history, pipe.history_row = self, len(self.held)
+            self.held.append([])
+        return pipe.history_row
+
+    def step(self, pipelines, generated):
+        """Bring the rows of these pipelines up to date.  Returns (row map, positions and ids to append,
+        lengths) as host lists; rows that had to be rewritten are already on the device."""
+        rows, pos, tok, lens = [], [], [], []
+        mine = [self.row_of(pipe) for pipe in pipelines]
+        self._grow(len(self.held), max((len(g) for g in generated), default=0) + 1)
+        for h, g in zip(mine, generated):
+            held = self.held[h]
+            n = len(g)
+            if n == len(held) + 1 and (n == 1 or g[-2] == held[-1]):
+                pos.append(n - 1)
+                tok.append(int(g[-1]))
+                held.append(int(g[-1]))
+            elif n == len(held) and (n == 0 or g[-1] == held[-1]):
+                pos.append(-1)
+                tok.append(0)
+            else:                                             # not the continuation of what the row holds
+                self.held[h] = [int(t) for t in g]
+                if n:
+                    self.ids[h, :n] = _to_device(self.held[h], torch.int32, self.device)
+                pos.append(-1)
+                tok.append(0)
+            rows.append(h)
+            lens.append(n)
+        return rows, pos, tok, lens
+
+
+def _to_device(values, dtype, device):
+    """Host numbers to a device tensor through pinned memory, without waiting for the stream: a copy
+    from pageable memory would hold the host until the step before it has finished."""
+    host = torch.tensor(values, dtype=dtype, pin_memory=device.type == "cuda")
+    return host.to(device, non_blocking=True)
+
+
+def _penalise(logits, pipelines, generated):
+    """The repetition penalty of every row, from the batch's history on the device."""
+    history = next((p.history for p in pipelines if p.history is not None), None)
+    if history is None or history.device != logits.device:
+        history = PenaltyHistory(logits.device)
+    rows, pos, tok, lens = history.step(pipelines, generated)
+    meta = _to_device([rows, pos, tok, lens, [p.penalty_window for p in pipelines]], torch.int32, logits.device)
+    pen = _to_device([p.penalty for p in pipelines], torch.float32, logits.device)
+    ops.repetition_penalty(logits, history.ids, meta[3], pen, meta[4], row_map=meta[0], append=(meta[1], meta[2]))
 
 
 def sample_rows(logits, pipelines, generated, sequence_indices, steps):
@@ -200,26 +277,16 @@ def sample_rows(logits, pipelines, generated, sequence_indices, steps):
         for proc in pipe.custom_processors:
             proc.process(logits[r], generated[r], pipe.context)
     if any(p.penalty != 1.0 for p in pipelines):
-        longest = max(1, max(len(g) for g in generated))
-        prev = torch.zeros((rows, longest), dtype=torch.int32)
-        for r, g in enumerate(generated):
-            if g:
-                prev[r, :len(g)] = torch.tensor(g, dtype=torch.int32)
-        meta_i = torch.tensor([[len(g) for g in generated], [p.penalty_window for p in pipelines]],
-                              dtype=torch.int32)
-        pen = torch.tensor([p.penalty for p in pipelines], dtype=torch.float32)
-        prev, meta_i, pen = prev.to(device), meta_i.to(device), pen.to(device)
-        ops.repetition_penalty(logits, prev, meta_i[0].contiguous(), pen, meta_i[1].contiguous())
+        _penalise(logits, pipelines, generated)
     for r, pipe in enumerate(pipelines):
         for step in pipe.custom_steps:
             step.apply(logits[r], pipe.context)
     if all(p.row_temperature() <= 0 for p in pipelines):
         return ops.sample(logits)
-    fl = torch.tensor([[p.row_temperature() for p in pipelines],
-                       [p.top_p for p in pipelines],
-                       [p.min_p for p in pipelines],
-                       [uniform(p.seed, n) for p, n in zip(pipelines, steps)]],
-                      dtype=torch.float32).to(device)
-    top_k = torch.tensor([p.top_k for p in pipelines], dtype=torch.int32).to(device)
+    fl = _to_device([[p.row_temperature() for p in pipelines],
+                     [p.top_p for p in pipelines],
+                     [p.min_p for p in pipelines],
+                     [uniform(p.seed, n) for p, n in zip(pipelines, steps)]], torch.float32, device)
+    top_k = _to_device([p.top_k for p in pipelines], torch.int32, device)
     return ops.sample(logits, temperature=fl[0].contiguous(), top_k=top_k, top_p=fl[1].contiguous(),
                       min_p=fl[2].contiguous(), uniform=fl[3].contiguous())

@@ -71,3 +71,41 @@ def first_wrong(got, want, dtype):
     rel = (g - w).pow(2).mean(dim=-1).sqrt() / w.pow(2).mean(dim=-1).sqrt().clamp_min(1e-30)
     bad = ((err.reshape(-1) > TOL[dtype]) | (rel > REL_RMS[dtype])).nonzero()
     return None if bad.numel() == 0 else int(bad[0])
+
+
+def penalty_history_check(device, steps=40):
+    """Greedy requests with repetition penalties through ``sample_rows`` step by step, as the generation
+    loop calls it - rows that end early, a window, a request without a penalty, a row whose list is
+    replaced by the caller - against the plain penalty and arg-max on each step's own copy of the logits."""
+    from dotllm_b200.sampling import InferenceOptions, SamplerPipeline
+    from dotllm_b200.sampling.pipeline import sample_rows
+    vocab = 97
+    g = torch.Generator().manual_seed(5)
+    options = [InferenceOptions(temperature=0.0, repetition_penalty=1.3), InferenceOptions(temperature=0.0, repetition_penalty=2.5,
+               repetition_penalty_window=4), InferenceOptions(temperature=0.0), InferenceOptions(temperature=0.0, repetition_penalty=0.7),
+               InferenceOptions(temperature=0.0, repetition_penalty=1.1)]
+    pipes = [SamplerPipeline(o) for o in options]
+    generated = [[] for _ in pipes]
+    live = list(range(len(pipes)))
+    for step in range(steps):
+        if step == 7:
+            live.remove(1)                                       # a request ends: the rows above it move down
+        if step == 12:
+            generated[3] = [5, 5, 9]                            # not what the device row holds: written again as a whole
+        if step == 20:
+            live.remove(0)
+        base = (torch.randn(len(live), vocab, generator=g) * 2).round() / 2 + torch.linspace(0.3, 0, vocab)   # few distinct values: the penalty decides
+        want = []
+        for row, i in enumerate(live):
+            o = options[i]
+            x = plain_llama.apply_repetition_penalty(base[row].clone(), generated[i], o.repetition_penalty, o.repetition_penalty_window)
+            want.append(int(torch.argmax(x)))
+        got = sample_rows(base.clone().to(device), [pipes[i] for i in live], [generated[i] for i in live], live,
+                          [len(generated[i]) for i in live])
+        got = [int(t) for t in (got.tolist() if hasattr(got, "tolist") else got)]
+        assert got == want, (step, got, want)
+        for i, t in zip(live, got):
+            generated[i].append(t)
+    history = pipes[2].history
+    assert history is not None and all(p.history is history for p in pipes)       # one history for the batch
+    assert history.held[pipes[4].history_row] == generated[4][:-1]             # the newest id goes up with the next step

@@ -122,9 +122,12 @@ def gated_linear(x, w_gate_up, resident=False):
     return swiglu(linear(x, w_gate_up, torch.float32)).to(x.dtype)
 
 
-def repetition_penalty(logits, prev, prev_len, penalty, window):
+def repetition_penalty(logits, prev, prev_len, penalty, window, row_map=None, append=None):
     for r in range(logits.shape[0]):
-        previous = prev[r, :int(prev_len[r])].tolist()
+        h = int(row_map[r]) if row_map is not None else r
+        if append is not None and int(append[0][r]) >= 0:
+            prev[h, int(append[0][r])] = int(append[1][r])
+        previous = prev[h, :int(prev_len[r])].tolist()
         logits[r] = plain_llama.apply_repetition_penalty(logits[r].cpu(), previous, float(penalty[r]),
                                                          int(window[r])).to(logits.device)
     return logits

@@ -181,6 +181,11 @@ def test_pipeline_is_built_like_the_references():
         InferenceOptions(repetition_penalty=0.0).validate()
 
 
+def test_repetition_penalty_from_a_history_kept_between_steps(cpu_kernels):
+    from engine_checks import penalty_history_check
+    penalty_history_check(torch.device("cpu"))
+
+
 def test_uniform_numbers_depend_on_seed_and_step_only():
     a = [uniform(1, s) for s in range(200)]
     assert all(0.0 <= u < 1.0 for u in a) and len(set(a)) > 190

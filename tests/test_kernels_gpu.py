@@ -385,6 +385,22 @@ def test_repetition_penalty():
     ref = kernel_refs.repetition_penalty(x.clone(), prev, n, pen, window)
     out = ops().repetition_penalty(x.to(DEV), prev.to(DEV), n.to(DEV), pen.to(DEV), window.to(DEV))
     close(out, ref, 1e-6)
+    # histories kept on the device: rows of a larger table in another order, one id appended by the kernel
+    table = torch.zeros(5, 8, dtype=torch.int32)
+    row_map = torch.tensor([3, 0, 4], dtype=torch.int32)
+    table[3, :3], table[0, :5], table[4, :0] = prev[0, :3], prev[1, :5], prev[2, :0]
+    pos = torch.tensor([3, 5, -1], dtype=torch.int32)
+    tok = torch.tensor([int(prev[0, 3]), int(prev[1, 5]), 0], dtype=torch.int32)
+    table_dev = table.to(DEV)
+    out = ops().repetition_penalty(x.to(DEV), table_dev, n.to(DEV), pen.to(DEV), window.to(DEV), row_map=row_map.to(DEV),
+                                   append=(pos.to(DEV), tok.to(DEV)))
+    close(out, ref, 1e-6)
+    assert table_dev[3, 3] == prev[0, 3] and table_dev[0, 5] == prev[1, 5]
+
+
+def test_repetition_penalty_from_a_history_kept_between_steps():
+    from engine_checks import penalty_history_check
+    penalty_history_check(DEV)
 
 
 def test_kernels_refuse_what_they_cannot_take():
