@@ -133,6 +133,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all of them)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="run only the 2,048-token prefill (for profiling)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="with --only-prefill: tokens of the one prompt (the line itself always reports 2,048)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -289,11 +291,11 @@ def main():
         L = cfg.num_hidden_layers
         return T * (L * qkv + (L - 1) * rest) + rows_out * (rest + 2 * cfg.hidden_size * vocab)
 
-    def prefill_point():
-        """One prompt of PREFILL_TOKENS tokens through model.step: best of ``reps`` after three warm-ups
+    def prefill_point(tokens=PREFILL_TOKENS):
+        """One prompt of ``tokens`` tokens through model.step: best of ``reps`` after three warm-ups
         (the first is eager, the second captures the step's graph, the rest replay it)."""
         import numpy as np
-        prompt = np.asarray(torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen))
+        prompt = np.asarray(torch.randint(0, vocab, (tokens,), generator=gen))
         times = []
         for it in range(3 + reps):
             s = cache.open_sequence()
@@ -307,7 +309,7 @@ def main():
                 times.append(a.elapsed_time(b_))
             cache.close_sequence(s)
         p_ms = min(times)
-        T = PREFILL_TOKENS
+        T = tokens
         flops = prefill_flops(T, 1) + cfg.num_hidden_layers * 2 * T * T * cfg.q_dim
         return {"value": round(T * 1000.0 / p_ms, 1), "tokens": T, "ms": round(p_ms, 3),
                 "frac": round(flops / (p_ms * 1e-3) / (compute_peak * 1e12), 4),
@@ -339,7 +341,7 @@ def main():
         return unequal_workload(args, model, cache, cfg, gen, pk, shape_name, dtype_name, compute_peak, weight_bytes, prefill_flops)
 
     if args.only_prefill:
-        print(json.dumps({"prefill": prefill_point(), "layers": cfg.num_hidden_layers}))
+        print(json.dumps({"prefill": prefill_point(args.prefill_tokens), "layers": cfg.num_hidden_layers}))
         return 0
 
     main_point = decode_point(args.batch, True)
