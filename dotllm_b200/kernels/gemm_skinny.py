@@ -1,7 +1,7 @@
 """Dispatch to the weight-streaming products for steps of a few rows (decode).
 
-Up to 16 rows go to the mma.sync kernel of csrc/gemm_skinny.cu, 17 to 128 rows to the tcgen05 kernel
-of csrc/gemm_decode_tc.cu (``gemm_decode_tc.run``, same contract).  The first cuts its work into
+Up to ``SKINNY_ROWS`` rows go to the mma.sync kernel of csrc/gemm_skinny.cu (it can take 16), more, up
+to 128, to the tcgen05 kernel of csrc/gemm_decode_tc.cu (``gemm_decode_tc.run``, same contract).  The first cuts its work into
 equal shares per warp; tiles that straddle two shares are summed through a scratch buffer with
 arrival counters.  Both are kept here per device (they are small and every launch leaves the
 counters zero).  Launches that share them must be on one stream.
@@ -22,7 +22,13 @@ _library.register_signatures({
     "dl_gemm_skinny_scratch": [_I, _I, _I, _I, _I, _P, _P],
 })
 
-SKINNY_ROWS = 16         # rows the mma.sync kernel takes; more go to the tcgen05 kernel
+KERNEL_ROWS = 16         # rows the mma.sync kernel can take (two tiles of eight)
+# Rows up to which the dispatcher gives a product to the mma.sync kernel; more go the way of 17 and
+# more (the gated product to the tcgen05 kernel, the plain ones to the library).  Measured on whole
+# decode steps at the 8B shape: 9 rows 4.76 against 4.79 ms, 12 rows 5.30 against 5.24, 16 rows 6.08
+# against 5.83 - the second tile of eight rows costs the mma.sync kernel more than the library's
+# launch costs the step.
+SKINNY_ROWS = 10
 MAX_ROWS = 128           # rows the two kernels take between them; beyond this the products are prefill products
 # Of 17 to 128 rows the gated product goes to the tcgen05 kernel (47 us against 56 for the library product plus
 # gating at the 8B shape and 64 rows).  The plain products do too when TC_PLAIN is set; measured inside a decode

@@ -102,7 +102,7 @@ class PendingProduct:
 
 class ScaledRows:
     """A normalised stream still lacking its factor per row: ``data`` = stream * gain (bfloat16) and the
-    sums of squares per part of 16 (up to 16 rows) or 128 columns, left by the product that added into the stream.  ``linear``
+    sums of squares per part of 16 (the mma.sync product's) or 128 columns (the tcgen05 product's), left by the product that added into the stream.  ``linear``
     and ``gated_linear`` take it as x and apply rsqrt(mean + eps) to their output rows - the product
     of the normalised rows, since the factor is one number per row.  ``tensor()`` gives the
     normalised rows themselves (valid until the stream is added to again)."""

@@ -420,8 +420,9 @@ def test_kernels_refuse_what_they_cannot_take():
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(64, 64), (200, 176), (1000, 320), (4096, 4096), (6144, 512)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_skinny(M, N, K, out_dtype):
+def test_gemm_skinny(M, N, K, out_dtype, monkeypatch):
     from dotllm_b200.kernels import gemm_skinny
+    monkeypatch.setattr(gemm_skinny, "SKINNY_ROWS", gemm_skinny.KERNEL_ROWS)      # every row count the kernel takes, not only those the dispatcher gives it
     g = torch.Generator().manual_seed(20)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
@@ -436,11 +437,12 @@ def test_gemm_skinny(M, N, K, out_dtype):
     assert torch.equal(gemm_skinny.run(x.to(DEV), w.to(DEV), out_dtype).cpu(), y.cpu())
 
 
-def test_gemm_skinny_repeats_with_full_rings():
+def test_gemm_skinny_repeats_with_full_rings(monkeypatch):
     """16 rows make the consumer warps the slower side, so the rings stay full and every slot is
     refilled the moment it is released: 30 launches must give the same bits as the first (a release
     that does not wait for the reads of the slot shows up as a few wrong output columns)."""
     from dotllm_b200.kernels import gemm_skinny
+    monkeypatch.setattr(gemm_skinny, "SKINNY_ROWS", gemm_skinny.KERNEL_ROWS)
     g = torch.Generator().manual_seed(27)
     x = torch.randn(16, 4096, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(4096, 4096, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
@@ -506,9 +508,9 @@ def test_products_that_add_and_normalise(M, H, K, N2, monkeypatch):
     # |d silu| <= 1.1; the output is rounded to bfloat16 once more
     slack = 1.1 * e_gate * (up.abs() + e_up) + (gate * torch.sigmoid(gate)).abs() * e_up + 2 ** -8 * want.abs() + 1e-5
     assert bool(((yg.double().cpu() - want).abs() <= slack).all())
-    # the same bits whatever else is in the batch: the first row alone (the first 17 where the
-    # tcgen05 product runs, which takes 17 rows or more)
-    sub = 1 if M <= 16 else 17
+    # the same bits whatever else is in the batch: the first row alone (where the tcgen05 product runs,
+    # the fewest rows that the dispatcher gives it)
+    sub = 1 if M <= gemm_skinny.SKINNY_ROWS else gemm_skinny.SKINNY_ROWS + 1
     if M > sub:
         s1 = stream0[:sub].clone()
         r1 = o.add_rmsnorm(s1, o.linear(a[:sub], w1, out_dtype=torch.float32, lazy=True), gain, eps, torch.bfloat16, lazy=True)
