@@ -901,13 +901,13 @@ extern "C" int dl_sample(const float* logits, int row_stride, int rows, int V, c
         DL_CHECK_LAUNCH("sample (greedy)");
         return DL_OK;
     }
-    // A cluster per row when the rows are long enough for the passes over global memory to matter and few
-    // enough for eight blocks each to find room at once; its slice must fit a block's shared memory.
+    // A cluster per row when the rows are long enough for the passes over global memory to matter; its
+    // slice must fit a block's shared memory.
     int span = (V + SMP_SPLIT - 1) / SMP_SPLIT;
     span = (span + 3) & ~3;
     const size_t slice_bytes = (size_t)span * sizeof(float);
     const bool fits = slice_bytes <= 160 * 1024 && rows <= 65535;
-    const bool split = mode == 2 || (mode == 0 && fits && V >= 8192 && rows <= 256);
+    const bool split = mode == 2 || (mode == 0 && fits && V >= 8192);
     if (mode == 2 && !fits) return dl_fail(DL_ERR_UNSUPPORTED, "sample: a row of %d values does not fit a cluster's shared memory", V);
     if (split && temperature != nullptr) {
         static size_t configured = 0;
