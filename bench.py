@@ -315,14 +315,18 @@ def main():
                 "frac": round(flops / (p_ms * 1e-3) / (compute_peak * 1e12), 4),
                 "peak": pk["source"] if args.dtype == "bfloat16" else "nominal fp32", "cv": spread(times)}
 
-    def generate_point(batch, prompt_len=128, new_tokens=256):
-        """Tokens per second of Model.generate itself: host prompts in, host tokens out, stop tokens off."""
+    def generate_point(batch, prompt_len=128, new_tokens=256, sampled=False):
+        """Tokens per second of Model.generate itself: host prompts in, host tokens out, stop tokens off.
+        ``sampled``: temperature 0.8, top-k 40, top-p 0.95 and a seed instead of greedy."""
         prompts = [torch.randint(0, vocab, (prompt_len,), generator=gen).tolist() for _ in range(batch)]
         need = batch * ((prompt_len + new_tokens + 63) // 64 * 64)
         if need > cache.max_tokens:
             return None
         generator = model.generator(cache=cache, max_batch=batch)
-        options = InferenceOptions(temperature=0.0, max_tokens=new_tokens, stop_token_ids=[])
+        if sampled:
+            options = InferenceOptions(temperature=0.8, top_k=40, top_p=0.95, seed=7, max_tokens=new_tokens, stop_token_ids=[])
+        else:
+            options = InferenceOptions(temperature=0.0, max_tokens=new_tokens, stop_token_ids=[])
         generator.generate(prompts[:batch], options)          # warm-up: captures the graph of this batch size
         times = []
         for _ in range(min(reps, 3)):
@@ -360,6 +364,9 @@ def main():
                 g = generate_point(b)
                 if g is not None:
                     generate[f"b{b}"] = g
+            g = generate_point(64, sampled=True)
+            if g is not None:
+                generate["b64_sampled"] = g
 
     step_bytes = weight_bytes + args.batch * main_point["mean_len"] * kv_bytes_per_token
     achieved = step_bytes / (main_point["ms"] * 1e-3) / 1e9
