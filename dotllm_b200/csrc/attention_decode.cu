@@ -434,13 +434,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
         }
     } else if (warp < n_stages) {
         // ------------------------------------------------------------ consumers (warp w owns stages w, w + n_stages, ...)
-        dl_grid_dependency_wait();       // q comes from the kernel before this one; out and the scratch may be in use by it
+        // The cut needs the lengths only, which are older than the kernel before this one: it is made
+        // while that kernel finishes, and q is waited for after it.
         float* my_o = merge_o + (size_t)warp * group * (HD + 4);
         const float scale2 = scale * 1.4426950408889634f;    // scores in units of log2
         int n0 = 0;                                          // pages of the runs before this one
         const AdCut cut = ad_cut(seq_len, n_seqs, nkv, window, gridDim.x, lane);
         AdWalk walk = ad_walk_begin(cut, seq_len, n_seqs, nkv, window, blockIdx.x, lane);
         AdSeg w;
+        dl_grid_dependency_wait();       // q comes from the kernel before this one; out and the scratch may be in use by it
         while (ad_walk_next(walk, w, seq_len, n_seqs, nkv, window)) {      // the same segments in every warp
             // Q rows g and g+8 of the group (zero beyond the group)
             uint4 qf_lo[DC], qf_hi[DC];
