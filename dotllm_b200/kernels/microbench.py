@@ -5,6 +5,7 @@
     python -m dotllm_b200.kernels.microbench attention_prefill --tokens 2048
     python -m dotllm_b200.kernels.microbench norm --rows 8 --width 4096
     python -m dotllm_b200.kernels.microbench rope --rows 8
+    python -m dotllm_b200.kernels.microbench sample --rows 8 --top-k 40 --top-p 0.95
 
 Prints one JSON line with the time, the algorithmic bytes or FLOPs, and the fraction of the
 measured peak.  The same command under ``ncu -k regex:<kernel>`` gives the kernel's counters.
@@ -88,7 +89,7 @@ def _paged(batch, context, nkv, hd, dev):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_skinny", "gemm_tc", "norm", "rope"])
+    ap.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_skinny", "gemm_tc", "norm", "rope", "sample"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -111,6 +112,10 @@ def main(argv=None):
                          "with DOTLLM_NVCC_EXTRA=-DPT_TIMELINE)")
     ap.add_argument("--no-tc", action="store_true", help="attention_prefill: the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--sequential-pages", action="store_true", help="pages of a sequence lie one after another")
+    ap.add_argument("--vocab", type=int, default=128256, help="sample: entries of a row of logits")
+    ap.add_argument("--top-k", type=int, default=0, help="sample: top-k (0: off)")
+    ap.add_argument("--top-p", type=float, default=1.0, help="sample: top-p (1: off)")
+    ap.add_argument("--one-block", action="store_true", help="sample: one block per row instead of a cluster of blocks")
     args = ap.parse_args(argv)
     if args.sequential_pages:
         global SCATTER_PAGES
@@ -280,6 +285,20 @@ def main(argv=None):
                                           table, k_pool, v_pool, nh, nkv, hd)
         ms, best = _time(fn, args.iters, flush)
         result.update(rows=rows, ms=ms, best_ms=best)
+    elif args.kernel == "sample":
+        # a temperature draw (optionally top-k and top-p) for `rows` rows of `vocab` logits; 20 launches a graph
+        rows, vocab = args.rows, args.vocab
+        x = torch.randn(rows, vocab, device=dev) * 3
+        one, u = torch.ones(rows, device=dev), torch.rand(rows, device=dev)
+        kw = {}
+        if args.top_k:
+            kw["top_k"] = torch.full((rows,), args.top_k, dtype=torch.int32, device=dev)
+        if args.top_p < 1.0:
+            kw["top_p"] = one * args.top_p
+        fn = lambda: ops.sample(x, temperature=one * 0.8, uniform=u, split=not args.one_block, **kw)
+        ms = _time_graph(lambda: [fn() for _ in range(20)], args.iters) / 20
+        result.update(rows=rows, vocab=vocab, top_k=args.top_k, top_p=args.top_p, one_block=args.one_block, ms=ms,
+                      bytes=rows * vocab * 4)
     result["peaks"] = source
     print(json.dumps(result))
     return 0
