@@ -3,7 +3,11 @@
 // The reference runs its prefill projections through cuBLAS and gates the feed-forward with a
 // separate kernel (src/DotLLM.Cuda/CudaGemm.cs:29-40, native/kernels/swiglu.cu:7-41).  This kernel
 // is for the products where fusing pays: with W = [gate; up] the epilogue writes silu(gate) * up, so
-// the [T, 2I] intermediate never goes to memory.  It also takes the plain product.
+// the [T, 2I] intermediate never goes to memory.  It also takes the plain product, and the Q/K/V
+// product of a prompt with the position encoding and the cache write in its epilogue: W = [Wq; Wk; Wv],
+// the query columns come out rotated, the key columns are rotated and go straight to their cache
+// pages, the value columns to theirs (transposed), so that no kernel has to read the product back to
+// do it (native/kernels/rope.cu and the cache write are kernels of their own in the reference).
 //
 // Shape: persistent, one block per multiprocessor, six warps with fixed roles.
 //   warp 0   one thread issues the tensor-map copies (TMA, 128-byte swizzle) of x and W tiles into a
@@ -24,6 +28,7 @@
 #include "tma.cuh"
 #include "tcgen05.cuh"
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #define GT_BM 128
@@ -76,12 +81,116 @@ __device__ __forceinline__ void gt_store32<float>(float* row_ptr, int col0, int 
     }
 }
 
-// GATED: W is [2N, K], gate rows then up rows; a tile's accumulator holds 128 gate columns then the
-// 128 matching up columns, and the output tile is 128 columns wide.
-template <typename TOut, bool GATED>
+enum { GT_PLAIN = 0, GT_GATED = 1, GT_QKV = 2 };
+
+// What the Q/K/V epilogue needs: the columns' split, the rotary tables, where every token (row of x)
+// stands in its sequence, and the cache.  Tiles of 256 columns never straddle two of the three ranges
+// (the host checks that q_cols and kv_cols are multiples of 256), nor a head (head_dim 64 or 128).
+struct GtQkv {
+    int q_cols, kv_cols, hd, nkv;
+    const float* cos_t;              // [table_rows, hd/2]
+    const float* sin_t;
+    int table_rows;
+    const int32_t* token_pos;        // [M] position of the row's token in its sequence
+    const int32_t* token_seq;        // [M] its sequence's row in the block table
+    const int32_t* block_table;      // [sequences, bt_stride] page ids
+    int bt_stride;
+    __nv_bfloat16* k_pool;
+    __nv_bfloat16* v_pool;
+    int n_pages;
+};
+
+// The same roundings as the rope kernels (no contraction), so that the fused and the separate way
+// give the same bits.
+__device__ __forceinline__ float gt_rot_lo(float x0, float x1, float c, float s) { return __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)); }
+__device__ __forceinline__ float gt_rot_hi(float x0, float x1, float c, float s) { return __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)); }
+
+// 32 consecutive bfloat16 values to a 16-byte aligned place.
+__device__ __forceinline__ void gt_store32_bf16(__nv_bfloat16* dst, const float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(gt_pack(v[8 * i], v[8 * i + 1]), gt_pack(v[8 * i + 2], v[8 * i + 3]),
+                                                            gt_pack(v[8 * i + 4], v[8 * i + 5]), gt_pack(v[8 * i + 6], v[8 * i + 7]));
+}
+
+// The Q/K/V epilogue of one 128 x 256 tile for this thread's row.  `taddr`: the thread's lane of the
+// accumulator.  Every lane of the warp runs the tensor-memory loads; stores are for live rows only.
+__device__ __forceinline__ void gt_qkv_epilogue(uint32_t taddr, int col_base, int row, bool row_ok, __nv_bfloat16* __restrict__ out,
+                                                int out_stride, const GtQkv& qkv) {
+    const int hd = qkv.hd, half = hd / 2;
+    const int region = col_base < qkv.q_cols ? 0 : (col_base < qkv.q_cols + qkv.kv_cols ? 1 : 2);
+    int pos = -1, in_page = 0;
+    long long page = -1;
+    if (row_ok) {
+        pos = qkv.token_pos[row];
+        if (pos < 0 || pos >= qkv.table_rows) pos = -1;       // host-validated; never index outside
+        if (pos >= 0 && region != 0) {
+            page = qkv.block_table[(size_t)qkv.token_seq[row] * qkv.bt_stride + pos / DL_PAGE];
+            if (page < 0 || page >= qkv.n_pages) page = -1;
+            in_page = pos % DL_PAGE;
+        }
+    }
+    if (region == 2) {
+        // values: no rotation; the cache holds them transposed, [dim][token in page] - the lanes of a
+        // warp are consecutive tokens, so each store instruction writes a run of one dimension's row
+        const int kv0 = (col_base - qkv.q_cols - qkv.kv_cols) / hd;
+#pragma unroll 1
+        for (int c0 = 0; c0 < GT_BN; c0 += 32) {
+            float v[32];
+            tc_tmem_load32(taddr + (uint32_t)c0, v);
+            if (page >= 0) {
+                const int kvh = kv0 + c0 / hd, d0 = c0 % hd;
+                __nv_bfloat16* dst = qkv.v_pool + dl_v_offset((int)page, qkv.nkv, kvh, d0, hd) + in_page;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dst[(size_t)i * DL_PAGE] = __float2bfloat16_rn(v[i]);
+            }
+        }
+        return;
+    }
+    // queries and keys: dims c .. c+31 of the low half of a head pair with the same dims of the high half
+#pragma unroll 1
+    for (int h0 = 0; h0 < GT_BN; h0 += hd) {
+#pragma unroll 1
+        for (int c = 0; c < half; c += 32) {
+            float lo[32], hi[32];
+            tc_tmem_load32(taddr + (uint32_t)(h0 + c), lo);
+            tc_tmem_load32(taddr + (uint32_t)(h0 + half + c), hi);
+            // no lane leaves the loop early: the loads above are the whole warp's
+            const float* cs = qkv.cos_t + (size_t)(pos < 0 ? 0 : pos) * half + c;
+            const float* sn = qkv.sin_t + (size_t)(pos < 0 ? 0 : pos) * half + c;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(cs + i), s4 = *reinterpret_cast<const float4*>(sn + i);
+                const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    // the product is rounded to bfloat16 before it is rotated, as the separate kernels see it
+                    const float x0 = __bfloat162float(__float2bfloat16_rn(lo[i + e])), x1 = __bfloat162float(__float2bfloat16_rn(hi[i + e]));
+                    lo[i + e] = gt_rot_lo(x0, x1, cc[e], ss[e]);
+                    hi[i + e] = gt_rot_hi(x0, x1, cc[e], ss[e]);
+                }
+            }
+            __nv_bfloat16* dst = nullptr;
+            if (region == 0) {
+                if (pos >= 0) dst = out + (size_t)row * out_stride + col_base + h0;
+            } else if (page >= 0) {
+                dst = qkv.k_pool + dl_k_offset((int)page, qkv.nkv, (col_base - qkv.q_cols + h0) / hd, in_page, hd);
+            }
+            if (dst != nullptr) {
+                gt_store32_bf16(dst + c, lo);
+                gt_store32_bf16(dst + half + c, hi);
+            }
+        }
+    }
+}
+
+// MODE GT_GATED: W is [2N, K], gate rows then up rows; a tile's accumulator holds 128 gate columns then
+// the 128 matching up columns, and the output tile is 128 columns wide.  GT_QKV: see GtQkv.
+template <typename TOut, int MODE>
 __global__ void __launch_bounds__(GT_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, TOut* __restrict__ out,
-               int out_stride, int M, int N, int K, int vec_ok, int* __restrict__ status) {
+               int out_stride, int M, int N, int K, int vec_ok, const GtQkv qkv, int* __restrict__ status) {
+    constexpr bool GATED = MODE == GT_GATED;
     extern __shared__ unsigned char gt_smem_raw[];
     // the swizzled tiles must start on 1024-byte boundaries
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)gt_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -205,17 +314,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * GT_BN);
             TOut* row_ptr = out + (size_t)row * out_stride;
             const int col_base = tn * OUT_BN;
+            if (MODE == GT_QKV) {
+                if (std::is_same<TOut, __nv_bfloat16>::value)
+                    gt_qkv_epilogue(taddr, col_base, row, row < M, reinterpret_cast<__nv_bfloat16*>(out), out_stride, qkv);
+            } else {
 #pragma unroll 1
-            for (int c0 = 0; c0 < OUT_BN; c0 += 32) {
-                float v[32];
-                tc_tmem_load32(taddr + (uint32_t)c0, v);        // every lane of the warp takes part
-                if (GATED) {
-                    float u[32];
-                    tc_tmem_load32(taddr + (uint32_t)(GT_BN / 2 + c0), u);
+                for (int c0 = 0; c0 < OUT_BN; c0 += 32) {
+                    float v[32];
+                    tc_tmem_load32(taddr + (uint32_t)c0, v);    // every lane of the warp takes part
+                    if (GATED) {
+                        float u[32];
+                        tc_tmem_load32(taddr + (uint32_t)(GT_BN / 2 + c0), u);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = v[i] * (1.0f / (1.0f + expf(-v[i]))) * u[i];
+                        for (int i = 0; i < 32; ++i) v[i] = v[i] * (1.0f / (1.0f + expf(-v[i]))) * u[i];
+                    }
+                    if (row < M && col_base + c0 < N) gt_store32<TOut>(row_ptr, col_base + c0, N, v, vec_ok != 0);
                 }
-                if (row < M && col_base + c0 < N) gt_store32<TOut>(row_ptr, col_base + c0, N, v, vec_ok != 0);
             }
             tc_fence_before();
             __syncwarp();
@@ -264,13 +378,14 @@ static int gt_tensor_map(CUtensorMap* out, const void* base, long long rows, lon
     return DL_OK;
 }
 
-template <typename TOut, bool GATED>
+template <typename TOut, int MODE>
 static int gt_launch(cudaStream_t s, const void* x, int x_stride, const void* w, void* out, int out_stride, int M, int N, int K,
-                     int blocks, int* status) {
+                     int blocks, int* status, const GtQkv& qkv = GtQkv{}) {
+    constexpr bool GATED = MODE == GT_GATED;
     const size_t smem = (size_t)GT_STAGES * GT_STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TOut, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TOut, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return dl_fail(DL_ERR_LAUNCH, "gemm_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -288,7 +403,7 @@ static int gt_launch(cudaStream_t s, const void* x, int x_stride, const void* w,
     if (blocks > n_tiles) blocks = (int)n_tiles;
     const int elem = (int)sizeof(TOut);
     const int vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)out_stride * elem) % 16 == 0) ? 1 : 0;
-    gemm_tc_kernel<TOut, GATED><<<blocks, GT_THREADS, smem, s>>>(tmap_x, tmap_w, (TOut*)out, out_stride, M, N, K, vec_ok, status);
+    gemm_tc_kernel<TOut, MODE><<<blocks, GT_THREADS, smem, s>>>(tmap_x, tmap_w, (TOut*)out, out_stride, M, N, K, vec_ok, qkv, status);
     DL_CHECK_LAUNCH("gemm_tc");
     return DL_OK;
 }
@@ -311,8 +426,37 @@ extern "C" int dl_gemm_tc_bf16(const void* x, int x_stride, const void* w, void*
     cudaStream_t s = (cudaStream_t)stream;
     if (flags & 1) {
         DL_REQUIRE(out_dtype == DL_BF16, "gemm_tc: the gated product writes bfloat16");
-        return gt_launch<__nv_bfloat16, true>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+        return gt_launch<__nv_bfloat16, GT_GATED>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
     }
-    if (out_dtype == DL_F32) return gt_launch<float, false>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
-    return gt_launch<__nv_bfloat16, false>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+    if (out_dtype == DL_F32) return gt_launch<float, GT_PLAIN>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+    return gt_launch<__nv_bfloat16, GT_PLAIN>(s, x, x_stride, w, out, out_stride, M, N, K, blocks, status);
+}
+
+// The Q/K/V product of a prompt with the rotation and the cache write in its epilogue.
+// x: bf16 [M, K]; w: bf16 [q_cols + 2 kv_cols, K] (query rows, key rows, value rows), contiguous.
+// q_out: bf16 [M, q_cols] rows q_stride apart: the rotated queries.  The rotated keys and the values go to
+// the pages of the cache (k_pool [pages, nkv, 64, hd], v_pool [pages, nkv, hd, 64]) that block_table
+// [sequences, bt_stride] names for token_seq[row] at position token_pos[row].  cos_t, sin_t: float32
+// [table_rows, hd/2] (a full-width rotation, pairs d and d + hd/2).  head_dim 64 or 128; q_cols and
+// kv_cols multiples of 256.  Same bits as the plain product followed by dl_rope_cache_write.
+extern "C" int dl_gemm_tc_qkv_bf16(const void* x, int x_stride, const void* w, void* q_out, int q_stride, int M, int K, int q_cols,
+                                   int kv_cols, int hd, int nkv, const float* cos_t, const float* sin_t, int table_rows,
+                                   const int32_t* token_pos, const int32_t* token_seq, const int32_t* block_table, int bt_stride,
+                                   void* k_pool, void* v_pool, int n_pages, int blocks, int* status, void* stream) {
+    DL_REQUIRE(M >= 1 && K >= 8 && K % 8 == 0, "gemm_tc_qkv: M=%d K=%d (K must be a positive multiple of 8)", M, K);
+    DL_REQUIRE(hd == 64 || hd == 128, "gemm_tc_qkv: head_dim %d (takes 64 and 128)", hd);
+    DL_REQUIRE(q_cols > 0 && kv_cols > 0 && q_cols % GT_BN == 0 && kv_cols % GT_BN == 0 && kv_cols == nkv * hd,
+               "gemm_tc_qkv: %d query and %d key columns must be multiples of %d (and the key columns nkv * head_dim)", q_cols,
+               kv_cols, GT_BN);
+    DL_REQUIRE(x_stride >= K && x_stride % 8 == 0 && q_stride >= q_cols && q_stride % 8 == 0, "gemm_tc_qkv: row strides");
+    DL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)q_out % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 &&
+                   ((uintptr_t)v_pool % 16) == 0 && ((uintptr_t)cos_t % 16) == 0 && ((uintptr_t)sin_t % 16) == 0,
+               "gemm_tc_qkv: x, W, q, the pools and the tables must be 16-byte aligned");
+    DL_REQUIRE(cos_t && sin_t && table_rows > 0 && token_pos && token_seq && block_table && bt_stride >= 1 && n_pages > 0,
+               "gemm_tc_qkv: needs tables, positions, a block table and a cache");
+    DL_REQUIRE(status != nullptr, "gemm_tc_qkv: needs a status word");
+    GtQkv qkv{q_cols, kv_cols, hd, nkv, cos_t, sin_t, table_rows, token_pos, token_seq, block_table, bt_stride,
+              (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages};
+    return gt_launch<__nv_bfloat16, GT_QKV>((cudaStream_t)stream, x, x_stride, w, q_out, q_stride, M, q_cols + 2 * kv_cols, K, blocks,
+                                            status, qkv);
 }

@@ -308,6 +308,29 @@ def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, bl
                      scale, window, plan=plan, score_hook=score_hook)
 
 
+def qkv_rope_cache(x, w_qkv, cos, sin, rotary_dim, token_seq, token_pos, block_table, k_pool, v_pool,
+                   n_heads, n_kv_heads, head_dim):
+    """The Q/K/V product of a prompt step with the rotation and the cache write in its epilogue: returns
+    the rotated queries [T, nh*hd] (the rotated keys and the values are in the cache), or None when the
+    step is not one the tcgen05 product takes this way (few rows, other head sizes, a partial rotation,
+    float32) - the caller then runs ``linear`` and ``rope_cache_attention``.  Same bits as those."""
+    from . import gemm_tc
+    q_cols, kv_cols = n_heads * head_dim, n_kv_heads * head_dim
+    if isinstance(x, ScaledRows) or not x.is_cuda \
+            or not gemm_tc.takes_qkv(x, w_qkv, q_cols, kv_cols, head_dim, rotary_dim, cos, sin, k_pool, v_pool):
+        return None
+    _need_cuda(x, w_qkv, cos, sin, token_seq, token_pos, block_table, k_pool, v_pool)
+    _check_pools(k_pool, v_pool, n_kv_heads, head_dim)
+    _int32(token_seq, "token_seq")
+    _int32(token_pos, "token_pos")
+    _int32(block_table, "block_table")
+    if token_pos.numel() != x.shape[0] or token_seq.numel() != x.shape[0] or cos.shape != sin.shape \
+            or cos.shape[1] != head_dim // 2:
+        raise KernelError("qkv_rope_cache: one position and sequence per row, tables [positions, head_dim/2]")
+    return gemm_tc.run_qkv(x, w_qkv, q_cols, kv_cols, head_dim, n_kv_heads, cos, sin, token_pos, token_seq, block_table,
+                           k_pool, v_pool)
+
+
 # ---------------------------------------------------------------- feed-forward
 def swiglu(gate_up):
     """silu(gate) * up for gate_up = [gate | up] of shape [T, 2I]; returns [T, I]."""

@@ -74,12 +74,22 @@ class AttentionMixer(Mixer):
 
     def forward(self, x, step, cache_view):
         qd, kvd = self.q_dim, self.kv_dim
+        fused = self.position.fused_rotary()
+        if cache_view.writes and fused is not None:
+            # a prompt step: rotation and cache write in the product's epilogue, then attention over the cache
+            q = ops.qkv_rope_cache(x, self.w_qkv, fused[0], fused[1], fused[2], step.token_seq, step.token_pos,
+                                   cache_view.block_table, cache_view.k, cache_view.v, self.n_heads, self.n_kv_heads,
+                                   self.head_dim)
+            if q is not None:
+                a = ops.attention(q, cache_view.k, cache_view.v, step.token_seq, step.token_pos, cache_view.block_table,
+                                  self.n_heads, self.n_kv_heads, self.head_dim, self.scale, int(self.window or 0),
+                                  plan=step.attention_plan, score_hook=self.score_hook if self.score_hook else None)
+                return ops.linear(a, self.w_o, out_dtype=BRANCH_DTYPE, resident=True, lazy=True)
         if cache_view.writes:
             qkv = ops.linear(x, self.w_qkv, resident=True)
             q, k, v = qkv[:, :qd], qkv[:, qd:qd + kvd], qkv[:, qd + kvd:]
         else:                                   # reads another execution's cache: only queries
             q, k, v = ops.linear(x, self.w_qkv[:qd], resident=True), None, None
-        fused = self.position.fused_rotary()
         if fused is None:
             self.position.apply(q, k, step.token_pos)
             cos = sin = None

@@ -207,6 +207,48 @@ def test_rope_cache_write(dtype, nh, nkv, hd, rd, news):
     assert torch.equal(d_pools[1].cpu(), ref_pools[1])  # V is copied, not computed
 
 
+@pytest.mark.parametrize("nh,nkv,hd,K", [(4, 2, 128, 192), (8, 4, 64, 320), (2, 2, 128, 4096)])
+def test_qkv_product_that_rotates_and_writes_the_cache(nh, nkv, hd, K, monkeypatch):
+    """A prompt step's Q/K/V product with the rotation and the cache write in its epilogue: the rotated
+    queries and every page of the cache must have the bits that the library product followed by the rope
+    and cache-write kernel gives - two sequences of unequal lengths that start at different positions
+    (one inside a page), rows that are no multiple of the tile, pages in another order than the tokens."""
+    from dotllm_b200.kernels import gemm_tc
+    monkeypatch.setattr(gemm_tc, "QKV_FUSED", True)            # off by default: the library's product is faster at the shapes met
+    g = torch.Generator().manual_seed(61)
+    starts, news = [70, 0], [200, 131]                         # positions 70 .. 269 and 0 .. 130
+    token_seq = [0] * news[0] + [1] * news[1]
+    token_pos = list(range(starts[0], starts[0] + news[0])) + list(range(starts[1], starts[1] + news[1]))
+    T = len(token_seq)
+    n_pages = 12
+    table = torch.tensor([[9, 3, 11, 0, 5], [7, 2, 10, -1, -1]], dtype=torch.int32)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((nh + 2 * nkv) * hd, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    cos, sin = plain_llama.rope_tables(range(512), hd, 10000.0)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    seq_t, pos_t = torch.tensor(token_seq, dtype=torch.int32, device=DEV), torch.tensor(token_pos, dtype=torch.int32, device=DEV)
+    def pools():
+        gp = torch.Generator().manual_seed(62)                  # what the pages held before must survive where nothing is written
+        return [torch.randn(n_pages, nkv, 64, hd, generator=gp).to(torch.bfloat16).to(DEV),
+                torch.randn(n_pages, nkv, hd, 64, generator=gp).to(torch.bfloat16).to(DEV)]
+    qd, kvd = nh * hd, nkv * hd
+    ref_pools = pools()
+    qkv = ops().linear(x, w)
+    ref_q = qkv[:, :qd].contiguous()
+    ops().rope_cache_write(ref_q, qkv[:, qd:qd + kvd], qkv[:, qd + kvd:], cos, sin, hd, seq_t, pos_t, table.to(DEV), *ref_pools,
+                           nh, nkv, hd)
+    got_pools = pools()
+    q = ops().qkv_rope_cache(x, w, cos, sin, hd, seq_t, pos_t, table.to(DEV), *got_pools, nh, nkv, hd)
+    assert q is not None
+    from dotllm_b200.kernels import library
+    library.check_status()
+    assert torch.equal(q, ref_q)
+    assert torch.equal(got_pools[0], ref_pools[0]) and torch.equal(got_pools[1], ref_pools[1])
+    # a decode step's few rows, a partial rotation and float32 are not its cases
+    assert ops().qkv_rope_cache(x[:64], w, cos, sin, hd, seq_t[:64], pos_t[:64], table.to(DEV), *got_pools, nh, nkv, hd) is None
+    assert ops().qkv_rope_cache(x, w, cos, sin, hd // 2, seq_t, pos_t, table.to(DEV), *got_pools, nh, nkv, hd) is None
+
+
 def test_rope_known_rotation():
     """Position 0 changes nothing; at position 1 the pair (1, 0) of frequency 1 becomes
     (cos 1, sin 1) (cf. RoPETests.PositionZero_NoChange / KnownRotation_HandCalculated,
