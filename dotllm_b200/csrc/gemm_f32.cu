@@ -62,12 +62,94 @@ gemm_f32_kernel(const float* __restrict__ x, int x_stride, const float* __restri
     }
 }
 
+// The same product for many rows: tiles of 128 x 128, eight by eight outputs per thread, operands
+// fetched sixteen bytes at a time and the next block of k on its way while this one is multiplied.
+// Every output is still one thread's chain of fused multiply-adds over k in ascending order, so the
+// bits are those of the kernel above (a row's result does not depend on which kernel its step met).
+#define GL_BM 128
+#define GL_BN 128
+#define GL_BK 16
+
+__global__ void __launch_bounds__(256)
+gemm_f32_large_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ w,
+                      float* __restrict__ y, int y_stride, int M, int N, int K) {
+    __shared__ __align__(16) float xs[2][GL_BK][GL_BM + 4];
+    __shared__ __align__(16) float ws[2][GL_BK][GL_BN + 4];
+    const int tid = threadIdx.x;
+    const int ty = tid / 16, tx = tid % 16;                  // outputs rows ty*8 .., columns tx*8 ..
+    const int m0 = blockIdx.y * GL_BM, n0 = blockIdx.x * GL_BN;
+    // loads: 128 rows x 16 k per operand = 512 pieces of four k; a thread takes two of each operand
+    const int lrow = tid / 4, lk = (tid % 4) * 4;            // rows lrow and lrow + 64
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+    float4 px[2], pw[2];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int xr = m0 + lrow + 64 * h, wr = n0 + lrow + 64 * h, k = k0 + lk;
+            px[h] = (xr < M && k < K) ? *reinterpret_cast<const float4*>(x + (size_t)xr * x_stride + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            pw[h] = (wr < N && k < K) ? *reinterpret_cast<const float4*>(w + (size_t)wr * K + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto stash = [&](int b) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = lrow + 64 * h;
+            xs[b][lk + 0][r] = px[h].x; xs[b][lk + 1][r] = px[h].y; xs[b][lk + 2][r] = px[h].z; xs[b][lk + 3][r] = px[h].w;
+            ws[b][lk + 0][r] = pw[h].x; ws[b][lk + 1][r] = pw[h].y; ws[b][lk + 2][r] = pw[h].z; ws[b][lk + 3][r] = pw[h].w;
+        }
+    };
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int b = 0;
+    for (int k0 = 0; k0 < K; k0 += GL_BK, b ^= 1) {
+        const bool more = k0 + GL_BK < K;
+        if (more) fetch(k0 + GL_BK);
+#pragma unroll
+        for (int kk = 0; kk < GL_BK; ++kk) {
+            float a[8], c[8];
+            const float4 a0 = *reinterpret_cast<const float4*>(&xs[b][kk][ty * 8]), a1 = *reinterpret_cast<const float4*>(&xs[b][kk][ty * 8 + 4]);
+            const float4 c0 = *reinterpret_cast<const float4*>(&ws[b][kk][tx * 8]), c1 = *reinterpret_cast<const float4*>(&ws[b][kk][tx * 8 + 4]);
+            a[0] = a0.x, a[1] = a0.y, a[2] = a0.z, a[3] = a0.w, a[4] = a1.x, a[5] = a1.y, a[6] = a1.z, a[7] = a1.w;
+            c[0] = c0.x, c[1] = c0.y, c[2] = c0.z, c[3] = c0.w, c[4] = c1.x, c[5] = c1.y, c[6] = c1.z, c[7] = c1.w;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], c[j], acc[i][j]);
+        }
+        if (more) stash(b ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = m0 + ty * 8 + i;
+        if (r >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = n0 + tx * 8 + j;
+            if (c < N) y[(size_t)r * y_stride + c] = acc[i][j];
+        }
+    }
+}
+
 // x: [M, K] rows x_stride apart; w: contiguous [N, K]; y: [M, N] rows y_stride apart.
 extern "C" int dl_gemm_f32(const float* x, int x_stride, const float* w, float* y, int y_stride, int M, int N,
                            int K, void* stream) {
     DL_REQUIRE(M >= 0 && N > 0 && K > 0 && x_stride >= K && y_stride >= N, "gemm_f32: bad sizes M=%d N=%d K=%d",
                M, N, K);
     if (M == 0) return DL_OK;
+    if (M >= 128 && K % 4 == 0 && x_stride % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0) {
+        dim3 lgrid((N + GL_BN - 1) / GL_BN, (M + GL_BM - 1) / GL_BM);
+        DL_REQUIRE(lgrid.y <= 65535, "gemm_f32: too many rows (%d)", M);
+        gemm_f32_large_kernel<<<lgrid, 256, 0, (cudaStream_t)stream>>>(x, x_stride, w, y, y_stride, M, N, K);
+        DL_CHECK_LAUNCH("gemm_f32");
+        return DL_OK;
+    }
     dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
     DL_REQUIRE(grid.y <= 65535, "gemm_f32: too many rows (%d)", M);
     gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, x_stride, w, y, y_stride, M, N, K);
