@@ -137,12 +137,58 @@ gemm_f32_large_kernel(const float* __restrict__ x, int x_stride, const float* __
     }
 }
 
+// And for a decode step's few rows (up to 16): blocks of 16 rows x 16 outputs, one output per thread,
+// so that a matrix of 4,096 rows is 256 blocks streaming 16 rows of W each (the 64 x 64 tiles above
+// would be 64 blocks, most of whose rows of x are padding).  The same chain per output, the same bits.
+#define GS32_BK 64
+
+__global__ void __launch_bounds__(256)
+gemm_f32_skinny_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ w,
+                       float* __restrict__ y, int y_stride, int M, int N, int K) {
+    __shared__ float xs[2][16][GS32_BK + 1];
+    __shared__ float ws[2][16][GS32_BK + 1];
+    const int tid = threadIdx.x;
+    const int m = tid / 16, n = tid % 16;                     // this thread's output
+    const int n0 = blockIdx.x * 16;
+    const int lrow = tid / 16, lk = (tid % 16) * 4;           // this thread's piece of a tile: four k of one row
+    float4 px, pw;
+    auto fetch = [&](int k0) {
+        const int k = k0 + lk, wr = n0 + lrow;
+        px = (lrow < M && k < K) ? *reinterpret_cast<const float4*>(x + (size_t)lrow * x_stride + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        pw = (wr < N && k < K) ? *reinterpret_cast<const float4*>(w + (size_t)wr * K + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto stash = [&](int b) {
+        xs[b][lrow][lk] = px.x, xs[b][lrow][lk + 1] = px.y, xs[b][lrow][lk + 2] = px.z, xs[b][lrow][lk + 3] = px.w;
+        ws[b][lrow][lk] = pw.x, ws[b][lrow][lk + 1] = pw.y, ws[b][lrow][lk + 2] = pw.z, ws[b][lrow][lk + 3] = pw.w;
+    };
+    float acc = 0.f;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int b = 0;
+    for (int k0 = 0; k0 < K; k0 += GS32_BK, b ^= 1) {
+        const bool more = k0 + GS32_BK < K;
+        if (more) fetch(k0 + GS32_BK);
+#pragma unroll
+        for (int kk = 0; kk < GS32_BK; ++kk) acc = fmaf(xs[b][m][kk], ws[b][n][kk], acc);
+        if (more) stash(b ^ 1);
+        __syncthreads();
+    }
+    if (m < M && n0 + n < N) y[(size_t)m * y_stride + n0 + n] = acc;
+}
+
 // x: [M, K] rows x_stride apart; w: contiguous [N, K]; y: [M, N] rows y_stride apart.
 extern "C" int dl_gemm_f32(const float* x, int x_stride, const float* w, float* y, int y_stride, int M, int N,
                            int K, void* stream) {
     DL_REQUIRE(M >= 0 && N > 0 && K > 0 && x_stride >= K && y_stride >= N, "gemm_f32: bad sizes M=%d N=%d K=%d",
                M, N, K);
     if (M == 0) return DL_OK;
+    const bool vec_ok = K % 4 == 0 && x_stride % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0;
+    if (M <= 16 && vec_ok) {
+        gemm_f32_skinny_kernel<<<(N + 15) / 16, 256, 0, (cudaStream_t)stream>>>(x, x_stride, w, y, y_stride, M, N, K);
+        DL_CHECK_LAUNCH("gemm_f32");
+        return DL_OK;
+    }
     if (M >= 128 && K % 4 == 0 && x_stride % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0) {
         dim3 lgrid((N + GL_BN - 1) / GL_BN, (M + GL_BM - 1) / GL_BM);
         DL_REQUIRE(lgrid.y <= 65535, "gemm_f32: too many rows (%d)", M);
