@@ -12,7 +12,11 @@ Here one object serves a batch:
   storage type when its mixer asks for one); a group with a window gives pages
   back once every token in them is older than the window.  A "state" group holds a fixed-size
   tensor per slot, zeroed when a sequence opens;
-* an execution that reads another execution's cache gets a view of that storage and never writes.
+* an execution that reads another execution's cache gets a view of that storage and never writes;
+* one slot and one page per group beyond those the pools hand out (``idle_slot``, ``idle_page``): a
+  step whose launch shapes are wider than its batch (a captured decode step that serves several
+  batch sizes) points its idle rows there, as sequences of one token whose results nobody reads.
+  No live sequence ever holds them, so what idle rows write reaches no result.
 
 Pages are counted in tokens: ``max_tokens`` is the most tokens live sequences may hold at once,
 each sequence's count rounded up to a whole page.
@@ -63,15 +67,16 @@ class CacheGroup:
             self.window = need.window
             self.pages = IdPool(n_pages, "page")
             dtype = need.dtype or runtime.dtype
-            self.k = torch.zeros((n, n_pages, need.n_kv_heads, PAGE, need.key_width()), dtype=dtype, device=runtime.device)
-            self.v = torch.zeros((n, n_pages, need.n_kv_heads, need.value_width(), PAGE), dtype=dtype, device=runtime.device)
+            # one page more than the pool hands out: the cache's idle page
+            self.k = torch.zeros((n, n_pages + 1, need.n_kv_heads, PAGE, need.key_width()), dtype=dtype, device=runtime.device)
+            self.v = torch.zeros((n, n_pages + 1, need.n_kv_heads, need.value_width(), PAGE), dtype=dtype, device=runtime.device)
             self.state = None
         elif self.kind == "state":
             self.window = None
             self.pages = None
             self.k = self.v = None
-            self.state = torch.zeros((n, n_slots, *need.state_shape), dtype=need.state_dtype,
-                                     device=runtime.device)
+            self.state = torch.zeros((n, n_slots + 1, *need.state_shape), dtype=need.state_dtype,
+                                     device=runtime.device)    # one slot more: the cache's idle slot
         else:
             raise CacheError(f"unknown cache kind {need.kind!r}")
 
@@ -100,6 +105,7 @@ class ModelCache:
         # every live sequence holds at least one page, so more slots than pages are never used
         self.n_slots = int(max_sequences) if max_sequences else self.n_pages
         self.slots = IdPool(self.n_slots, "slot")
+        self.idle_slot, self.idle_page = self.n_slots, self.n_pages      # never handed out
         self.groups = []
         self.entry_group = {}                       # schedule entry -> (group index, owner entry)
         by_key = {}

@@ -12,6 +12,8 @@ The same kernels run, on the same data, as in an eager step: graphs change launc
 """
 from __future__ import annotations
 
+import time
+
 import numpy as np
 import torch
 
@@ -26,6 +28,7 @@ class _Captured:
     def __init__(self, model, cache, batch, pages, n_groups):
         dev = model.runtime.device
         self.batch, self.pages = batch, pages
+        self.idle_slot, self.idle_pages = cache.idle_slot, [cache.idle_page]
         self.capacity = pages * PAGE                       # longest sequence this graph serves
         n = 3 * batch + n_groups * batch * pages           # positions, lengths, slots, block tables
         self.ints = torch.zeros(n, dtype=torch.int32, device=dev)
@@ -63,7 +66,10 @@ class _Captured:
 
     def stage(self, seqs, tokens, kv_groups, metadata=True):
         """Copy this step's positions, lengths, slots and block tables (``metadata``) and its tokens
-        (when the host supplies them) to the device."""
+        (when the host supplies them) to the device.  Fewer sequences than the graph has rows: the
+        other rows are idle, each token 0 at position 0 of a sequence in the cache's idle slot and
+        page, with a length of 0 after the step (`AttentionPlan.seq_total`): the decode attention
+        gives it no work, whatever else runs on it stays in its own row."""
         i = self.turn
         self.turn = (self.turn + 1) % _RING
         if self.events[i] is not None:
@@ -72,18 +78,20 @@ class _Captured:
         if not metadata:
             host, view = self.host[i], self.host_views[i]
             n = 3 * b + self.table_mirror.size
-            view[n:n + b] = tokens
+            view[n:n + len(tokens)] = tokens
+            view[n + len(tokens):n + b] = 0
             self.tokens.copy_(host[n:n + b], non_blocking=True)
             self.h2d_bytes += 4 * b
             ev = torch.cuda.Event()
             ev.record()
             self.events[i] = ev
             return
+        idle = b - len(seqs)
         # Block tables change only when a sequence takes or gives back a page (or the batch changes):
         # keep a host mirror, rewrite the rows that changed, and send the tables only then.
         for gi, g in enumerate(kv_groups):
-            for r, s in enumerate(seqs):
-                pages = s.pages[g.index]
+            for r in range(b):
+                pages = seqs[r].pages[g.index] if r < len(seqs) else self.idle_pages
                 if self.table_rows[gi][r] != pages:
                     self.table_mirror[gi, r, :len(pages)] = pages
                     self.table_mirror[gi, r, len(pages):] = -1
@@ -92,9 +100,9 @@ class _Captured:
         host = self.host[i]
         view = self.host_views[i]
         small = 3 * b
-        view[:b] = [s.length for s in seqs]
-        view[b:2 * b] = [s.length + 1 for s in seqs]
-        view[2 * b:small] = [s.slot for s in seqs]
+        view[:b] = [s.length for s in seqs] + [0] * idle
+        view[b:2 * b] = [s.length + 1 for s in seqs] + [0] * idle      # an idle row attends to nothing
+        view[2 * b:small] = [s.slot for s in seqs] + [self.idle_slot] * idle
         n = small + self.table_mirror.size
         if self.device_version != self.table_version:
             if self.host_version[i] != self.table_version:
@@ -107,7 +115,8 @@ class _Captured:
             self.ints[:small].copy_(host[:small], non_blocking=True)
             self.h2d_bytes += 4 * small
         if tokens is not None:
-            view[n:n + b] = tokens
+            view[n:n + len(tokens)] = tokens
+            view[n + len(tokens):n + b] = 0
             self.tokens.copy_(host[n:n + b], non_blocking=True)
             self.h2d_bytes += 4 * b
         ev = torch.cuda.Event()
@@ -115,22 +124,66 @@ class _Captured:
         self.events[i] = ev
 
     def capture(self, model, cache):
-        # One eager run first: lazy allocations (counters, library workspaces) must not happen
-        # inside the capture.  It writes the same cache entries the replay will write.
-        side = torch.cuda.Stream(device=model.runtime.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            model.forward(self.ctx, cache)
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        self.ctx.attention_plan.scratch.clear()            # scratch must come from the graph's own pool
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.logits = model.forward(self.ctx, cache)
+        self.graph, self.logits = capture_forward(model, self.ctx, cache)
+
+
+_capture_streams = {}          # device -> the side stream captures are made on
+
+
+def capture_forward(model, ctx, cache):
+    """The forward pass of ``ctx`` as a CUDA graph: (graph, its logits buffer).  One eager run first:
+    lazy allocations (counters, library workspaces) must not happen inside the capture; it writes the
+    same cache entries the replay will write.  The capture is begun and ended by hand on one side
+    stream per device: the ready-made context manager empties the allocator's device and pinned-host
+    caches at every entry, which cost 1 - 17 ms a capture here and once 1.3 s."""
+    device = model.runtime.device
+    side = _capture_streams.get(device)
+    if side is None:
+        side = _capture_streams[device] = torch.cuda.Stream(device=device)
+    current = torch.cuda.current_stream(device)
+    side.wait_stream(current)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        model.forward(ctx, cache)
+        torch.cuda.synchronize(device)
+        if ctx.attention_plan is not None:
+            ctx.attention_plan.scratch.clear()             # scratch must come from the graph's own pool
+        graph.capture_begin()
+        try:
+            logits = model.forward(ctx, cache)
+        finally:
+            graph.capture_end()
+    current.wait_stream(side)
+    return graph, logits
+
+
+LAUNCH_BOUND = 0.75            # host launch time / device time of an eager step from which a graph is worth its capture
+LAUNCH_BOUND_PATIENCE = 8      # a device-bound batch size must come this many times as often before it is captured
+
+
+def sightings_needed(capture_after, launch_share):
+    """How many eager steps a batch size runs before it gets a graph.  A replayed graph saves the
+    host's launches; where the device needs longer for the step than the host for launching it
+    (``launch_share`` well below 1: large layers), the replay is no faster than the eager step, and
+    a capture pays only for a batch size that stays for very long."""
+    if launch_share is None or launch_share >= LAUNCH_BOUND:
+        return capture_after
+    return capture_after * LAUNCH_BOUND_PATIENCE
+
+
+def graph_rows(batch):
+    """Rows of the graph that serves ``batch`` sequences when one graph serves several batch sizes:
+    the next power of two up to 16, the next multiple of 16 above.  The idle rows cost little: a
+    decode step's time is the weights' and the live sequences' cache, read once whatever the rows,
+    and the weight-streaming products work in steps of 16 rows anyway."""
+    batch = int(batch)
+    if batch <= 16:
+        return 1 << max(0, batch - 1).bit_length()
+    return (batch + 15) // 16 * 16
 
 
 class DecodeGraphs:
-    """Captured decode steps of one model and cache, by batch size."""
+    """Captured decode steps of one model and cache, by number of rows."""
 
     def __init__(self, model, cache):
         self.model = model
@@ -138,7 +191,9 @@ class DecodeGraphs:
         self.captured = {}
         self.captures = 0
         self.ahead_hits = 0                                # steps that found their positions and tables already sent
-        self.eager_steps = {}                              # batch size -> steps run eagerly while waiting to be worth a capture
+        self.eager_steps = {}                              # graph rows -> steps run eagerly while waiting to be worth a capture
+        self.launch_share = None                           # of the last eager step: host time to launch it / device time to run it
+        self._probe = None                                 # (start event, end event, host ms) of an eager step not yet read
 
     def takes(self, entries):
         return all(len(e.tokens) == 1 and (e.want is None or list(e.want) == [0]) for e in entries)
@@ -147,19 +202,28 @@ class DecodeGraphs:
         """One decode step for ``entries`` (one token each).  Returns float32 logits [B, vocab] in a
         buffer that the next replay of the same batch size overwrites.  With ``device_tokens`` the
         tokens already in the graph's token buffer are used (``token_buffer(B)``), and the entries'
-        tokens are ignored.  ``capture_after``: a batch size without a graph runs eagerly that many
-        times before it is captured (a capture costs about 10 ms and two forward passes: a batch that
-        shrinks by one request every few steps is faster without; 64 requests ending four steps
-        apart took 1.89 s eagerly and 2.3 - 2.7 s with a capture per size)."""
+        tokens are ignored.
+
+        ``capture_after`` (the generation loop's way): the step runs in a graph of `graph_rows(B)`
+        rows whose other rows are idle (`_Captured.stage`), so that a batch that loses its requests
+        one by one needs a graph per sixteen sizes and not per size; a width
+        without a graph runs eagerly that many times before it is captured, and
+        `LAUNCH_BOUND_PATIENCE` times as often while the eager steps are bound by the device and not
+        by their launches (`sightings_needed`).  A capture costs two forward passes and 10 - 30 ms.
+        64 requests of the 8B shape that ended five steps apart: 2.24 s eagerly; with a graph per
+        batch size 3.64 s in the call that captured them and 1.56 s in the calls after it; with
+        shared widths 1.96 s in the first call, captures included, and 1.54 s after it."""
         model, cache = self.model, self.cache
         seqs = [e.sequence for e in entries]
-        b = len(seqs)
+        b = rows = len(seqs)
         if capture_after and not device_tokens and b not in self.captured:
-            n = self.eager_steps.get(b, 0)
-            if n < capture_after:
-                from .step import run_step
-                self.eager_steps[b] = n + 1
-                return run_step(model, cache, entries)
+            rows = graph_rows(b)
+            if rows not in self.captured:
+                n = self.eager_steps.get(rows, 0)
+                self._read_probe()
+                if n < sightings_needed(capture_after, self.launch_share):
+                    self.eager_steps[rows] = n + 1
+                    return self._eager_step(entries)
         slots = set()
         for i, (e, s) in enumerate(zip(entries, seqs)):
             if not getattr(s, "open", False):
@@ -173,7 +237,7 @@ class DecodeGraphs:
             if not device_tokens and not 0 <= int(e.tokens[0]) < model.spec.vocab_size:
                 raise StepError(f"entry {i}: token id {e.tokens[0]} is outside the vocabulary")
         tokens = None if device_tokens else [int(e.tokens[0]) for e in entries]
-        cap = self.captured.get(b)
+        cap = self.captured.get(rows)
         if cap is not None and self._staged(cap, seqs, cache.kv_groups):
             # the step before this one already reserved the pages and sent everything but the tokens
             if tokens is not None:
@@ -186,8 +250,8 @@ class DecodeGraphs:
             fresh = cap is None or cap.pages < pages
             if fresh:
                 room = min((model.spec.max_positions + PAGE - 1) // PAGE, max(pages + 16, (pages * 5) // 4))
-                cap = _Captured(model, cache, b, max(room, pages), len(cache.kv_groups))
-                self.captured[b] = cap
+                cap = _Captured(model, cache, rows, max(room, pages), len(cache.kv_groups))
+                self.captured[rows] = cap
             cap.stage(seqs, tokens, cache.kv_groups)
         cap.staged_for = None
         if fresh:
@@ -197,7 +261,27 @@ class DecodeGraphs:
         for s in seqs:
             cache.commit(s, s.length + 1)
         self._stage_ahead(cap, seqs)
-        return cap.logits
+        return cap.logits if rows == b else cap.logits[:b]
+
+    def _eager_step(self, entries):
+        """The step without a graph, timed twice: the host's time to launch it and the device's time
+        to run it (read at the next call, after the caller has waited for this step's result)."""
+        from .step import run_step
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        logits = run_step(self.model, self.cache, entries)
+        end.record()
+        self._probe = (start, end, (time.perf_counter() - t0) * 1e3)
+        return logits
+
+    def _read_probe(self):
+        if self._probe is not None and self._probe[1].query():
+            start, end, host_ms = self._probe
+            self._probe = None
+            device_ms = start.elapsed_time(end)
+            if device_ms > 0:
+                self.launch_share = host_ms / device_ms
 
     @staticmethod
     def _staged(cap, seqs, kv_groups):
@@ -290,18 +374,7 @@ class StepGraphs:
         buffer = torch.empty_like(ctx.packed)
         ctx, new_lengths = plan_step(entries, cache, model.spec.vocab_size, model.spec.max_positions,
                                      model.runtime.device, into=buffer)
-        # One eager run first (on a side stream, as capture needs): lazy allocations must not happen inside the capture.
-        side = torch.cuda.Stream(device=model.runtime.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            model.forward(ctx, cache)
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        if ctx.attention_plan is not None:
-            ctx.attention_plan.scratch.clear()              # scratch must come from the graph's own pool
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = model.forward(ctx, cache)
+        graph, logits = capture_forward(model, ctx, cache)
         graph.replay()                                      # the capture itself computes nothing
         for e, length in zip(entries, new_lengths):
             cache.commit(e.sequence, length)

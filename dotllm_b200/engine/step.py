@@ -41,7 +41,8 @@ class AttentionPlan:
     seq_start: torch.Tensor       # int32 [B] cached length before the step
     seq_new: torch.Tensor         # int32 [B] tokens brought
     cu_new: torch.Tensor          # int32 [B+1] offsets of each sequence's tokens in the packed step
-    seq_total: torch.Tensor       # int32 [B] length after the step
+    seq_total: torch.Tensor       # int32 [B] length after the step; 0: an idle row (a captured step wider than
+                                  # its batch), which attends to nothing and whose output nobody reads
     starts: list = field(default_factory=list)
     news: list = field(default_factory=list)
     scratch: dict = field(default_factory=dict)

@@ -138,8 +138,9 @@ class Model:
         if graphs:
             runner = self.decode_graphs(cache)
             if runner.takes(entries):
-                # graphs="lazy": a batch size earns its graph by coming eight times (the generation loop's choice)
-                return runner.run(entries, capture_after=8 if graphs == "lazy" else 0)
+                # graphs="lazy" (the generation loop's choice): graphs of a few widths that serve every batch
+                # size, each captured when it is needed for the fifth time
+                return runner.run(entries, capture_after=4 if graphs == "lazy" else 0)
             return self.step_graphs(cache).run(entries)
         return run_step(self.decoder, cache, entries)
 

@@ -98,7 +98,7 @@ def test_groups_follow_needs_and_shared_caches():
     v0, v6, v5, v4 = (cache.view(e, tables, slots) for e in (0, 6, 5, 4))
     assert v0.writes and not v6.writes and v6.k.data_ptr() == v0.k.data_ptr()
     assert v5 is None
-    assert v4.kind == "state" and v4.state.shape == (4, 3, 5)
+    assert v4.kind == "state" and v4.state.shape == (4 + 1, 3, 5)          # the four slots and the idle one
     assert cache.view(2, tables, slots).k.data_ptr() != v0.k.data_ptr()
     with pytest.raises(CacheError):
         ModelCache([None, full], [None, 0], CPU, max_tokens=64)     # reads a cache that does not exist

@@ -240,11 +240,13 @@ def test_greedy_generation_through_the_entry_point(tmp, which, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("which,n_seqs", [("A", 40), ("D", 64), ("C", 33)])
-@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("graphs", [False, True, "shared"])
 def test_decoding_many_sequences_at_once(tmp, which, n_seqs, dtype, graphs):
     """Decode steps of 33, 40 and 64 sequences of unequal lengths that end at different steps (the
-    batch shrinks through 17 and 16 rows, where the decode products change kernels), eagerly and
-    through captured graphs, every logit against the plain implementation."""
+    batch shrinks through 17 and 16 rows, where the decode products change kernels), eagerly, through
+    a captured graph per batch size, and through graphs of a few widths whose other rows
+    are idle ("shared": the idle page is poisoned, so an idle row that reached a live one would
+    show); every logit against the plain implementation."""
     from dotllm_b200 import StepEntry
     model, cfg, weights, _ = load_pair(tmp, which, dtype)
     vocab, positions = cfg["vocab_size"], cfg["max_position_embeddings"]
@@ -263,7 +265,15 @@ def test_decoding_many_sequences_at_once(tmp, which, n_seqs, dtype, graphs):
     sizes = set()
     while live:
         sizes.add(len(live))
-        out = model.step(cache, [StepEntry(seqs[i], [reqs[i][lens[i] + done[i]]]) for i in live], graphs=graphs).clone()
+        entries = [StepEntry(seqs[i], [reqs[i][lens[i] + done[i]]]) for i in live]
+        if graphs == "shared":
+            for g in cache.kv_groups:
+                g.k[:, cache.idle_page] = float("nan")
+                g.v[:, cache.idle_page] = float("nan")
+            out = model.decode_graphs(cache).run(entries, capture_after=1).clone()
+            assert out.shape[0] == len(live)
+        else:
+            out = model.step(cache, entries, graphs=graphs).clone()
         for row, i in enumerate(live):
             assert_close(out[row], refs[i][lens[i] + done[i]], dtype,
                          f"{len(live)} live: sequence {i} position {lens[i] + done[i]}")
@@ -275,6 +285,31 @@ def test_decoding_many_sequences_at_once(tmp, which, n_seqs, dtype, graphs):
         cache.fill_free_pages(float("nan"))
     assert max(sizes) == n_seqs and min(sizes) <= 16 and any(16 < n <= 32 for n in sizes)
     cache.check()
+    if graphs == "shared":
+        runner = model.decode_graphs(cache)
+        assert runner.captured and all(rows % 16 == 0 or rows in (1, 2, 4, 8) for rows in runner.captured)
+        assert len(runner.captured) <= 8 < len(sizes)
+
+
+def test_generation_that_loses_its_requests_one_by_one(tmp):
+    """Twenty greedy requests that end three steps apart, through the generation loop with and
+    without graphs (float32: the same bits whatever the batch, so the tokens must be the same).  The
+    loop's graphs come in few widths (1, 2, 4, 8, 16, 32, 48 ...): the batch sizes 20 .. 1 share five or fewer."""
+    from dotllm_b200 import InferenceOptions
+    model, cfg, _, _ = load_pair(tmp, "B", torch.float32)
+    prompts = [tiny_models.random_tokens(4 + (7 * i) % 23, cfg["vocab_size"], seed=300 + i) for i in range(20)]
+    options = [InferenceOptions(temperature=0.0, max_tokens=10 + 3 * i, stop_token_ids=[]) for i in range(20)]
+    outs = {}
+    for use_graphs in (False, True):
+        cache = model.new_cache(max_tokens=20 * 128)
+        generator = model.generator(cache=cache, max_batch=20, use_graphs=use_graphs)
+        outs[use_graphs] = [r.generated_token_ids for r in generator.generate(prompts, options)]
+        cache.check()
+        if use_graphs:
+            runner = model.decode_graphs(cache)
+            assert 2 <= len(runner.captured) <= 5 and set(runner.captured) <= {1, 2, 4, 8, 16, 32}
+    assert [len(t) for t in outs[True]] == [10 + 3 * i for i in range(20)]
+    assert outs[True] == outs[False]
 
 
 def test_a_sampled_request_gives_the_same_tokens_alone_and_in_any_batch(tmp):

@@ -192,3 +192,14 @@ def test_uniform_numbers_depend_on_seed_and_step_only():
     assert a == [uniform(1, s) for s in range(200)]
     assert uniform(1, 1) != uniform(1, 0) != uniform(2, 0)
     assert abs(sum(uniform(i, j) for i in range(50) for j in range(50)) / 2500 - 0.5) < 0.02
+
+
+def test_a_device_bound_batch_size_waits_longer_for_its_graph():
+    """The rule that decides when a decode batch size is captured: at once where the host's launches
+    bound the step (or nothing is known yet), much later where the device does."""
+    from dotllm_b200.engine.decode_graph import LAUNCH_BOUND, LAUNCH_BOUND_PATIENCE, sightings_needed
+    assert sightings_needed(8, None) == 8
+    assert sightings_needed(8, 1.3) == 8
+    assert sightings_needed(8, LAUNCH_BOUND) == 8
+    assert sightings_needed(8, 0.5) == 8 * LAUNCH_BOUND_PATIENCE
+    assert sightings_needed(0, 0.5) == 0                     # graphs=True: always at once

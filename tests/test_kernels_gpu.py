@@ -812,6 +812,69 @@ def test_attention_decode_with_the_new_token_inside(nh, nkv, hd, rotate, window,
     assert torch.equal(k_one, k_two) and torch.equal(v_one, v_two)
 
 
+@pytest.mark.parametrize("fused", [False, True])
+def test_attention_decode_rows_that_hold_nothing(fused):
+    """Rows whose length after the step is 0 (the idle rows of a captured step wider than its batch)
+    get no work: the live rows come out with the same bits as without them, and the page the idle
+    rows point to is left as it was."""
+    from dotllm_b200.kernels import library
+    nh, nkv, hd = 8, 2, 64
+    live_lengths = [70, 200, 1, 640]
+    k_pool, v_pool, table, _ = make_paged(4, live_lengths, nkv, hd, torch.bfloat16, seed=70, n_pages=30)
+    used = set(table[table >= 0].tolist())
+    idle_page = [p for p in range(30) if p not in used][0]
+    k_pool[idle_page], v_pool[idle_page] = 3.0, 5.0
+    rows = [None, 0, None, None, 1, 2, None, 3, None]                  # None: idle
+    B = len(rows)
+    g = torch.Generator().manual_seed(71)
+    qkv_live = torch.randn(4, (nh + 2 * nkv) * hd, generator=g).to(torch.bfloat16)
+    cos, sin = plain_llama.rope_tables(range(1024), hd, 10000.0)
+    scale = 1.0 / math.sqrt(hd)
+
+    def run(with_idle):
+        if with_idle:
+            lengths = [0 if r is None else live_lengths[r] for r in rows]
+            qkv = torch.stack([torch.full_like(qkv_live[0], 7.0) if r is None else qkv_live[r] for r in rows])
+            tab = torch.full((B, table.shape[1]), -1, dtype=torch.int32)
+            for i, r in enumerate(rows):
+                if r is None:
+                    tab[i, 0] = idle_page
+                else:
+                    tab[i] = table[r]
+        else:
+            lengths, qkv, tab = live_lengths, qkv_live, table
+        n = len(lengths)
+        x = qkv.to(DEV).clone()
+        q, k, v = x[:, :nh * hd], x[:, nh * hd:(nh + nkv) * hd], x[:, (nh + nkv) * hd:]
+        kp, vp = k_pool.to(DEV).clone(), v_pool.to(DEV).clone()
+        seqs = torch.arange(n, dtype=torch.int32, device=DEV)
+        pos = torch.tensor([max(0, v - 1) for v in lengths], dtype=torch.int32, device=DEV)
+        plan = _decode_plan(lengths)
+        plan.seq_start = pos
+        if fused:
+            out = ops().rope_cache_attention(q, k, v, cos.to(DEV), sin.to(DEV), hd, seqs, pos, tab.to(DEV), kp, vp,
+                                             nh, nkv, hd, scale, 0, plan=plan)
+        else:
+            live = torch.tensor([i for i, v in enumerate(lengths) if v > 0], dtype=torch.long, device=DEV)
+            ql, kl, vl = q[live].contiguous(), k[live].contiguous(), v[live].contiguous()
+            ops().rope_cache_write(ql, kl, vl, cos.to(DEV), sin.to(DEV), hd, seqs[:len(live)].contiguous(),
+                                   pos[live].contiguous(), tab.to(DEV)[live].contiguous(), kp, vp, nh, nkv, hd)
+            q = q.clone()
+            q[live] = ql
+            out = ops().attention(q, kp, vp, seqs, pos, tab.to(DEV), nh, nkv, hd, scale, 0, plan=plan)
+        library.check_status()
+        return out, kp, vp
+
+    alone, k_alone, v_alone = run(False)
+    padded, k_padded, v_padded = run(True)
+    keep = [i for i, r in enumerate(rows) if r is not None]
+    assert bool(torch.isfinite(alone).all())
+    assert torch.equal(padded[keep], alone)
+    bits = lambda t: t.view(torch.int16)                               # unused places hold NaN
+    assert torch.equal(bits(k_padded), bits(k_alone)) and torch.equal(bits(v_padded), bits(v_alone))
+    assert bool((k_padded[idle_page] == 3.0).all()) and bool((v_padded[idle_page] == 5.0).all())
+
+
 def test_attention_decode_far_key():
     nh, nkv, hd, n = 8, 2, 128, 3000
     k_pool, v_pool, table, dense = make_paged(1, [n], nkv, hd, torch.bfloat16, seed=24)
