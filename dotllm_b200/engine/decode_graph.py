@@ -3,7 +3,8 @@
 A decode step launches a few hundred small kernels; issued one by one the host cannot keep up
 with the device (the reference pays ~14 launches per layer per token,
 src/DotLLM.Cuda/CudaTransformerModel.cs:198-286).  Here the whole forward pass of a step that
-brings one token per sequence is captured once per batch size and replayed.  Everything that
+brings one token per sequence is captured once per batch size (or once per width, for the batch
+sizes up to it, with idle rows: the generation loop's way) and replayed.  Everything that
 changes from step to step - tokens, positions, lengths, slots, block tables - lives in fixed device
 buffers that one pinned host-to-device copy refreshes before each replay, so a captured graph
 serves any set of sequences of its batch size, wherever they are in the cache.
@@ -198,11 +199,14 @@ class DecodeGraphs:
     def takes(self, entries):
         return all(len(e.tokens) == 1 and (e.want is None or list(e.want) == [0]) for e in entries)
 
-    def run(self, entries, device_tokens=False, capture_after=0):
+    def run(self, entries, device_tokens=False, capture_after=0, device_ids=None):
         """One decode step for ``entries`` (one token each).  Returns float32 logits [B, vocab] in a
         buffer that the next replay of the same batch size overwrites.  With ``device_tokens`` the
         tokens already in the graph's token buffer are used (``token_buffer(B)``), and the entries'
-        tokens are ignored.
+        tokens are ignored.  ``device_ids``: an int32 device tensor [B] with the tokens, copied into
+        the graph's token buffer on the stream (the entries' tokens are ignored); with
+        ``capture_after`` the call then returns None, having done nothing, when the width has no
+        graph yet (an eager step needs its tokens on the host).
 
         ``capture_after`` (the generation loop's way): the step runs in a graph of `graph_rows(B)`
         rows whose other rows are idle (`_Captured.stage`), so that a batch that loses its requests
@@ -219,11 +223,14 @@ class DecodeGraphs:
         if capture_after and not device_tokens and b not in self.captured:
             rows = graph_rows(b)
             if rows not in self.captured:
+                if device_ids is not None:
+                    return None
                 n = self.eager_steps.get(rows, 0)
                 self._read_probe()
                 if n < sightings_needed(capture_after, self.launch_share):
                     self.eager_steps[rows] = n + 1
                     return self._eager_step(entries)
+        on_device = device_tokens or device_ids is not None
         slots = set()
         for i, (e, s) in enumerate(zip(entries, seqs)):
             if not getattr(s, "open", False):
@@ -234,9 +241,9 @@ class DecodeGraphs:
             if s.length + 1 > model.spec.max_positions:
                 raise StepError(f"entry {i}: position {s.length} is beyond the model's max positions "
                                 f"{model.spec.max_positions}")
-            if not device_tokens and not 0 <= int(e.tokens[0]) < model.spec.vocab_size:
+            if not on_device and not 0 <= int(e.tokens[0]) < model.spec.vocab_size:
                 raise StepError(f"entry {i}: token id {e.tokens[0]} is outside the vocabulary")
-        tokens = None if device_tokens else [int(e.tokens[0]) for e in entries]
+        tokens = None if on_device else [int(e.tokens[0]) for e in entries]
         cap = self.captured.get(rows)
         if cap is not None and self._staged(cap, seqs, cache.kv_groups):
             # the step before this one already reserved the pages and sent everything but the tokens
@@ -254,6 +261,10 @@ class DecodeGraphs:
                 self.captured[rows] = cap
             cap.stage(seqs, tokens, cache.kv_groups)
         cap.staged_for = None
+        if device_ids is not None:
+            if device_ids.dtype != torch.int32 or device_ids.numel() != b:
+                raise StepError(f"device_ids must be {b} int32 values")
+            cap.tokens[:b].copy_(device_ids.reshape(-1), non_blocking=True)
         if fresh:
             cap.capture(model, cache)
             self.captures += 1

@@ -113,10 +113,21 @@ class TextGenerator:
     ``fetch(ids) -> list of ints`` brings a step's sampled ids to the host; it is the one point of a
     step where the host waits for the device (the default takes ids that are already host values).
     ``clock`` marks the boundaries between a step's forward pass and its sampling for the timings:
-    ``clock.mark()`` now, ``clock.ms(a, b)`` once the batch is over (so marks may be device events)."""
+    ``clock.mark()`` now, ``clock.ms(a, b)`` once the batch is over (so marks may be device events).
+
+    ``ahead_fn(sequences, ids, rows) -> logits or None`` (optional) starts the next decode step
+    before the host has seen this step's tokens: the step of ``sequences`` whose tokens are
+    ``ids[rows]``, the sampling function's result as it is (on the device, where the model is).
+    The loop calls it between ``fetch.start(ids)`` and ``fetch.finish(...)``, so that the device
+    runs the next forward pass while the host waits for the ids, applies the stop rules and prepares
+    the sampling.  It gives it every request that goes on unless its new token is a stop token; a
+    request that then does stop has run one row in vain (rows do not depend on one another, and its
+    sequence is closed right after).  None: not now; the loop then steps in the ordinary way.
+    ``take_rows(logits, keep)`` picks the rows of the requests that go on."""
 
     def __init__(self, step_fn: Callable, sample_fn: Callable, cache, *, max_positions, vocab_size,
-                 default_stop_ids=(), bos_token_id=None, max_batch=None, fetch=None, clock=None):
+                 default_stop_ids=(), bos_token_id=None, max_batch=None, fetch=None, clock=None,
+                 ahead_fn=None, take_rows=None):
         self.step_fn = step_fn
         self.sample_fn = sample_fn
         self.cache = cache
@@ -127,6 +138,10 @@ class TextGenerator:
         self.max_batch = max_batch or cache.n_slots
         self.fetch = fetch or (lambda ids: [int(t) for t in (ids.tolist() if hasattr(ids, "tolist") else ids)])
         self.clock = clock or HostClock()
+        self.ahead_fn = ahead_fn
+        self.take_rows = take_rows or (lambda logits, keep: logits[keep])
+        self.ahead_steps = 0                                 # decode steps started before their tokens reached the host
+        self.ahead_rows_in_vain = 0                          # rows of such steps whose request had just stopped
 
     # ---------------------------------------------------------------- api
     def generate(self, prompts, options=None, on_token=None):
@@ -190,18 +205,33 @@ class TextGenerator:
         if verdict == StopResult.STOP_INCLUDE:
             self._finish(r, FinishReason.LENGTH)
             return False
-        if len(r.generated) >= r.options.max_tokens:        # a caller's own conditions may lack the cap
-            self._finish(r, FinishReason.LENGTH)
-            return False
-        # the next step would place this token at position prompt + generated - 1
-        if len(r.prompt) + len(r.generated) - 1 >= self.max_positions:
+        if self._last_token(r, len(r.generated)):
             self._finish(r, FinishReason.LENGTH)
             return False
         return True
 
+    def _last_token(self, r, n_generated):
+        """Is the request's token number ``n_generated`` its last, whatever it is?  (A caller's own
+        conditions may lack the cap; the next step would place the token at position
+        prompt + generated - 1.)"""
+        return n_generated >= r.options.max_tokens or len(r.prompt) + n_generated - 1 >= self.max_positions
+
     def _sample(self, logits, live):
         return self.sample_fn(logits, [r.pipeline for r in live], [r.generated for r in live],
                               [r.index for r in live], [len(r.generated) for r in live])
+
+    def _step_ahead(self, live, ids):
+        """Start the next decode step for the requests that go on unless their new token stops them.
+        Returns (those requests, logits, marks around the forward pass), or None."""
+        rows = [i for i, r in enumerate(live) if not self._last_token(r, len(r.generated) + 1)]
+        if not rows:
+            return None
+        t0 = self.clock.mark()
+        logits = self.ahead_fn([live[i].sequence for i in rows], ids, rows)
+        if logits is None:
+            return None
+        self.ahead_steps += 1
+        return [live[i] for i in rows], logits, t0, self.clock.mark()
 
     def _run_batch(self, batch, on_token):
         clock = self.clock
@@ -214,25 +244,40 @@ class TextGenerator:
             t1 = clock.mark()
             ids = self._sample(logits, batch)
             t2 = clock.mark()
-            marks.append((t0, t1, t2, None))
-            tokens = self.fetch(ids)                         # the step's one wait for the device
-            live = [r for r, tok in zip(batch, tokens) if self._accept(r, tok, on_token)]
-            while live:
-                t0 = clock.mark()
-                logits = self.step_fn([StepEntry(r.sequence, [r.generated[-1]]) for r in live])
-                t1 = clock.mark()
+            marks.append((t0, t1, t1, t2, None))
+            live = batch
+            while True:
+                start = getattr(self.fetch, "start", None)
+                pending = start(ids) if start is not None else None
+                ahead = self._step_ahead(live, ids) if self.ahead_fn is not None else None
+                tokens = self.fetch.finish(pending) if start is not None else self.fetch(ids)   # the step's one wait for the device
+                live = [r for r, tok in zip(live, tokens) if self._accept(r, tok, on_token)]
+                if not live:
+                    break
+                if ahead is not None:
+                    ran, logits, t0, t1 = ahead
+                    if len(ran) != len(live):
+                        going = {id(r) for r in live}
+                        keep = [i for i, r in enumerate(ran) if id(r) in going]
+                        self.ahead_rows_in_vain += len(ran) - len(keep)
+                        if len(keep) != len(live):
+                            raise RuntimeError("a request goes on that the step started ahead did not hold")
+                        logits = self.take_rows(logits, keep)
+                else:
+                    t0 = clock.mark()
+                    logits = self.step_fn([StepEntry(r.sequence, [r.generated[-1]]) for r in live])
+                    t1 = clock.mark()
+                ts = clock.mark()
                 ids = self._sample(logits, live)
                 t2 = clock.mark()
-                marks.append((t0, t1, t2, list(live)))
-                tokens = self.fetch(ids)
-                live = [r for r, tok in zip(live, tokens) if self._accept(r, tok, on_token)]
+                marks.append((t0, t1, ts, t2, list(live)))
         finally:
             for r in batch:                                  # an error must not leak slots
                 if r.sequence is not None and r.sequence.open:
                     self.cache.close_sequence(r.sequence)
         prefill_ms = clock.ms(marks[0][0], marks[0][1])
-        sampling_ms = sum(clock.ms(t1, t2) for _, t1, t2, _ in marks)
-        for t0, t1, _, live in marks[1:]:
+        sampling_ms = sum(clock.ms(ts, t2) for _, _, ts, t2, _ in marks)
+        for t0, t1, _, _, live in marks[1:]:
             step_ms = clock.ms(t0, t1)
             for r in live:
                 r.decode_ms += step_ms

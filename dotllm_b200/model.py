@@ -34,18 +34,29 @@ class _IdFetcher:
         self.device = device
         self.pinned = torch.empty(4096, dtype=torch.int32).pin_memory()
 
-    def __call__(self, ids):
+    def start(self, ids):
+        """Send the copy; what follows on the stream (the next step, started ahead) does not delay it."""
         from .kernels import library
         n = ids.numel()
         if n + 1 > self.pinned.numel():
             self.pinned = torch.empty(2 * (n + 1), dtype=torch.int32).pin_memory()
         both = torch.cat([ids.to(torch.int32).reshape(-1), library.status_word(self.device)])
         self.pinned[:n + 1].copy_(both, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        done = torch.cuda.Event()
+        done.record()
+        return n, done
+
+    def finish(self, pending):
+        from .kernels import library
+        n, done = pending
+        done.synchronize()
         values = self.pinned[:n + 1].tolist()
         if values[n]:
             library.check_status()                           # raises with the kernel's reason and clears the word
         return values[:n]
+
+    def __call__(self, ids):
+        return self.finish(self.start(ids))
 
 
 class _EventClock:
@@ -160,14 +171,29 @@ class Model:
             cache._step_graphs = runner
         return runner
 
-    def generator(self, cache=None, max_tokens=None, max_batch=None, use_graphs=True):
-        """A TextGenerator over this model.  Without a cache one is made for ``max_tokens``."""
+    def generator(self, cache=None, max_tokens=None, max_batch=None, use_graphs=True, ahead=True):
+        """A TextGenerator over this model.  Without a cache one is made for ``max_tokens``.
+        ``ahead``: with graphs, a decode step is started before the tokens of the step before it
+        have reached the host (they are taken from the device), so the device does not wait for the
+        host between steps."""
         if cache is None:
             cache = self.new_cache(max_tokens or min(self.spec.max_positions * 8, 1 << 16))
         return TextGenerator(lambda entries: self.step(cache, entries, graphs="lazy" if use_graphs else False), sample_rows, cache,
                              max_positions=self.spec.max_positions, vocab_size=self.spec.vocab_size,
                              default_stop_ids=self.spec.stop_token_ids, bos_token_id=self.spec.bos_token_id,
-                             max_batch=max_batch, fetch=_IdFetcher(self.runtime.device), clock=_EventClock())
+                             max_batch=max_batch, fetch=_IdFetcher(self.runtime.device), clock=_EventClock(),
+                             ahead_fn=(lambda sequences, ids, rows: self._step_ahead(cache, sequences, ids, rows))
+                             if use_graphs and ahead else None,
+                             take_rows=lambda logits, keep: logits[torch.tensor(keep, device=logits.device)])
+
+    def _step_ahead(self, cache, sequences, ids, rows):
+        """The decode step of ``sequences`` with the tokens ``ids[rows]`` that are still on the device,
+        through the graph of their width if there is one (None otherwise: a width without a graph
+        runs eagerly, which needs the tokens on the host)."""
+        if len(rows) != ids.numel():
+            ids = ids[torch.tensor(rows, device=ids.device)]
+        entries = [StepEntry(s, [0]) for s in sequences]
+        return self.decode_graphs(cache).run(entries, capture_after=4, device_ids=ids)
 
     def generate(self, prompts, options=None, on_token=None, **option_fields):
         """Generate for one prompt (a list of ints) or many.  Options as an InferenceOptions (or

@@ -292,24 +292,42 @@ def test_decoding_many_sequences_at_once(tmp, which, n_seqs, dtype, graphs):
 
 
 def test_generation_that_loses_its_requests_one_by_one(tmp):
-    """Twenty greedy requests that end three steps apart, through the generation loop with and
-    without graphs (float32: the same bits whatever the batch, so the tokens must be the same).  The
-    loop's graphs come in few widths (1, 2, 4, 8, 16, 32, 48 ...): the batch sizes 20 .. 1 share five or fewer."""
+    """Twenty greedy requests that end three steps apart, through the generation loop without graphs,
+    with graphs, and with graphs and every decode step started before the tokens of the step before
+    it are on the host (float32: the same bits whatever the batch, so the tokens must be the same).
+    The loop's graphs come in few widths (1, 2, 4, 8, 16, 32, 48 ...): the batch sizes 20 .. 1 share
+    five or fewer.  Then the same with a stop token that some requests meet on their way: a request
+    that stops has run one row of the step started ahead in vain."""
     from dotllm_b200 import InferenceOptions
     model, cfg, _, _ = load_pair(tmp, "B", torch.float32)
     prompts = [tiny_models.random_tokens(4 + (7 * i) % 23, cfg["vocab_size"], seed=300 + i) for i in range(20)]
-    options = [InferenceOptions(temperature=0.0, max_tokens=10 + 3 * i, stop_token_ids=[]) for i in range(20)]
-    outs = {}
-    for use_graphs in (False, True):
+
+    def run(options, use_graphs, ahead):
         cache = model.new_cache(max_tokens=20 * 128)
-        generator = model.generator(cache=cache, max_batch=20, use_graphs=use_graphs)
-        outs[use_graphs] = [r.generated_token_ids for r in generator.generate(prompts, options)]
+        generator = model.generator(cache=cache, max_batch=20, use_graphs=use_graphs, ahead=ahead)
+        outs = generator.generate(prompts, options)
         cache.check()
-        if use_graphs:
-            runner = model.decode_graphs(cache)
-            assert 2 <= len(runner.captured) <= 5 and set(runner.captured) <= {1, 2, 4, 8, 16, 32}
-    assert [len(t) for t in outs[True]] == [10 + 3 * i for i in range(20)]
-    assert outs[True] == outs[False]
+        assert not cache.live
+        return outs, generator, cache
+
+    options = [InferenceOptions(temperature=0.0, max_tokens=10 + 3 * i, stop_token_ids=[]) for i in range(20)]
+    eager, _, _ = run(options, False, False)
+    assert [len(o.generated_token_ids) for o in eager] == [10 + 3 * i for i in range(20)]
+    for ahead in (False, True):
+        outs, generator, cache = run(options, True, ahead)
+        assert [o.generated_token_ids for o in outs] == [o.generated_token_ids for o in eager], f"ahead={ahead}"
+        runner = model.decode_graphs(cache)
+        assert 2 <= len(runner.captured) <= 5 and set(runner.captured) <= {1, 2, 4, 8, 16, 32}
+        assert (generator.ahead_steps > 30) == ahead and generator.ahead_rows_in_vain == 0
+    # a stop token that request 5 meets at its thirteenth token (and others wherever they meet it)
+    stop = eager[5].generated_token_ids[12]
+    stopping = [InferenceOptions(temperature=0.0, max_tokens=10 + 3 * i, stop_token_ids=[stop]) for i in range(20)]
+    eager, _, _ = run(stopping, False, False)
+    assert eager[5].finish_reason.value == "stop" and len(eager[5].generated_token_ids) <= 12
+    outs, generator, _ = run(stopping, True, True)
+    assert [o.generated_token_ids for o in outs] == [o.generated_token_ids for o in eager]
+    assert [o.finish_reason for o in outs] == [o.finish_reason for o in eager]
+    assert generator.ahead_rows_in_vain >= 1
 
 
 def test_a_sampled_request_gives_the_same_tokens_alone_and_in_any_batch(tmp):

@@ -203,3 +203,79 @@ def test_a_device_bound_batch_size_waits_longer_for_its_graph():
     assert sightings_needed(8, LAUNCH_BOUND) == 8
     assert sightings_needed(8, 0.5) == 8 * LAUNCH_BOUND_PATIENCE
     assert sightings_needed(0, 0.5) == 0                     # graphs=True: always at once
+
+
+class OrderedFetch:
+    """A fetch in two halves that records when each half ran."""
+
+    def __init__(self, log):
+        self.log = log
+
+    def start(self, ids):
+        self.log.append("fetch starts")
+        return list(ids)
+
+    def finish(self, pending):
+        self.log.append("fetch ends")
+        return [int(t) for t in pending]
+
+
+def make_ahead(refuse_first=0, **kw):
+    from dotllm_b200.engine import StepEntry
+    gen, model, cache = make(**kw)
+    log, refused = [], [refuse_first]
+
+    def ahead(sequences, ids, rows):
+        log.append(("ahead", [s.slot for s in sequences], [ids[i] for i in rows]))
+        if refused[0] > 0:
+            refused[0] -= 1
+            return None
+        return model.step([StepEntry(s, [ids[i]]) for s, i in zip(sequences, rows)])
+
+    gen.ahead_fn = ahead
+    gen.fetch = OrderedFetch(log)
+    return gen, model, cache, log
+
+
+def test_steps_started_ahead_give_the_same_tokens():
+    """With a function that starts the next step before the tokens are on the host, every request
+    gets the tokens it gets without; the step starts between the two halves of the fetch; a request
+    whose next token is its last by the count is left out of it; a request that meets its stop token
+    has run one row in vain, and the others' rows are picked from the step's result."""
+    prompts = [[3], [10], [40], [20, 21]]
+    options = [InferenceOptions(max_tokens=n, **GREEDY) for n in (6, 6, 3, 5)]
+    plain, plain_model, _ = make(stop=(13,))
+    want = plain.generate(prompts, options)
+    gen, model, cache, log = make_ahead(stop=(13,))
+    got = gen.generate(prompts, options)
+    assert [o.generated_token_ids for o in got] == [o.generated_token_ids for o in want]
+    assert [o.finish_reason for o in got] == [o.finish_reason for o in want]
+    assert got[1].generated_token_ids == [11, 12] and got[1].finish_reason == FinishReason.STOP
+    # order within a step: the copy is sent, the next step starts, the host waits for the copy
+    assert log[:3] == ["fetch starts", ("ahead", [0, 1, 2, 3], [4, 11, 41, 22]), "fetch ends"]
+    sizes = [len(s) for s in model.steps]
+    # prompts; 4 rows; 4 rows (request 2's third token is its last: it is left out of the step after);
+    # 3 rows, of which request 1's ran in vain (its token 13 stopped it); 2; 1 (request 3 left: fifth token)
+    assert sizes == [4, 4, 4, 3, 2, 1]
+    assert sizes != [len(s) for s in plain_model.steps]               # [4, 4, 4, 2, 2, 1] without
+    assert gen.ahead_rows_in_vain == 1 and gen.ahead_steps == 5
+    assert [o.timings.decode_steps for o in got] == [5, 1, 2, 4]
+    cache.check()
+    assert cache.slots.n_held == 0
+
+
+def test_a_refused_step_ahead_falls_back_to_the_ordinary_step():
+    gen, model, cache, log = make_ahead(refuse_first=2)
+    outs = gen.generate([[3], [10]], InferenceOptions(max_tokens=5, **GREEDY))
+    assert [o.generated_token_ids for o in outs] == [[4, 5, 6, 7, 8], [11, 12, 13, 14, 15]]
+    assert [len(s) for s in model.steps] == [2, 2, 2, 2, 2]
+    assert gen.ahead_steps == 2 and sum(1 for e in log if isinstance(e, tuple)) == 4
+    cache.check()
+
+
+def test_steps_ahead_stop_at_the_models_last_position():
+    gen, model, cache, _ = make_ahead(max_positions=8)
+    out = gen.generate([[1, 2, 3, 4, 5]], InferenceOptions(max_tokens=50, **GREEDY))[0]
+    assert out.generated_token_ids == [6, 7, 8, 9] and out.finish_reason == FinishReason.LENGTH
+    assert model.steps[-1][0][2] == 7 and len(model.steps) == 4        # no step beyond the last position
+    cache.check()
