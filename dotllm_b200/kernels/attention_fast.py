@@ -49,7 +49,7 @@ def _decode(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_k
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim,
                   scale, window, DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots,
                   counters.data_ptr(), counters.numel(),
-                  _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  _library.status_word(q.device).data_ptr(), _library.current_stream())
     return True
 
 
@@ -107,7 +107,7 @@ def decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_h
                   k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], plan.seq_total.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window,
                   DECODE_BLOCKS, part_o.data_ptr(), part_ml.data_ptr(), slots, counters.data_ptr(), counters.numel(),
-                  _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  _library.status_word(q.device).data_ptr(), _library.current_stream())
     return out
 
 
@@ -130,13 +130,13 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
                       k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),
                       n_tiles, plan.seq_start.data_ptr(), plan.seq_new.data_ptr(), plan.cu_new.data_ptr(),
                       block_table.data_ptr(), block_table.shape[1], n_heads, n_kv_heads, head_dim, scale, window,
-                      _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                      _library.status_word(q.device).data_ptr(), _library.current_stream())
         return True
     _library.call("dl_attention_prefill_bf16", q.data_ptr(), q_stride, out.data_ptr(), out.stride(0),
                   k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),
                   n_tiles, plan.seq_start.data_ptr(), plan.seq_new.data_ptr(), plan.cu_new.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], n_heads, n_kv_heads, head_dim, scale, window,
-                  _library.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  _library.status_word(q.device).data_ptr(), _library.current_stream())
     return True
 
 

@@ -77,5 +77,5 @@ def run(x, w, out_dtype, fuse_swiglu=False, resident=False, row_sums=None, into=
                   sums_out.data_ptr() if sums_out is not None else None,
                   sums_in.data_ptr() if sums_in is not None else None, parts, 1.0 / width, float(eps),
                   partials.data_ptr(), partials.numel(), counters.data_ptr(), counters.numel(),
-                  _library.status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  _library.status_word(x.device).data_ptr(), _library.current_stream())
     return result

@@ -12,6 +12,7 @@ import ctypes
 
 import torch
 
+from . import gemm_decode_tc
 from . import library as _library
 
 _P, _I, _F = _library._P, _library._I, _library._F
@@ -52,14 +53,12 @@ def _device_state(device):
 
 def sum_stride(rows):
     """Floats between two parts of the sums of squares that a product of ``rows`` rows leaves."""
-    from . import gemm_decode_tc
     return SUM_STRIDE if rows <= SKINNY_ROWS else gemm_decode_tc.SUM_STRIDE
 
 
 def takes(x, w, fuse_swiglu=False, max_rows=None):
     M, K = x.shape
     if M > SKINNY_ROWS:
-        from . import gemm_decode_tc
         return (fuse_swiglu or TC_PLAIN) and M <= (max_rows or MAX_ROWS) and gemm_decode_tc.takes(x, w, fuse_swiglu)
     n_out = w.shape[0] // 2 if fuse_swiglu else w.shape[0]
     tiles = (n_out + 7) // 8 if fuse_swiglu else (n_out + 15) // 16
@@ -77,14 +76,13 @@ def run(x, w, out_dtype, fuse_swiglu=False, resident=False, row_sums=None, into=
     returns (stream * gain as bfloat16 [M, N], sums of squares float32 [ceil(N / 16) * 16])."""
     M, K = x.shape
     if M > SKINNY_ROWS:
-        from . import gemm_decode_tc
         return gemm_decode_tc.run(x, w, out_dtype, fuse_swiglu, resident, row_sums, into)
     n_out = w.shape[0] // 2 if fuse_swiglu else w.shape[0]
     counters, partials, sms = _device_state(x.device)
     x_stride = x.stride(0) if M > 1 else max(K, x.stride(0))
     flags = (1 if fuse_swiglu else 0) | (2 if resident else 0)
     tail = (partials.data_ptr(), partials.numel(), counters.data_ptr(), counters.numel(),
-            _library.status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+            _library.status_word(x.device).data_ptr(), _library.current_stream())
     if row_sums is None and into is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
         _library.call("dl_gemm_skinny_bf16", x.data_ptr(), x_stride, w.data_ptr(), out.data_ptr(),

@@ -38,7 +38,7 @@ def run(x, w, out_dtype, fuse_swiglu=False):
     out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     _library.call("dl_gemm_tc_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(),
                   0 if out_dtype == torch.float32 else 1, n_out, M, n_out, K, 1 if fuse_swiglu else 0, BLOCKS,
-                  _library.status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  _library.status_word(x.device).data_ptr(), _library.current_stream())
     return out
 
 
@@ -59,5 +59,5 @@ def run_qkv(x, w, q_cols, kv_cols, head_dim, n_kv_heads, cos, sin, token_pos, to
     _library.call("dl_gemm_tc_qkv_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), q.data_ptr(), q_cols, M, K, q_cols, kv_cols,
                   head_dim, n_kv_heads, cos.data_ptr(), sin.data_ptr(), cos.shape[0], token_pos.data_ptr(), token_seq.data_ptr(),
                   block_table.data_ptr(), block_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], BLOCKS,
-                  _library.status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  _library.status_word(x.device).data_ptr(), _library.current_stream())
     return q

@@ -101,6 +101,24 @@ def set_dependent_launch(on):
     library().dl_set_dependent_launch(1 if on else 0)
 
 
+_raw_stream = None
+
+
+def current_stream():
+    """The current CUDA stream's handle, for a kernel launch.  ``torch.cuda.current_stream()`` builds
+    a Python stream object after several device-index and environment look-ups, 10 - 15 us a call with
+    a few hundred launches a step; the handle alone comes from the binding underneath it."""
+    global _raw_stream
+    if _raw_stream is None:
+        import torch
+        raw, device = getattr(torch._C, "_cuda_getCurrentRawStream", None), getattr(torch._C, "_cuda_getDevice", None)
+        if raw is not None and device is not None:
+            _raw_stream = lambda: raw(device())
+        else:
+            _raw_stream = lambda: torch.cuda.current_stream().cuda_stream
+    return _raw_stream()
+
+
 def call(name, *args):
     lib = library()
     status = getattr(lib, name)(*args)

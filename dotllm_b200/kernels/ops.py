@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..errors import KernelError
+from . import attention_fast, gemm_skinny, gemm_tc
 from . import library as _library
 
 PAGE = 64                      # tokens per cache page (DL_PAGE in csrc/common.cuh)
@@ -23,7 +24,7 @@ def _code(dtype):
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    return _library.current_stream()
 
 
 def _need_cuda(*tensors):
@@ -90,7 +91,6 @@ class PendingProduct:
         rounding of accumulator + stream, as the separate addition has; no [T, N] product is
         written and read back).  False when the sizes belong to the decode kernels or the
         tensors do not fit; nothing has happened then."""
-        from . import gemm_skinny
         x = self.x
         if isinstance(x, ScaledRows) or x.dtype != torch.bfloat16 or not x.is_cuda or x.dim() != 2 \
                 or residual.dtype != torch.float32 or not residual.is_contiguous() \
@@ -113,7 +113,6 @@ class ScaledRows:
         self.shape, self.dtype = data.shape, data.dtype
 
     def row_sums(self):
-        from . import gemm_skinny
         return self.sums, self.sums.numel() // gemm_skinny.sum_stride(self.data.shape[0]), self.width, self.eps
 
     def tensor(self):
@@ -166,7 +165,6 @@ def add_rmsnorm(residual, delta, gain, eps, out_dtype, lazy=False):
 
 
 def _add_product_scaled(residual, product, gain, eps, out_dtype):
-    from . import gemm_skinny
     x = product.x
     rows = x.row_sums() if isinstance(x, ScaledRows) else None
     xt = x.data if rows is not None else x
@@ -279,7 +277,6 @@ def attention(q, k_pool, v_pool, token_seq, token_pos, block_table, n_heads, n_k
                                    or not slopes.is_cuda):
             raise KernelError(f"attention: a score hook's slopes must be contiguous float32 [{n_heads}] on the device")
     if plan is not None and q.dtype == torch.bfloat16 and not score_hook:
-        from . import attention_fast
         if attention_fast.run(q, qs, out, k_pool, v_pool, n_pages, token_seq, token_pos, block_table,
                               n_heads, n_kv_heads, head_dim, float(scale), int(window), plan):
             return out
@@ -297,7 +294,6 @@ def rope_cache_attention(q, k, v, cos, sin, rotary_dim, token_seq, token_pos, bl
     with no rotation, runs as one kernel that rotates q, puts the new keys and values into the
     cache and attends; everything else runs the two kernels one after the other."""
     if plan is not None and q.is_cuda and q.dtype == torch.bfloat16 and k is not None and not score_hook:
-        from . import attention_fast
         out = attention_fast.decode_fresh(q, k, v, cos, sin, rotary_dim, block_table, k_pool, v_pool, n_heads,
                                           n_kv_heads, head_dim, float(scale), int(window), plan)
         if out is not None:
@@ -314,7 +310,6 @@ def qkv_rope_cache(x, w_qkv, cos, sin, rotary_dim, token_seq, token_pos, block_t
     the rotated queries [T, nh*hd] (the rotated keys and the values are in the cache), or None when the
     step is not one the tcgen05 product takes this way (few rows, other head sizes, a partial rotation,
     float32) - the caller then runs ``linear`` and ``rope_cache_attention``.  Same bits as those."""
-    from . import gemm_tc
     q_cols, kv_cols = n_heads * head_dim, n_kv_heads * head_dim
     if isinstance(x, ScaledRows) or not x.is_cuda \
             or not gemm_tc.takes_qkv(x, w_qkv, q_cols, kv_cols, head_dim, rotary_dim, cos, sin, k_pool, v_pool):
@@ -359,7 +354,6 @@ def linear(x, w, out_dtype=None, resident=False, lazy=False):
     reference also uses for its projections (src/DotLLM.Cuda/CudaGemm.cs:29-40)."""
     given, rows = x, None
     if isinstance(x, ScaledRows):
-        from . import gemm_skinny
         if gemm_skinny.takes(x.data, w):
             rows, x = x.row_sums(), x.data
         else:
@@ -375,7 +369,6 @@ def linear(x, w, out_dtype=None, resident=False, lazy=False):
     if lazy and out_dtype == torch.float32 and x.dtype == torch.bfloat16 and M > 0:
         return PendingProduct(given, w, resident)
     if rows is not None:
-        from . import gemm_skinny
         return gemm_skinny.run(x, w, out_dtype, resident=resident, row_sums=rows)
     if x.dtype == torch.float32:
         if out_dtype != torch.float32:
@@ -387,7 +380,6 @@ def linear(x, w, out_dtype=None, resident=False, lazy=False):
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported dtype {x.dtype}")
     if M > 0:
-        from . import gemm_skinny
         y = gemm_skinny.maybe_run(x, w, out_dtype, resident=resident)
         if y is not None:
             return y
@@ -402,7 +394,6 @@ def gated_linear(x, w_gate_up, resident=False):
     kernel for a few rows, the tcgen05 kernel for many.  In float32 the product is followed by
     the gating kernel."""
     if isinstance(x, ScaledRows):
-        from . import gemm_skinny
         if w_gate_up.dim() == 2 and x.shape[1] == w_gate_up.shape[1] and gemm_skinny.takes(x.data, w_gate_up, True):
             _need_cuda(x.data, w_gate_up)
             return gemm_skinny.run(x.data, w_gate_up, x.dtype, fuse_swiglu=True, resident=resident, row_sums=x.row_sums())
@@ -412,11 +403,9 @@ def gated_linear(x, w_gate_up, resident=False):
             or x.shape[1] != w_gate_up.shape[1]:
         raise KernelError(f"gated_linear: x {tuple(x.shape)} does not match W {tuple(w_gate_up.shape)}")
     if x.dtype == torch.bfloat16 and x.shape[0] > 0:
-        from . import gemm_skinny
         y = gemm_skinny.maybe_run(x, w_gate_up, x.dtype, fuse_swiglu=True, resident=resident)
         if y is not None:
             return y
-        from . import gemm_tc
         if gemm_tc.takes(x, w_gate_up, fuse_swiglu=True):
             return gemm_tc.run(x, w_gate_up, x.dtype, fuse_swiglu=True)
     return swiglu(linear(x, w_gate_up))

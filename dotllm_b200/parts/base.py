@@ -126,11 +126,11 @@ def normalised_for(consumer, norm, residual, pending):
     a norm that ``fuses_products`` then lets that product do the addition, and a consumer that
     ``takes_scaled_rows`` (it hands its input straight to ``ops.linear`` / ``ops.gated_linear``) lets its
     first product do the normalisation.  Everyone else gets and gives plain tensors."""
-    from ..kernels import ops
     if pending is None:
         return norm.forward(residual)
     if norm.fuses_products:
         return norm.add_forward(residual, pending, lazy=bool(getattr(consumer, "takes_scaled_rows", False)))
+    from ..kernels import ops
     return norm.add_forward(residual, ops.resolve(pending))
 
 
