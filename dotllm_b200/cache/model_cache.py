@@ -228,6 +228,18 @@ class ModelCache:
             return LayerCacheView("kv", writes, k=g.k[local], v=g.v[local], block_table=block_tables[gi])
         return LayerCacheView("state", writes, state=g.state[local], slots=slots)
 
+    def snapshot_state(self, slots):
+        """Copies of the fixed-size state of the given slots (an int32 device tensor), for a step that
+        has to run twice (the trial run before a graph capture).  Keys and values need none: a second
+        run writes the same values to the same places."""
+        index = slots.long()
+        return [(g, index, g.state[:, index].clone()) for g in self.groups if g.kind == "state"]
+
+    @staticmethod
+    def restore_state(saved):
+        for g, index, values in saved:
+            g.state[:, index] = values
+
     # ---------------------------------------------------------------- admin
     def bytes(self):
         return sum(g.bytes() for g in self.groups)

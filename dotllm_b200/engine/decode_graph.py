@@ -14,6 +14,7 @@ The same kernels run, on the same data, as in an eager step: graphs change launc
 from __future__ import annotations
 
 import time
+import warnings
 
 import numpy as np
 import torch
@@ -131,12 +132,19 @@ class _Captured:
 _capture_streams = {}          # device -> the side stream captures are made on
 
 
+class CaptureFailed(RuntimeError):
+    """The forward pass could not be captured as a CUDA graph (a part waited for the device or read
+    device values on the host).  The cache is as it was before the step."""
+
+
 def capture_forward(model, ctx, cache):
     """The forward pass of ``ctx`` as a CUDA graph: (graph, its logits buffer).  One eager run first:
-    lazy allocations (counters, library workspaces) must not happen inside the capture; it writes the
-    same cache entries the replay will write.  The capture is begun and ended by hand on one side
-    stream per device: the ready-made context manager empties the allocator's device and pinned-host
-    caches at every entry, which cost 1 - 17 ms a capture here and once 1.3 s."""
+    lazy allocations (counters, library workspaces) must not happen inside the capture.  It writes the
+    keys and values the replay will write again; per-sequence state, which a second run would
+    advance twice, is put back after it (`ModelCache.snapshot_state`).  The capture is begun and ended
+    by hand on one side stream per device: the ready-made context manager empties the allocator's
+    device and pinned-host caches at every entry, which cost 1 - 17 ms a capture here and once 1.3 s.
+    Raises CaptureFailed, with the model marked not ``graph_safe``, if the pass cannot be captured."""
     device = model.runtime.device
     side = _capture_streams.get(device)
     if side is None:
@@ -144,17 +152,32 @@ def capture_forward(model, ctx, cache):
     current = torch.cuda.current_stream(device)
     side.wait_stream(current)
     graph = torch.cuda.CUDAGraph()
+    failure = None
     with torch.cuda.stream(side):
+        saved = cache.snapshot_state(ctx.slots)
         model.forward(ctx, cache)
+        cache.restore_state(saved)
         torch.cuda.synchronize(device)
         if ctx.attention_plan is not None:
             ctx.attention_plan.scratch.clear()             # scratch must come from the graph's own pool
         graph.capture_begin()
         try:
             logits = model.forward(ctx, cache)
-        finally:
+        except Exception as exc:                           # noqa: BLE001 - whatever the part raised, the capture must end
+            failure = exc
+        try:
             graph.capture_end()
+        except RuntimeError as exc:
+            failure = failure or exc
     current.wait_stream(side)
+    if failure is not None:
+        model.graph_safe = False
+        torch.cuda.synchronize(device)
+        if ctx.attention_plan is not None:
+            ctx.attention_plan.scratch.clear()
+        raise CaptureFailed(f"a step could not be captured as a CUDA graph ({type(failure).__name__}: {failure}); "
+                            "the model runs its steps eagerly from now on.  A part whose forward waits for the "
+                            "device or reads device values on the host declares graph_safe = False") from failure
     return graph, logits
 
 
@@ -266,7 +289,14 @@ class DecodeGraphs:
                 raise StepError(f"device_ids must be {b} int32 values")
             cap.tokens[:b].copy_(device_ids.reshape(-1), non_blocking=True)
         if fresh:
-            cap.capture(model, cache)
+            try:
+                cap.capture(model, cache)
+            except CaptureFailed as exc:
+                del self.captured[rows]
+                if device_tokens:
+                    raise
+                warnings.warn(str(exc), RuntimeWarning, stacklevel=2)
+                return None if device_ids is not None else self._eager_step(entries)
             self.captures += 1
         cap.graph.replay()
         for s in seqs:
@@ -378,14 +408,18 @@ class StepGraphs:
         return cap.logits
 
     def _capture(self, key, entries):
-        from .step import plan_step
+        from .step import plan_step, run_step
         model, cache = self.model, self.cache
         ctx, new_lengths = plan_step(entries, cache, model.spec.vocab_size, model.spec.max_positions, model.runtime.device)
         # the description moves into a buffer that stays: the graph's kernels read it at every replay
         buffer = torch.empty_like(ctx.packed)
         ctx, new_lengths = plan_step(entries, cache, model.spec.vocab_size, model.spec.max_positions,
                                      model.runtime.device, into=buffer)
-        graph, logits = capture_forward(model, ctx, cache)
+        try:
+            graph, logits = capture_forward(model, ctx, cache)
+        except CaptureFailed as exc:
+            warnings.warn(str(exc), RuntimeWarning, stacklevel=2)
+            return run_step(model, cache, entries)
         graph.replay()                                      # the capture itself computes nothing
         for e, length in zip(entries, new_lengths):
             cache.commit(e.sequence, length)

@@ -144,9 +144,11 @@ class Model:
         With ``graphs`` a step that brings one token per sequence and wants each one's logits is
         replayed as a CUDA graph (captured once per batch size), and any other step is replayed from a
         graph of its exact shape once that shape has been seen twice (prompts of equal lengths, chunks
-        of a fixed size); the returned tensor is then a buffer that the next such step overwrites."""
+        of a fixed size); the returned tensor is then a buffer that the next such step overwrites.
+        A model with a part that is not ``graph_safe`` (it reads device values on the host in its
+        forward) runs eagerly whatever ``graphs`` says, and so does a model whose capture failed once."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        if graphs:
+        if graphs and self.decoder.graph_safe:
             runner = self.decode_graphs(cache)
             if runner.takes(entries):
                 # graphs="lazy" (the generation loop's choice): graphs of a few widths that serve every batch
@@ -183,7 +185,7 @@ class Model:
                              default_stop_ids=self.spec.stop_token_ids, bos_token_id=self.spec.bos_token_id,
                              max_batch=max_batch, fetch=_IdFetcher(self.runtime.device), clock=_EventClock(),
                              ahead_fn=(lambda sequences, ids, rows: self._step_ahead(cache, sequences, ids, rows))
-                             if use_graphs and ahead else None,
+                             if use_graphs and ahead and self.decoder.graph_safe else None,
                              take_rows=lambda logits, keep: logits[torch.tensor(keep, device=logits.device)])
 
     def _step_ahead(self, cache, sequences, ids, rows):

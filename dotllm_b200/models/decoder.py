@@ -32,6 +32,9 @@ class DecoderModel:
         self.final_norm = make_part("norm", spec.final_norm, h, runtime)
         self.head = make_part("head", spec.head, h, runtime)
         self._named_parts += [(spec.final_norm.prefix, self.final_norm), (spec.head.prefix, self.head)]
+        # may a step be captured as a CUDA graph?  Only if every part just launches work (Part.graph_safe)
+        self.graph_safe = all(getattr(part, "graph_safe", True) for _, part in self._named_parts) and \
+            all(getattr(block, "graph_safe", True) for block in self.blocks)
         self.bound = False
 
     # ------------------------------------------------------------- weights

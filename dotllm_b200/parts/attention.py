@@ -40,6 +40,7 @@ class AttentionMixer(Mixer):
         pos = params.get("position") or {"kind": "none", "params": {}}
         self.position = make_part("position_encoding", PartSpec(pos["kind"], pos.get("params", {})),
                                   hidden_size, runtime)
+        self.graph_safe = bool(getattr(self.position, "graph_safe", True))
         score = params.get("score") or {}
         slopes = score.get("slopes")
         if slopes is not None and len(slopes) != self.n_heads:

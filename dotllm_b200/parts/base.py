@@ -83,7 +83,14 @@ class CacheNeed:
 
 
 class Part:
-    """Base of every part: declares tensors, receives them, runs."""
+    """Base of every part: declares tensors, receives them, runs.
+
+    ``graph_safe``: the part's forward only launches work on the current stream, so a step may be
+    captured as a CUDA graph and replayed.  A part that waits for the device or reads device values
+    on the host in its forward (``.tolist()``, ``.item()``, a Python loop over a tensor's values) sets
+    it to False; a model that holds such a part runs every step eagerly."""
+
+    graph_safe = True
 
     def __init__(self, params: dict, hidden_size: int, runtime: Runtime):
         self.params = dict(params)
@@ -185,6 +192,7 @@ class Arrangement:
     needs = ()
     cached_mixer = "mixer"
     narrows = False
+    graph_safe = True            # as Part.graph_safe: the arrangement's own forward waits for nothing
 
     def __init__(self, parts: dict):
         lacking = [n for n in self.needs if n not in parts]

@@ -196,6 +196,11 @@ def toy_parts():
 
         def forward(self, x, step, view):
             u = x.float() @ self.w_in.float().T                      # [T, width]
+            if step.attention_plan.all_single and not self.host_loop:
+                # one token a sequence: all on the device, nothing read back (a step that a graph can hold)
+                slots = view.slots.long()
+                view.state[slots] = self.decay * view.state[slots] + u
+                return (view.state[slots] @ self.w_out.float().T).to(torch.float32)
             out = torch.empty_like(u)
             seqs, slots = step.token_seq.tolist(), view.slots.tolist()
             for t in range(u.shape[0]):                              # tokens of a sequence arrive in order
@@ -203,6 +208,13 @@ def toy_parts():
                 view.state[slot] = self.decay * view.state[slot] + u[t]
                 out[t] = view.state[slot]
             return (out @ self.w_out.float().T).to(torch.float32)
+
+        host_loop = False
+
+    class HostDecayMixer(DecayMixer):
+        """The same mixer reading its indices on the host at every step, and saying so."""
+        graph_safe = False
+        host_loop = True
 
     class ShiftEncoding(PositionEncoding):
         """Adds pos * slope to the first dimension of every query and key head (not a rotation)."""
@@ -236,14 +248,13 @@ def toy_parts():
         def forward(self, x):
             choice = (x.float() @ self.router.float().T).argmax(dim=1)
             out = torch.zeros(x.shape[0], self.hidden_size, dtype=torch.float32, device=x.device)
-            for e in range(self.n_experts):
-                rows = (choice == e).nonzero().flatten()
-                if rows.numel():
-                    h = torch.nn.functional.silu(x[rows].float() @ self.up[e].float().T)
-                    out[rows] = h @ self.down[e].float().T
+            for e in range(self.n_experts):                          # every expert on every row, the chosen one kept
+                h = torch.nn.functional.silu(x.float() @ self.up[e].float().T)
+                out += (choice == e)[:, None] * (h @ self.down[e].float().T)
             return out
 
     register_mixer("toy_decay", DecayMixer)
+    register_mixer("toy_decay_host", HostDecayMixer)
     register_position_encoding("toy_shift", ShiftEncoding)
     register_feed_forward("toy_routed", RoutedFeedForward)
 
@@ -256,26 +267,26 @@ class ToyConfig:
 
     @classmethod
     def from_dict(cls, d):
-        return cls(int(d["vocab_size"]), int(d["hidden_size"]))
+        return cls(int(d["vocab_size"]), int(d["hidden_size"]), (d.get("architectures") or ["ToyForCausalLM"])[0])
 
     def to_dict(self):
         return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size}
 
 
-def toy_spec(cfg):
+def toy_spec(cfg, decay_mixer="toy_decay"):
     from dotllm_b200.config import ModelSpec, PartSpec, ScheduleEntry, pre_norm_layer
     norm = lambda p: PartSpec("rmsnorm", {"eps": 1e-5, "gain_init": ("one_plus_uniform", 0.1)}, p)
     ffn = lambda p, i: PartSpec("gated_mlp", {"intermediate_size": i, "activation": "silu"}, p)
     attn = PartSpec("attention", {"n_heads": 3, "n_kv_heads": 1, "head_dim": 16, "window": 40,
                                   "position": {"kind": "toy_shift", "params": {"head_dim": 16, "slope": 0.01}}},
                     "l0.attn.")
-    decay = PartSpec("toy_decay", {"state_width": 24, "decay": 0.9}, "l1.mix.")
+    decay = PartSpec(decay_mixer, {"state_width": 24, "decay": 0.9}, "l1.mix.")
     routed = PartSpec("toy_routed", {"n_experts": 3, "inner": 40}, "l1.moe.")
     layers = (pre_norm_layer(attn, ffn("l0.ffn.", 80), norm("l0.n1."), norm("l0.n2.")),
               pre_norm_layer(decay, routed, norm("l1.n1."), norm("l1.n2.")))
     # layer 0, layer 1, layer 1 again (its own state), layer 0 again reading the first run's cache
     schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(0, cache_of=0))
-    return ModelSpec("ToyForCausalLM", cfg.hidden_size, cfg.vocab_size, 512,
+    return ModelSpec(cfg.architecture, cfg.hidden_size, cfg.vocab_size, 512,
                      PartSpec("token_embedding", {"vocab_size": cfg.vocab_size}, "emb."), layers, schedule,
                      norm("final."), PartSpec("linear_head", {"vocab_size": cfg.vocab_size}, "head."))
 
@@ -360,6 +371,68 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path):
     out = model.step(cache, [StepEntry(sc, b[:30], list(range(30)))])
     assert float((out.cpu() - rb[:30]).abs().max()) < 5e-5
     cache.check()
+
+
+def _toy_decode(model, w, step_fn, n_steps=14):
+    """Three sequences of unequal lengths: prompts in one eager step, then ``n_steps`` decode steps
+    through ``step_fn(cache, entries)``; every logit against the toy's plain form."""
+    from dotllm_b200 import StepEntry
+    cache = model.new_cache(64 * 8, max_sequences=4)
+    starts = (20, 50, 3)
+    reqs = [tiny_models.random_tokens(n + n_steps, 97, 40 + i) for i, n in enumerate(starts)]
+    refs = [toy_plain(w, r) for r in reqs]
+    seqs = [cache.open_sequence() for _ in reqs]
+    out = model.step(cache, [StepEntry(s, r[:n]) for s, r, n in zip(seqs, reqs, starts)])
+    for i, n in enumerate(starts):
+        assert float((out[i].cpu() - refs[i][n - 1]).abs().max()) < 5e-5
+    for t in range(n_steps):
+        out = step_fn(cache, [StepEntry(s, [r[n + t]]) for s, r, n in zip(seqs, reqs, starts)])
+        for i, n in enumerate(starts):
+            assert float((out[i].cpu() - refs[i][n + t]).abs().max()) < 5e-5, f"step {t}, sequence {i}"
+    cache.check()
+    return cache
+
+
+def test_toy_model_with_state_decodes_through_graphs(tmp_path, monkeypatch):
+    """The toy model's decode steps as CUDA graphs: a graph per batch size, and graphs of a width with
+    an idle row (three sequences in four rows: the idle row works on the cache's idle slot and page).
+    The mixer's state must advance once in the step that captures (the trial run before the capture
+    is undone).  A part that reads device values on the host says so (`graph_safe = False`) and the
+    model then steps eagerly whatever the caller asks; a capture that fails although no part said so
+    ends in a warning and eager steps."""
+    from dotllm_b200 import Model
+    from dotllm_b200.config import register_architecture
+    from dotllm_b200.engine import decode_graph
+    from dotllm_b200.weights import write_random_model
+    toy_parts()
+    register_architecture("ToyForCausalLM", ToyConfig, toy_spec)
+    folder = write_random_model(tmp_path / "toy", ToyConfig(), seed=2, dtype=torch.float32)
+    _, w = plain_llama.read_model_folder(folder)
+    model = Model.load(folder, dtype="float32")
+    assert model.decoder.graph_safe
+    cache = _toy_decode(model, w, lambda cache, entries: model.step(cache, entries, graphs=True).clone())
+    assert list(model.decode_graphs(cache).captured) == [3]
+    cache = _toy_decode(model, w, lambda cache, entries: model.decode_graphs(cache).run(entries, capture_after=1).clone())
+    assert list(model.decode_graphs(cache).captured) == [4]
+
+    # the same model with a mixer that loops over its tokens on the host
+    host_cfg = ToyConfig(architecture="ToyHostForCausalLM")
+    register_architecture("ToyHostForCausalLM", ToyConfig, lambda cfg: toy_spec(cfg, "toy_decay_host"))
+    host_folder = write_random_model(tmp_path / "toy_host", host_cfg, seed=2, dtype=torch.float32)
+    _, hw = plain_llama.read_model_folder(host_folder)
+    host_model = Model.load(host_folder, dtype="float32")
+    assert not host_model.decoder.graph_safe
+    cache = _toy_decode(host_model, hw, lambda cache, entries: host_model.step(cache, entries, graphs=True).clone())
+    assert getattr(cache, "_decode_graphs", None) is None                 # nothing was captured
+
+    # a capture that fails although every part claims to be safe: a warning, eager steps from then on
+    def failing(decoder, ctx, cache):
+        decoder.graph_safe = False
+        raise decode_graph.CaptureFailed("a part waited for the device")
+    monkeypatch.setattr(decode_graph, "capture_forward", failing)
+    with pytest.warns(RuntimeWarning, match="waited for the device"):
+        cache = _toy_decode(model, w, lambda cache, entries: model.step(cache, entries, graphs=True).clone())
+    assert not model.decoder.graph_safe and not model.decode_graphs(cache).captured
 
 
 # ------------------------------------------------------- a second toy: other shapes of layer and cache
