@@ -137,3 +137,32 @@ def test_truncate():
     with pytest.raises(CacheError):
         cache.truncate(s, 66)
     cache.check()
+
+
+def test_idle_slot_and_page_lie_outside_the_pools_and_state_can_be_put_back():
+    """The cache keeps one slot and one page per group that its pools never hand out (the idle rows of
+    a step wider than its batch work there), and the fixed-size state of given slots can be copied
+    and put back (a step that has to run twice must not advance it twice)."""
+    kv = CacheNeed("kv", n_kv_heads=1, head_dim=16)
+    state = CacheNeed("state", state_shape=(3,), state_dtype=torch.float32)
+    cache = ModelCache([kv, state], [None, None], CPU, max_tokens=64 * 4, max_sequences=2)
+    assert cache.idle_slot == 2 and cache.idle_page == 4
+    seqs = [cache.open_sequence() for _ in range(2)]
+    cache.reserve([(s, 128) for s in seqs])
+    assert cache.idle_slot not in {s.slot for s in seqs}
+    assert all(cache.idle_page not in s.pages[g.index] for s in seqs for g in cache.kv_groups)
+    for g in cache.kv_groups:
+        assert g.k.shape[1] == 4 + 1 and g.pages.n_free == 0       # every page of the pool is out, the idle one is not of it
+    group = [g for g in cache.groups if g.kind == "state"][0]
+    assert group.state.shape == (1, 2 + 1, 3)
+    group.state[0, seqs[1].slot] = torch.tensor([1.0, 2.0, 3.0])
+    slots = torch.tensor([seqs[1].slot, cache.idle_slot], dtype=torch.int32)
+    saved = cache.snapshot_state(slots)
+    group.state[0, seqs[1].slot] += 5.0
+    group.state[0, cache.idle_slot] = 9.0
+    group.state[0, seqs[0].slot] = 7.0                              # not among the saved slots: stays
+    cache.restore_state(saved)
+    assert group.state[0, seqs[1].slot].tolist() == [1.0, 2.0, 3.0]
+    assert group.state[0, cache.idle_slot].tolist() == [0.0, 0.0, 0.0]
+    assert group.state[0, seqs[0].slot].tolist() == [7.0, 7.0, 7.0]
+    cache.check()
