@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
                     [--dtype bfloat16|float32] [--shape 8b|1b|13b] [--repeats 5]
     python bench.py --shape 1b --workload unequal     # 64 prompts of 16..2048 tokens in one step, then 256 decode steps
+    python bench.py --workload staggered              # Model.generate while 64 requests end one by one (also --shape 1b)
     python bench.py --impl plain-cpu                  # the plain implementation under tests/, timed on the CPU
 
 A "step" is one decode step: one new token for each of ``batch`` sequences that already hold
@@ -124,8 +125,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--repeats", type=int, default=5, help="repetitions of every timed region (best and CV are reported)")
-    ap.add_argument("--workload", default="steady", choices=["steady", "unequal"],
-                    help="unequal: 64 prompts of 16..2048 tokens in one prefill step, then 256 decode steps")
+    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered"],
+                    help="unequal: 64 prompts of 16..2048 tokens in one prefill step, then 256 decode steps; "
+                         "staggered: Model.generate on 64 prompts whose requests end five steps apart")
     ap.add_argument("--no-generate", action="store_true", help="skip the Model.generate cells")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -341,6 +343,8 @@ def main():
                 "decode_tok_s": round(batch * t.decode_steps / (t.decode_ms / 1e3), 1), "prefill_ms": round(t.prefill_ms, 2),
                 "sampling_ms": round(t.sampling_ms, 2), "cv": spread(times)}
 
+    if args.workload == "staggered":
+        return staggered_workload(args, model, cfg, gen, shape_name, dtype_name)
     if args.workload == "unequal":
         return unequal_workload(args, model, cache, cfg, gen, pk, shape_name, dtype_name, compute_peak, weight_bytes, prefill_flops)
 
@@ -399,6 +403,42 @@ def main():
     if generate:
         line["generate"] = generate
     print(json.dumps(line))
+    return 0
+
+
+def staggered_workload(args, model, cfg, gen, shape_name, dtype_name):
+    """`Model.generate` on 64 prompts of 128 tokens whose requests end one by one, five steps apart
+    (request i generates 40 + 5 i tokens: 12,640 in all, 355 steps, every batch size from 64 to 1):
+    what the loop's ways of stepping cost and give when the batch keeps shrinking.  Three generators,
+    each on a cache of its own, each called four times: without graphs; with graphs of a few widths;
+    with those and every step started before the host has the tokens of the step before it.  The
+    first call of a generator captures its graphs.  Prints its own JSON line."""
+    import torch
+    from dotllm_b200 import InferenceOptions
+    n = 64
+    prompts = [torch.randint(0, cfg.vocab_size, (128,), generator=gen).tolist() for _ in range(n)]
+    options = [InferenceOptions(temperature=0.0, max_tokens=40 + 5 * i, stop_token_ids=[]) for i in range(n)]
+    total = sum(o.max_tokens for o in options)
+    out = {}
+    for label, use_graphs, ahead in (("eager", False, False), ("graphs", True, False), ("graphs_ahead", True, True)):
+        cache = model.new_cache(max_tokens=n * 512, max_sequences=n)
+        generator = model.generator(cache=cache, max_batch=n, use_graphs=use_graphs, ahead=ahead)
+        seconds = []
+        for _ in range(4):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            results = generator.generate(prompts, options)
+            torch.cuda.synchronize()
+            seconds.append(time.perf_counter() - t0)
+            assert sum(r.generated_token_count for r in results) == total
+        runner = getattr(cache, "_decode_graphs", None)
+        out[label] = {"first_call": round(total / seconds[0], 1), "later_calls": round(total / min(seconds[1:]), 1),
+                      "first_call_s": round(seconds[0], 3), "later_call_s": round(min(seconds[1:]), 3),
+                      "graphs": len(runner.captured) if runner is not None else 0, "steps_ahead": generator.ahead_steps}
+        del generator, cache
+    print(json.dumps({"metric": "generate tokens/s while 64 requests end one by one", "model": shape_name, "dtype": dtype_name,
+                      "requests": n, "prompt_tokens": 128, "new_tokens": total, "unit": "tokens/s", **out,
+                      "data": "synthetic: seeded random weights and token ids; greedy, stop tokens off"}))
     return 0
 
 
