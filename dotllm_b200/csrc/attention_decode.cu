@@ -120,7 +120,9 @@ __device__ __forceinline__ uint4 ad_lds128(uint32_t addr) {
     return v;
 }
 
-// Pages of a sequence that its newest token sees (from the page of the first visible key).
+// Pages of a sequence that its newest token sees (from the page of the first visible key).  A length
+// of 0 marks a row that holds nothing (an idle row of a captured step wider than its batch): it has
+// no pages, so no block walks it, nothing is read or written for it and its output row stays as it was.
 __device__ __forceinline__ int ad_first_key(int len, int window) { return (window > 0 && len - window > 0) ? len - window : 0; }
 __device__ __forceinline__ int ad_pages_of(int len, int window) {
     if (len <= 0) return 0;
