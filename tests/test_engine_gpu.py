@@ -330,6 +330,41 @@ def test_generation_that_loses_its_requests_one_by_one(tmp):
     assert generator.ahead_rows_in_vain >= 1
 
 
+@pytest.mark.parametrize("which", ["A", "D"])
+def test_random_generation_workloads_give_the_same_tokens_whatever_the_loop_does(tmp, which):
+    """Seeded random workloads (1 to 40 requests, greedy or drawn with a repetition penalty, with and
+    without stop tokens that some requests meet, batches cut by a batch limit) through the loop
+    without graphs, with graphs of shared widths, and with steps started ahead; every workload twice,
+    so that the second call meets its graphs from the first step on.  float32: the same tokens and
+    the same reasons to end; nothing is left in the cache."""
+    import random
+    from dotllm_b200 import InferenceOptions
+    model, cfg, _, _ = load_pair(tmp, which, torch.float32)
+    vocab, positions = cfg["vocab_size"], cfg["max_position_embeddings"]
+    rng = random.Random(11)
+    for trial in range(6):
+        n = rng.choice([1, 3, 9, 17, 24, 40])
+        prompts = [tiny_models.random_tokens(rng.randint(1, min(60, positions // 3)), vocab, seed=rng.randint(0, 10 ** 6))
+                   for _ in range(n)]
+        stops = [rng.randrange(vocab) for _ in range(rng.choice([0, 3, 12]))]
+        drawn = trial % 2 == 1
+        options = [InferenceOptions(temperature=0.9 if drawn else 0.0, top_k=20 if drawn else 0, seed=rng.randint(0, 999),
+                                    repetition_penalty=rng.choice([1.0, 1.3]), max_tokens=rng.randint(1, min(70, positions - 61)),
+                                    stop_token_ids=stops) for _ in range(n)]
+        max_batch = rng.choice([n, max(1, n // 2)])
+        outs = {}
+        for mode, (use_graphs, ahead) in {"eager": (False, False), "graphs": (True, False), "ahead": (True, True)}.items():
+            cache = model.new_cache(max_tokens=max(n, 4) * 192)
+            generator = model.generator(cache=cache, max_batch=max_batch, use_graphs=use_graphs, ahead=ahead)
+            for _ in range(2):
+                results = generator.generate(prompts, options)
+            outs[mode] = [(r.generated_token_ids, r.finish_reason) for r in results]
+            cache.check()
+            assert not cache.live
+        assert outs["graphs"] == outs["eager"], f"trial {trial}: graphs"
+        assert outs["ahead"] == outs["eager"], f"trial {trial}: steps ahead"
+
+
 def test_a_sampled_request_gives_the_same_tokens_alone_and_in_any_batch(tmp):
     """A request's draws depend on its own seed and step only: the same prompt, options and seed give
     the same tokens alone, as the first of a batch and as the last of another (float32, where the
