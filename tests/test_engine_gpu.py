@@ -330,6 +330,63 @@ def test_generation_that_loses_its_requests_one_by_one(tmp):
     assert generator.ahead_rows_in_vain >= 1
 
 
+@pytest.mark.parametrize("which,dtype", [("B", torch.float32), ("D", torch.float32), ("B", torch.bfloat16), ("D", torch.bfloat16)])
+def test_random_walks_of_steps_rollbacks_and_graph_modes(tmp, which, dtype):
+    """Seeded random walks over one cache: chunks of unequal sizes for some of the sequences, decode
+    steps for others (eagerly, through a graph per batch size, through the loop's shared widths with
+    idle rows), rollbacks to random lengths in between, NaN in every page that nobody holds.  Every
+    logit that a step returns is compared with the plain implementation of the whole sequence."""
+    import random
+    from dotllm_b200 import StepEntry
+    model, cfg, weights, _ = load_pair(tmp, which, dtype)
+    vocab, positions = cfg["vocab_size"], cfg["max_position_embeddings"]
+    rng = random.Random(5)
+    checked = 0
+    for trial in range(4):
+        n = rng.randint(1, 6)
+        cache = model.new_cache(max_tokens=n * ((positions + 63) // 64 * 64), max_sequences=n)
+        cache.fill_free_pages(float("nan"))
+        full = [tiny_models.random_tokens(rng.randint(20, min(positions, 230)), vocab, seed=rng.randint(0, 10 ** 6)) for _ in range(n)]
+        refs = [plain_llama.forward(cfg, weights, f) for f in full]
+        seqs = [cache.open_sequence() for _ in range(n)]
+        for op in range(40):
+            live = [i for i in range(n) if seqs[i].length < len(full[i])]
+            if not live:
+                break
+            kind = rng.random()
+            if kind < 0.15:                                              # roll a sequence back
+                i = rng.randrange(n)
+                if seqs[i].length > 1:
+                    cache.truncate(seqs[i], rng.randint(1, seqs[i].length))
+                    cache.fill_free_pages(float("nan"))
+                continue
+            started = [i for i in live if seqs[i].length > 0]
+            if kind < 0.65 and started:                                  # one token each
+                chosen = rng.sample(started, rng.randint(1, len(started)))
+                entries = [StepEntry(seqs[i], [full[i][seqs[i].length]]) for i in chosen]
+                wanted = [(i, seqs[i].length) for i in chosen]
+                mode = rng.choice([False, True, "lazy", "shared"])
+                if mode == "shared":
+                    out = model.decode_graphs(cache).run(entries, capture_after=1).clone()
+                else:
+                    out = model.step(cache, entries, graphs=mode).clone()
+            else:                                                        # chunks of unequal sizes
+                chosen = rng.sample(live, rng.randint(1, len(live)))
+                entries, wanted, mode = [], [], "chunks"
+                for i in chosen:
+                    start = seqs[i].length
+                    size = min(rng.choice([1, 2, 7, 33, 64, 70]), len(full[i]) - start)
+                    entries.append(StepEntry(seqs[i], full[i][start:start + size], [0, size - 1] if size > 1 else [0]))
+                    wanted += [(i, start), (i, start + size - 1)] if size > 1 else [(i, start)]
+                out = model.step(cache, entries, graphs=rng.choice([False, True])).clone()
+            assert out.shape[0] == len(wanted)
+            for row, (i, p) in enumerate(wanted):
+                assert_close(out[row], refs[i][p], dtype, f"walk {trial}, step {op} ({mode}): sequence {i}, position {p}")
+                checked += 1
+        cache.check()
+    assert checked > 100
+
+
 @pytest.mark.parametrize("which", ["A", "D"])
 def test_random_generation_workloads_give_the_same_tokens_whatever_the_loop_does(tmp, which):
     """Seeded random workloads (1 to 40 requests, greedy or drawn with a repetition penalty, with and
