@@ -121,10 +121,11 @@ def _prefill(q, q_stride, out, k_pool, v_pool, n_pages, block_table, n_heads, n_
         tiles = [(b, r0) for b, n in enumerate(plan.news) for r0 in range(0, n, rows)]
         tiles.sort(key=lambda t: -(plan.starts[t[0]] + min(plan.news[t[0]], t[1] + rows)))
         tile_seq, tile_row0 = [t[0] for t in tiles], [t[1] for t in tiles]
-        host = torch.tensor(tile_seq + tile_row0, dtype=torch.int32)
-        dev = host.pin_memory().to(q.device, non_blocking=True)
-        plan.scratch[("prefill_tiles", rows)] = (dev[:len(tile_seq)], dev[len(tile_seq):], len(tile_seq))
-    tile_seq, tile_row0, n_tiles = plan.scratch[("prefill_tiles", rows)]
+        host = torch.tensor(tile_seq + tile_row0, dtype=torch.int32).pin_memory()
+        dev = host.to(q.device, non_blocking=True)
+        # the pinned list stays with the plan: a captured step copies it again, from this memory, at every replay
+        plan.scratch[("prefill_tiles", rows)] = (dev[:len(tile_seq)], dev[len(tile_seq):], len(tile_seq), host)
+    tile_seq, tile_row0, n_tiles, _ = plan.scratch[("prefill_tiles", rows)]
     if tc:
         _library.call("dl_attention_prefill_tc_bf16", q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0),
                       k_pool.data_ptr(), v_pool.data_ptr(), n_pages, tile_seq.data_ptr(), tile_row0.data_ptr(),

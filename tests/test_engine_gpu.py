@@ -647,6 +647,39 @@ def test_two_layers_at_the_benchmark_models_sizes(tmp_path):
         print(f"real sizes {dtype}: max |logit difference| {worst:.3e}")
 
 
+@pytest.mark.parametrize("which", ["B", "D"])
+def test_a_captured_prompt_step_keeps_what_it_copies_from_the_host(tmp, which):
+    """The bfloat16 prefill attention gets its list of tiles from the host inside the step; a captured
+    step copies it again at every replay, from the same pinned memory.  That memory must stay the
+    step's own: here another step with as many tiles in another order runs between the capture and
+    the replay, and small pinned buffers come and go.  The replay must give the eager step's bits."""
+    from dotllm_b200 import StepEntry
+    model, cfg, _, _ = load_pair(tmp, which, torch.bfloat16)
+    vocab = cfg["vocab_size"]
+    lens, other = (200, 9, 33), (9, 33, 200)
+
+    def step(cache, sizes, seed, graphs):
+        seqs = [cache.open_sequence() for _ in sizes]
+        prompts = [tiny_models.random_tokens(n, vocab, seed=seed + i) for i, n in enumerate(sizes)]
+        out = model.step(cache, [StepEntry(s, p, [0, len(p) - 1]) for s, p in zip(seqs, prompts)], graphs=graphs).clone()
+        for s in seqs:
+            cache.close_sequence(s)
+        return out
+
+    cache = model.new_cache(max_tokens=2048)
+    want = step(cache, lens, 30, False)
+    cache = model.new_cache(max_tokens=2048)
+    step(cache, lens, 10, True)                                  # seen once: eager
+    step(cache, lens, 20, True)                                  # seen twice: captured
+    assert model.step_graphs(cache).captures == 1
+    step(cache, other, 40, False)                                # as many tiles, in another order
+    churn = [torch.full((n,), 7, dtype=torch.int32).pin_memory() for n in (4, 8, 12, 16, 24, 32, 64) for _ in range(4)]
+    del churn
+    got = step(cache, lens, 30, True)                            # replayed
+    assert model.step_graphs(cache).replays == 1
+    assert torch.equal(got, want), f"max diff {(got - want).abs().max()}"
+
+
 def test_prompt_steps_replayed_from_graphs_of_their_shape(tmp):
     """A step of any shape is captured when its shape comes a second time and replayed from then on:
     the same bits as eager steps (float32), for other tokens, other slots and other pages than the
