@@ -279,3 +279,13 @@ def test_steps_ahead_stop_at_the_models_last_position():
     assert out.generated_token_ids == [6, 7, 8, 9] and out.finish_reason == FinishReason.LENGTH
     assert model.steps[-1][0][2] == 7 and len(model.steps) == 4        # no step beyond the last position
     cache.check()
+
+
+def test_widths_of_the_loops_decode_graphs():
+    """A graph of `graph_rows(b)` rows serves b sequences: powers of two up to 16, multiples of 16
+    above, never fewer rows than sequences, and few widths for many batch sizes."""
+    from dotllm_b200.engine.decode_graph import graph_rows
+    assert [graph_rows(b) for b in (1, 2, 3, 4, 5, 8, 9, 16, 17, 32, 33, 48, 49, 64, 65, 200)] == \
+        [1, 2, 4, 4, 8, 8, 16, 16, 32, 32, 48, 48, 64, 64, 80, 208]
+    assert all(graph_rows(b) >= b for b in range(1, 600))
+    assert len({graph_rows(b) for b in range(1, 65)}) == 8
