@@ -4,6 +4,7 @@
                     [--dtype bfloat16|float32] [--shape 8b|1b|13b] [--repeats 5]
     python bench.py --shape 1b --workload unequal     # 64 prompts of 16..2048 tokens in one step, then 256 decode steps
     python bench.py --workload staggered              # Model.generate while 64 requests end one by one (also --shape 1b)
+    python bench.py --workload short-prompts          # time to the first token of single short prompts, eager and captured
     python bench.py --impl plain-cpu                  # the plain implementation under tests/, timed on the CPU
 
 A "step" is one decode step: one new token for each of ``batch`` sequences that already hold
@@ -125,9 +126,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--repeats", type=int, default=5, help="repetitions of every timed region (best and CV are reported)")
-    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered"],
+    ap.add_argument("--workload", default="steady", choices=["steady", "unequal", "staggered", "short-prompts"],
                     help="unequal: 64 prompts of 16..2048 tokens in one prefill step, then 256 decode steps; "
-                         "staggered: Model.generate on 64 prompts whose requests end five steps apart")
+                         "staggered: Model.generate on 64 prompts whose requests end five steps apart; "
+                         "short-prompts: the time to the first token of single prompts of 20 to 1,024 tokens")
     ap.add_argument("--no-generate", action="store_true", help="skip the Model.generate cells")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -343,6 +345,8 @@ def main():
                 "decode_tok_s": round(batch * t.decode_steps / (t.decode_ms / 1e3), 1), "prefill_ms": round(t.prefill_ms, 2),
                 "sampling_ms": round(t.sampling_ms, 2), "cv": spread(times)}
 
+    if args.workload == "short-prompts":
+        return short_prompt_workload(args, model, cfg, gen, shape_name, dtype_name)
     if args.workload == "staggered":
         return staggered_workload(args, model, cfg, gen, shape_name, dtype_name)
     if args.workload == "unequal":
@@ -403,6 +407,39 @@ def main():
     if generate:
         line["generate"] = generate
     print(json.dumps(line))
+    return 0
+
+
+def short_prompt_workload(args, model, cfg, gen, shape_name, dtype_name):
+    """The time from a prompt's tokens on the host to its first token on the host, for single prompts
+    of random lengths in five ranges: stepped eagerly (the host launches every kernel) and through
+    captured steps that prompts of other lengths share (`Model.step(graphs=True)`: a prompt's tokens
+    are filled up to the next multiple of 64, a power of two below, and forgotten after the step).
+    Median of ten prompts after four that warm up and capture.  Prints its own JSON line."""
+    import random
+    import torch
+    from dotllm_b200 import StepEntry
+    rng = random.Random(3)
+    out = {}
+    for lo, hi in ((20, 32), (65, 128), (193, 256), (449, 512), (961, 1024)):
+        cell = {}
+        for label, graphs in (("eager_ms", False), ("captured_ms", True)):
+            cache = model.new_cache(max_tokens=4096)
+            times = []
+            for _ in range(14):
+                prompt = torch.randint(0, cfg.vocab_size, (rng.randint(lo, hi),), generator=gen).tolist()
+                seq = cache.open_sequence()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                first = int(model.step(cache, [StepEntry(seq, prompt)], graphs=graphs).argmax())
+                times.append((time.perf_counter() - t0) * 1e3)
+                cache.close_sequence(seq)
+            assert 0 <= first < cfg.vocab_size
+            cell[label] = round(sorted(times[4:])[5], 3)
+            del cache
+        out[f"{lo}-{hi}"] = cell
+    print(json.dumps({"metric": "time to the first token of one short prompt", "model": shape_name, "dtype": dtype_name, "unit": "ms",
+                      "prompt_tokens": out, "data": "synthetic: seeded random weights, prompt lengths and token ids"}))
     return 0
 
 

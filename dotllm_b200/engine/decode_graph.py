@@ -361,29 +361,57 @@ class _CapturedStep:
 
 
 class StepGraphs:
-    """Captured steps of any shape (prompts, chunks), by exact shape.
+    """Captured steps of any shape (prompts, chunks), by shape.
 
-    A prompt step is some hundred launches with a few microseconds between two dependent ones; replayed
-    from a graph the gaps go (2,048 tokens of the 8B shape: 25.4 -> 23.6 ms).  A graph serves only steps
-    of its own shape (tokens per sequence, starting lengths, wanted rows, table widths: the launch
-    grids depend on them), so this pays where shapes repeat - fixed-size prompt chunks, batches of
-    equal prompts, benchmarks.  A shape is captured when it is seen for the second time; at most
+    A prompt step is some hundred launches, and for a short prompt the host needs longer to launch
+    them than the device to run them (128 tokens of the 8B sizes: 5.5 ms of launches, 3.3 ms of
+    work); replayed from a graph the launches cost nothing and the gaps between dependent kernels go
+    (2,048 tokens: 25.4 -> 23.6 ms).  A graph serves only steps of its own shape (tokens per sequence,
+    starting lengths, number of wanted rows, table widths: the launch grids depend on them).  So that
+    shapes repeat, a sequence's tokens are filled up to a few lengths (`bucket_tokens`: powers of two
+    up to 64, multiples of 64 up to 1,024) with tokens that are forgotten after the step
+    (`_filled_up`); longer prompts run at their own length (fixed-size chunks, batches of equal
+    prompts, benchmarks).  A shape is captured when it is seen for the second time; at most
     ``capacity`` graphs are kept (each holds its own activations), the least recently used goes first.
     The same kernels run on the same data as in an eager step."""
 
-    def __init__(self, model, cache, capacity=4):
+    def __init__(self, model, cache, capacity=16):
         self.model, self.cache, self.capacity = model, cache, capacity
         self.seen = {}
         self.captured = {}                                  # shape key -> _CapturedStep, in order of last use
         self.captures = 0
         self.replays = 0
+        # Filling a sequence's tokens up and forgetting the rest afterwards needs a cache that can forget:
+        # keys and values only (state cannot go back), no window (its pages may be gone by then).
+        self.pads = all(g.kind == "kv" and not g.window for g in cache.groups)
+
+    def _filled_up(self, entries):
+        """The entries at the lengths a captured step runs them (`bucket_tokens`): token 0 after each
+        one's own tokens.  Causal attention keeps those from every earlier row, and they are
+        forgotten after the step (`ModelCache.truncate`), so the wanted logits and the cache are those
+        of the step as it was asked for.  An entry stays as it is where the model's positions end."""
+        from .step import StepEntry, bucket_tokens
+        if not self.pads:
+            return entries
+        out = []
+        for e in entries:
+            n = len(e.tokens)
+            room = bucket_tokens(n)
+            if room == n or e.sequence.length + room > self.model.spec.max_positions:
+                out.append(e)
+                continue
+            want = [n - 1] if e.want is None else list(e.want)
+            out.append(StepEntry(e.sequence, [int(t) for t in e.tokens] + [0] * (room - n), want))
+        return out
 
     def run(self, entries):
         """Logits float32 [wanted, vocab]; a replayed step returns a buffer that the next replay of the
         same shape overwrites."""
+        from ..errors import CacheFullError
         from .step import plan_step, run_step, shape_key
         model, cache = self.model, self.cache
-        key = shape_key(entries, cache)
+        filled = self._filled_up(entries)
+        key = shape_key(filled, cache)
         cap = self.captured.get(key)
         if cap is None:
             self.seen[key] = self.seen.get(key, 0) + 1
@@ -391,10 +419,12 @@ class StepGraphs:
                 if len(self.seen) > 4096:
                     self.seen.clear()
                 return run_step(model, cache, entries)
-            return self._capture(key, entries)
+            return self._capture(key, entries, filled)
         try:
-            _, new_lengths = plan_step(entries, cache, model.spec.vocab_size, model.spec.max_positions,
+            _, new_lengths = plan_step(filled, cache, model.spec.vocab_size, model.spec.max_positions,
                                        model.runtime.device, into=cap.buffer)
+        except CacheFullError:
+            return run_step(model, cache, entries)          # no room for the tokens that fill up: as asked for, eagerly
         except StepError as exc:
             if "does not fit" not in str(exc):
                 raise
@@ -403,17 +433,28 @@ class StepGraphs:
         self.captured[key] = self.captured.pop(key)         # most recently used last
         cap.graph.replay()
         self.replays += 1
-        for e, length in zip(entries, new_lengths):
-            cache.commit(e.sequence, length)
+        self._commit(entries, filled, new_lengths)
         return cap.logits
 
-    def _capture(self, key, entries):
+    def _commit(self, entries, filled, new_lengths):
+        """Record the step and forget the tokens that only filled it up."""
+        for e, f, length in zip(entries, filled, new_lengths):
+            self.cache.commit(e.sequence, length)
+            extra = len(f.tokens) - len(e.tokens)
+            if extra:
+                self.cache.truncate(e.sequence, length - extra)
+
+    def _capture(self, key, entries, filled):
+        from ..errors import CacheFullError
         from .step import plan_step, run_step
         model, cache = self.model, self.cache
-        ctx, new_lengths = plan_step(entries, cache, model.spec.vocab_size, model.spec.max_positions, model.runtime.device)
+        try:
+            ctx, new_lengths = plan_step(filled, cache, model.spec.vocab_size, model.spec.max_positions, model.runtime.device)
+        except CacheFullError:
+            return run_step(model, cache, entries)
         # the description moves into a buffer that stays: the graph's kernels read it at every replay
         buffer = torch.empty_like(ctx.packed)
-        ctx, new_lengths = plan_step(entries, cache, model.spec.vocab_size, model.spec.max_positions,
+        ctx, new_lengths = plan_step(filled, cache, model.spec.vocab_size, model.spec.max_positions,
                                      model.runtime.device, into=buffer)
         try:
             graph, logits = capture_forward(model, ctx, cache)
@@ -421,8 +462,7 @@ class StepGraphs:
             warnings.warn(str(exc), RuntimeWarning, stacklevel=2)
             return run_step(model, cache, entries)
         graph.replay()                                      # the capture itself computes nothing
-        for e, length in zip(entries, new_lengths):
-            cache.commit(e.sequence, length)
+        self._commit(entries, filled, new_lengths)
         while len(self.captured) >= self.capacity:
             self.captured.pop(next(iter(self.captured)))
         self.captured[key] = _CapturedStep(buffer, ctx, graph, logits)

@@ -68,15 +68,31 @@ class StepContext:
     packed: Optional[torch.Tensor] = None     # the one int32 device buffer all of the above are views of
 
 
+PROMPT_PAD_LIMIT = 1024         # prompts (or chunks) of more tokens than this run at their own length in a captured step
+
+
+def bucket_tokens(n):
+    """The length at which a captured step runs ``n`` tokens of a sequence: the next power of two up to
+    64, the next multiple of 64 up to `PROMPT_PAD_LIMIT`, ``n`` itself beyond (and for one token: a
+    decode step).  The tokens that fill it up are run and then forgotten (`StepGraphs`)."""
+    if n <= 1 or n > PROMPT_PAD_LIMIT:
+        return n
+    if n <= 64:
+        return 1 << (n - 1).bit_length()
+    return (n + 63) // 64 * 64
+
+
 def shape_key(entries, cache):
     """What two steps must share for one captured graph to serve both: how many tokens each sequence
-    brings, where it starts, which rows are wanted, and how many pages each block table is wide after
-    the step (launch shapes depend on all of these; the tokens, slots and page ids do not enter)."""
+    brings, where it starts, how many rows of each are wanted (and whether that is every row of the
+    step), and how many pages each block table is wide after the step.  Launch shapes depend on all
+    of these; the tokens, slots, page ids and which rows are wanted are data and do not enter."""
     news = tuple(len(e.tokens) for e in entries)
     starts = tuple(e.sequence.length for e in entries)
-    wants = tuple(None if e.want is None else tuple(int(w) for w in e.want) for e in entries)
+    wants = tuple(1 if e.want is None else len(e.want) for e in entries)
+    every_row = all(e.want is not None and [int(w) for w in e.want] == list(range(len(e.tokens))) for e in entries)
     widths = tuple(max(1, max((s + n + 63) // 64 for s, n in zip(starts, news))) for _ in cache.kv_groups)
-    return news, starts, wants, widths
+    return news, starts, wants, every_row, widths
 
 
 def plan_step(entries, cache, vocab_size, max_positions, device, into=None):

@@ -680,6 +680,52 @@ def test_a_captured_prompt_step_keeps_what_it_copies_from_the_host(tmp, which):
     assert torch.equal(got, want), f"max diff {(got - want).abs().max()}"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompts_of_other_lengths_share_a_captured_step(tmp, dtype):
+    """A captured prompt step runs at a length that several prompt lengths share (the next multiple
+    of 64, a power of two below): the tokens that fill it up come after the prompt's own, so no
+    wanted row sees them, and the cache forgets them after the step.  Prompts of 70, 100, 90, 128 and
+    65 tokens, and batches of three, through one graph each; then decode steps from what the cache
+    holds.  float32: the bits of eager steps.  bfloat16: against the plain implementation."""
+    from dotllm_b200 import StepEntry
+    model, cfg, weights, _ = load_pair(tmp, "D", dtype)
+    vocab = cfg["vocab_size"]
+    singles = [[n] for n in (70, 100, 90, 128, 65)]
+    batches = [[70, 9, 33], [100, 12, 40], [65, 16, 64], [128, 10, 50]]
+
+    def run(graphs):
+        cache = model.new_cache(max_tokens=64 * 16)
+        outs, seed = [], 0
+        for sizes in singles + batches:
+            seqs = [cache.open_sequence() for _ in sizes]
+            reqs = [tiny_models.random_tokens(n + 3, vocab, seed=7000 + (seed := seed + 1)) for n in sizes]
+            entries = [StepEntry(s, r[:n], [0, n - 1]) for s, r, n in zip(seqs, reqs, sizes)]
+            outs.append((reqs, [p for n in sizes for p in (0, n - 1)], model.step(cache, entries, graphs=graphs).clone()))
+            assert [s.length for s in seqs] == list(sizes)
+            assert [len(s.pages[cache.kv_groups[0].index]) for s in seqs] == [(n + 63) // 64 for n in sizes]
+            for t in range(3):                                   # the cache holds the prompt and nothing else
+                step = model.step(cache, [StepEntry(s, [r[n + t]]) for s, r, n in zip(seqs, reqs, sizes)]).clone()
+                outs.append((reqs, [n + t for n in sizes], step))
+            for s in seqs:
+                cache.close_sequence(s)
+            cache.check()
+        if graphs:
+            g = model.step_graphs(cache)
+            assert g.captures == 2 and g.replays == 3 + 2        # one graph for the singles, one for the batches
+        return outs
+
+    graphed = run(True)
+    if dtype == torch.float32:
+        eager = run(False)
+        for (_, _, a), (_, _, b) in zip(eager, graphed):
+            assert torch.equal(a, b), f"max diff {(a - b).abs().max()}"
+    for reqs, positions, got in graphed:
+        refs = [plain_llama.forward(cfg, weights, r) for r in reqs]
+        per = len(positions) // len(reqs)
+        for row, p in enumerate(positions):
+            assert_close(got[row], refs[row // per][p], dtype, f"position {p} of a request of {len(reqs[row // per])} tokens")
+
+
 def test_prompt_steps_replayed_from_graphs_of_their_shape(tmp):
     """A step of any shape is captured when its shape comes a second time and replayed from then on:
     the same bits as eager steps (float32), for other tokens, other slots and other pages than the
