@@ -367,8 +367,9 @@ class StepGraphs:
     them than the device to run them (128 tokens of the 8B sizes: 5.5 ms of launches, 3.3 ms of
     work); replayed from a graph the launches cost nothing and the gaps between dependent kernels go
     (2,048 tokens: 25.4 -> 23.6 ms).  A graph serves only steps of its own shape (tokens per sequence,
-    starting lengths, number of wanted rows, table widths: the launch grids depend on them).  So that
-    shapes repeat, a sequence's tokens are filled up to a few lengths (`bucket_tokens`: powers of two
+    number of wanted rows, table widths: the launch grids depend on them; where a sequence starts is
+    data).  So that shapes repeat, block tables are as wide as sixteen pages need or a multiple of
+    that (`table_widths`), and a sequence's tokens are filled up to a few lengths (`bucket_tokens`: powers of two
     up to 64, multiples of 64 up to 1,024) with tokens that are forgotten after the step
     (`_filled_up`); longer prompts run at their own length (fixed-size chunks, batches of equal
     prompts, benchmarks).  A shape is captured when it is seen for the second time; at most
@@ -422,7 +423,7 @@ class StepGraphs:
             return self._capture(key, entries, filled)
         try:
             _, new_lengths = plan_step(filled, cache, model.spec.vocab_size, model.spec.max_positions,
-                                       model.runtime.device, into=cap.buffer)
+                                       model.runtime.device, into=cap.buffer, widths=key[-1])
         except CacheFullError:
             return run_step(model, cache, entries)          # no room for the tokens that fill up: as asked for, eagerly
         except StepError as exc:
@@ -449,13 +450,14 @@ class StepGraphs:
         from .step import plan_step, run_step
         model, cache = self.model, self.cache
         try:
-            ctx, new_lengths = plan_step(filled, cache, model.spec.vocab_size, model.spec.max_positions, model.runtime.device)
+            ctx, new_lengths = plan_step(filled, cache, model.spec.vocab_size, model.spec.max_positions, model.runtime.device,
+                                         widths=key[-1])
         except CacheFullError:
             return run_step(model, cache, entries)
         # the description moves into a buffer that stays: the graph's kernels read it at every replay
         buffer = torch.empty_like(ctx.packed)
         ctx, new_lengths = plan_step(filled, cache, model.spec.vocab_size, model.spec.max_positions,
-                                     model.runtime.device, into=buffer)
+                                     model.runtime.device, into=buffer, widths=key[-1])
         try:
             graph, logits = capture_forward(model, ctx, cache)
         except CaptureFailed as exc:

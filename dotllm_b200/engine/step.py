@@ -43,8 +43,8 @@ class AttentionPlan:
     cu_new: torch.Tensor          # int32 [B+1] offsets of each sequence's tokens in the packed step
     seq_total: torch.Tensor       # int32 [B] length after the step; 0: an idle row (a captured step wider than
                                   # its batch), which attends to nothing and whose output nobody reads
-    starts: list = field(default_factory=list)
-    news: list = field(default_factory=list)
+    starts: list = field(default_factory=list)    # host copies of seq_start and seq_new, for scheduling only: a step replayed
+    news: list = field(default_factory=list)      # from a graph carries the starts of the step it was captured from
     scratch: dict = field(default_factory=dict)
 
 
@@ -82,24 +82,36 @@ def bucket_tokens(n):
     return (n + 63) // 64 * 64
 
 
+TABLE_WIDTH_STEP = 16           # a captured step's block tables are a multiple of this many pages wide
+
+
 def shape_key(entries, cache):
     """What two steps must share for one captured graph to serve both: how many tokens each sequence
-    brings, where it starts, how many rows of each are wanted (and whether that is every row of the
-    step), and how many pages each block table is wide after the step.  Launch shapes depend on all
-    of these; the tokens, slots, page ids and which rows are wanted are data and do not enter."""
+    brings, how many rows of each are wanted (and whether that is every row of the step), and how
+    wide the block tables are (`table_widths`).  Launch shapes depend on these; the tokens, where a
+    sequence starts, slots, page ids and which rows are wanted are data and do not enter."""
     news = tuple(len(e.tokens) for e in entries)
-    starts = tuple(e.sequence.length for e in entries)
     wants = tuple(1 if e.want is None else len(e.want) for e in entries)
     every_row = all(e.want is not None and [int(w) for w in e.want] == list(range(len(e.tokens))) for e in entries)
-    widths = tuple(max(1, max((s + n + 63) // 64 for s, n in zip(starts, news))) for _ in cache.kv_groups)
-    return news, starts, wants, every_row, widths
+    return news, wants, every_row, table_widths(entries, cache)
 
 
-def plan_step(entries, cache, vocab_size, max_positions, device, into=None):
+def table_widths(entries, cache):
+    """Columns of a captured step's block table in every kv group: the pages of the longest sequence
+    after the step, rounded up to `TABLE_WIDTH_STEP` (unused columns hold -1), so that a step's shape
+    does not change with every page a sequence grows by."""
+    pages = max(1, max((e.sequence.length + len(e.tokens) + 63) // 64 for e in entries))
+    wide = (pages + TABLE_WIDTH_STEP - 1) // TABLE_WIDTH_STEP * TABLE_WIDTH_STEP
+    return tuple(wide for _ in cache.kv_groups)
+
+
+def plan_step(entries, cache, vocab_size, max_positions, device, into=None, widths=None):
     """Validate the entries, reserve cache room, and build the device-side description with one
     host-to-device copy.  Returns (StepContext, new lengths).  Per-token work is done on arrays, not
     in Python loops: a step may bring tens of thousands of prompt tokens.  ``into``: an int32 device
-    buffer of exactly the description's size that receives it instead of a fresh one."""
+    buffer of exactly the description's size that receives it instead of a fresh one.  ``widths``:
+    columns of the block table of every kv group, in the groups' order (at least the pages of the
+    longest sequence; default: exactly those)."""
     if not entries:
         raise StepError("a step needs at least one sequence")
     B = len(entries)
@@ -149,8 +161,12 @@ def plan_step(entries, cache, vocab_size, max_positions, device, into=None):
     R = int(want_rows.size)
     seqs = [e.sequence for e in entries]
     tables = {}
-    for g in cache.kv_groups:
+    for gi, g in enumerate(cache.kv_groups):
         width = max(1, max(len(s.pages[g.index]) for s in seqs))
+        if widths is not None:
+            if widths[gi] < width:
+                raise StepError(f"a block table of {widths[gi]} columns does not fit sequences of {width} pages")
+            width = widths[gi]
         rows = np.full((B, width), -1, dtype=np.int64)
         for r, s in enumerate(seqs):
             pages = s.pages[g.index]

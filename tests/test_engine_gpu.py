@@ -726,6 +726,44 @@ def test_prompts_of_other_lengths_share_a_captured_step(tmp, dtype):
             assert_close(got[row], refs[row // per][p], dtype, f"position {p} of a request of {len(reqs[row // per])} tokens")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_chunks_that_continue_a_sequence_share_captured_steps(tmp, dtype):
+    """One to three sequences brought in four chunks each (64 tokens, then 33 - 64, 5 - 8 and 65 - 128
+    more): the chunk lengths of a round share captured steps with the rounds before and with each
+    other (64, 64, 8, 128 rows a sequence; where a chunk starts is data of the step), a chunk's filling
+    lies beyond its own tokens and is forgotten before the next chunk starts where the sequence
+    really ends.  Three logits of every chunk against the plain
+    implementation of the whole sequence."""
+    import random
+    from dotllm_b200 import StepEntry
+    model, cfg, weights, _ = load_pair(tmp, "D", dtype)
+    vocab = cfg["vocab_size"]
+    rng = random.Random(9)
+    cache = model.new_cache(max_tokens=64 * 24)
+    for trial in range(8):
+        n = 1 + trial % 3
+        sizes = [[64, rng.randint(33, 64), rng.randint(5, 8), rng.randint(65, 128)] for _ in range(n)]
+        full = [tiny_models.random_tokens(sum(s), vocab, seed=rng.randint(0, 10 ** 6)) for s in sizes]
+        refs = [plain_llama.forward(cfg, weights, f) for f in full]
+        seqs = [cache.open_sequence() for _ in range(n)]
+        for c in range(4):
+            entries, wanted = [], []
+            for i in range(n):
+                start, size = seqs[i].length, sizes[i][c]
+                entries.append(StepEntry(seqs[i], full[i][start:start + size], [0, size // 2, size - 1]))
+                wanted += [(i, start), (i, start + size // 2), (i, start + size - 1)]
+            out = model.step(cache, entries, graphs=True).clone()
+            for row, (i, p) in enumerate(wanted):
+                assert_close(out[row], refs[i][p], dtype, f"round {trial}, chunk {c}: sequence {i}, position {p}")
+            assert [s.length for s in seqs] == [sum(sizes[i][:c + 1]) for i in range(n)]
+        for s in seqs:
+            cache.close_sequence(s)
+        cache.check()
+    g = model.step_graphs(cache)
+    # three batch sizes, three chunk lengths each (64, 8 and 128 rows a sequence: where a chunk starts is data)
+    assert g.captures == 9 and g.replays == 14
+
+
 def test_prompt_steps_replayed_from_graphs_of_their_shape(tmp):
     """A step of any shape is captured when its shape comes a second time and replayed from then on:
     the same bits as eager steps (float32), for other tokens, other slots and other pages than the
