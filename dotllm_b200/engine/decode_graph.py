@@ -373,11 +373,12 @@ class StepGraphs:
     up to 64, multiples of 64 up to 1,024) with tokens that are forgotten after the step
     (`_filled_up`); longer prompts run at their own length (fixed-size chunks, batches of equal
     prompts, benchmarks).  A shape is captured when it is seen for the second time; at most
-    ``capacity`` graphs are kept (each holds its own activations), the least recently used goes first.
+    ``capacity`` graphs and ``row_budget`` token rows in all are kept (a graph holds the activations of
+    its rows), the least recently used goes first.
     The same kernels run on the same data as in an eager step."""
 
-    def __init__(self, model, cache, capacity=16):
-        self.model, self.cache, self.capacity = model, cache, capacity
+    def __init__(self, model, cache, capacity=16, row_budget=1 << 15):
+        self.model, self.cache, self.capacity, self.row_budget = model, cache, capacity, row_budget
         self.seen = {}
         self.captured = {}                                  # shape key -> _CapturedStep, in order of last use
         self.captures = 0
@@ -465,7 +466,10 @@ class StepGraphs:
             return run_step(model, cache, entries)
         graph.replay()                                      # the capture itself computes nothing
         self._commit(entries, filled, new_lengths)
-        while len(self.captured) >= self.capacity:
+        # room for the new graph: at most `capacity` graphs and `row_budget` token rows in all (a graph
+        # holds the activations of its rows), the least recently used go first
+        while self.captured and (len(self.captured) >= self.capacity or
+                                 sum(c.ctx.n_tokens for c in self.captured.values()) + ctx.n_tokens > self.row_budget):
             self.captured.pop(next(iter(self.captured)))
         self.captured[key] = _CapturedStep(buffer, ctx, graph, logits)
         self.captures += 1
